@@ -1,0 +1,200 @@
+// Grouped-query attention over the paged cache: the kernel that prepares q, k
+// and v (per-head RMSNorm, rotation, append to the cache) and the generic
+// attention kernel that serves every head size, dtype, window and cut of the
+// token stream.
+//
+// Cache layout of one layer: pool[page][2 (K, V)][kv head][page_size][hd].
+// A sequence's token t lies in page table[b][t / page_size] at row
+// t % page_size.  page_size is a power of two.
+//
+// Reference: per-head norm of q and k with one [hd] weight and the layer
+// norms' eps, before the rotation (crates/mivi-model/src/transformer.rs:81-96);
+// rotation of pairs (2i, 2i+1) by pos * theta^(-2i/hd)
+// (crates/mivi-core/src/rope.rs:59-61, 219-229); store k and v at pos
+// (transformer.rs:108); head h reads kv head h / (nh / nkv); scores
+// q.k / sqrt(hd) over t <= pos, running-maximum softmax in 32-bit, weighted
+// sum of v, division by the sum at the end (transformer.rs:114-167, 293-298).
+#include "common.cuh"
+
+#define MV_MAX_HEAD_DIM 256
+
+// ----------------------------------------------------- q/k norm, rope, append
+// One warp per (token, head slot); head slots are nh query heads, then nkv key
+// heads, then nkv value heads, as they lie in a row of the fused projection.
+template <typename T>
+__global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __restrict__ wq,
+                                  const float* __restrict__ wk, float eps,
+                                  const float* __restrict__ inv_freq, int half_split,
+                                  const int* __restrict__ positions, const int* __restrict__ seq_of,
+                                  const int* __restrict__ page_table, int table_stride, int page_shift,
+                                  T* __restrict__ pool, long long page_stride, int append,
+                                  T* __restrict__ q_out, int N, int nh, int nkv, int hd) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int slots_per_tok = nh + 2 * nkv;
+    if (warp >= N * slots_per_tok) return;
+    const int n = warp / slots_per_tok, hs = warp - n * slots_per_tok;
+    const float* row = qkv + (size_t)n * slots_per_tok * hd + (size_t)hs * hd;
+    const int pos = positions[n];
+    const int half = hd >> 1;
+    const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)n * nh * hd + (size_t)hs * hd;
+    } else {
+        if (!append) return;
+        const int g = is_k ? hs - nh : hs - nh - nkv;
+        const int page_size = 1 << page_shift;
+        const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
+        dst = pool + (size_t)page * page_stride + (size_t)(is_k ? 0 : 1) * nkv * page_size * hd +
+              ((size_t)g * page_size + (pos & (page_size - 1))) * hd;
+    }
+    if (!is_q && !is_k) {                       // value head: copy
+        for (int d = lane; d < hd; d += 32) dst[d] = mv_from_f32<T>(row[d]);
+        return;
+    }
+    const float* w = is_q ? wq : wk;
+    float scale = 1.f;
+    if (w) {
+        float ss = 0.f;
+        for (int d = lane; d < hd; d += 32) ss = fmaf(row[d], row[d], ss);
+        ss = mv_warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    for (int i = lane; i < half; i += 32) {
+        const int ia = half_split ? i : 2 * i;
+        const int ib = half_split ? i + half : 2 * i + 1;
+        float a = row[ia], b = row[ib];
+        if (w) { a = a * scale * w[ia]; b = b * scale * w[ib]; }
+        if (inv_freq) {
+            float s, c;
+            sincosf((float)pos * inv_freq[i], &s, &c);
+            const float ra = a * c - b * s, rb = a * s + b * c;
+            a = ra; b = rb;
+        }
+        dst[ia] = mv_from_f32<T>(a);
+        dst[ib] = mv_from_f32<T>(b);
+    }
+}
+
+MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, float eps,
+                         const float* inv_freq, int half_split, const int* positions,
+                         const int* seq_of, const int* page_table, int table_stride, int page_size,
+                         void* pool, long long page_stride, int append, void* q_out, int dtype, int N,
+                         int nh, int nkv, int hd, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (hd % 2 || hd > MV_MAX_HEAD_DIM || (page_size & (page_size - 1))) return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    const long long warps = (long long)N * (nh + 2 * nkv);
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
+    if (dtype == MV_DT_BF16)
+        qk_prepare_kernel<<<blocks, threads, 0, stream>>>(
+            qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
+            page_shift, (__nv_bfloat16*)pool, page_stride, append, (__nv_bfloat16*)q_out, N, nh, nkv, hd);
+    else
+        qk_prepare_kernel<<<blocks, threads, 0, stream>>>(
+            qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
+            page_shift, (float*)pool, page_stride, append, (float*)q_out, N, nh, nkv, hd);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------ attention
+// One warp per (token, query head).  Keys are taken 32 at a time: each lane
+// scores one key (its row of hd elements is contiguous), the warp agrees on the
+// running maximum, then the lanes split the head's elements for the weighted
+// sum of the values.  Works for every hd that is a multiple of 8 up to 256.
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_stride,
+                         const int* __restrict__ page_table, int table_stride, int page_shift,
+                         const int* __restrict__ positions, const int* __restrict__ seq_of,
+                         T* __restrict__ o, int N, int nh, int nkv, int hd, float scale, int window) {
+    __shared__ float qs[4][MV_MAX_HEAD_DIM];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 4 + wib;
+    if (warp >= (long long)N * nh) return;
+    const int n = (int)(warp / nh), h = (int)(warp - (long long)n * nh);
+    const int g = h / (nh / nkv);
+    const int pos = positions[n];
+    const int page_size = 1 << page_shift;
+    const int* table = page_table + (size_t)seq_of[n] * table_stride;
+    const size_t v_off = (size_t)nkv * page_size * hd;
+
+    const T* qrow = q + (size_t)n * nh * hd + (size_t)h * hd;
+    for (int d = lane; d < hd; d += 32) qs[wib][d] = mv_to_f32(qrow[d]) * scale;
+    __syncwarp();
+
+    float acc[MV_MAX_HEAD_DIM / 32];
+#pragma unroll
+    for (int r = 0; r < MV_MAX_HEAD_DIM / 32; ++r) acc[r] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+
+    for (int t0 = lo; t0 <= pos; t0 += 32) {
+        const int t = t0 + lane;
+        const bool valid = t <= pos;
+        const T* krow = nullptr;
+        float s = -INFINITY;
+        if (valid) {
+            const int page = table[t >> page_shift];
+            krow = pool + (size_t)page * page_stride + ((size_t)g * page_size + (t & (page_size - 1))) * hd;
+            float dot = 0.f;
+            for (int d = 0; d < hd; d += 8) {
+                float kv[8];
+                mv_load8(krow + d, kv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dot = fmaf(qs[wib][d + e], kv[e], dot);
+            }
+            s = dot;
+        }
+        const float m_new = fmaxf(m, mv_warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);          // 0 on the first chunk (m = -inf)
+        l = l * corr + mv_warp_sum(p);
+#pragma unroll
+        for (int r = 0; r < MV_MAX_HEAD_DIM / 32; ++r) acc[r] *= corr;
+        m = m_new;
+        const int cnt = min(32, pos - t0 + 1);
+        const unsigned long long kaddr = (unsigned long long)krow;
+        for (int j = 0; j < cnt; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            const T* vrow = (const T*)__shfl_sync(0xffffffffu, kaddr, j) + v_off;
+#pragma unroll
+            for (int r = 0; r < MV_MAX_HEAD_DIM / 32; ++r) {
+                const int d = lane + 32 * r;
+                if (d < hd) acc[r] = fmaf(pj, mv_to_f32(vrow[d]), acc[r]);
+            }
+        }
+    }
+    const float inv = 1.0f / l;
+    T* orow = o + (size_t)n * nh * hd + (size_t)h * hd;
+#pragma unroll
+    for (int r = 0; r < MV_MAX_HEAD_DIM / 32; ++r) {
+        const int d = lane + 32 * r;
+        if (d < hd) orow[d] = mv_from_f32<T>(acc[r] * inv);
+    }
+}
+
+MV_API int mv_attention_generic(const void* q, const void* pool, long long page_stride,
+                                const int* page_table, int table_stride, int page_size,
+                                const int* positions, const int* seq_of, void* o, int dtype, int N,
+                                int nh, int nkv, int hd, float scale, int window, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (hd % 8 || hd > MV_MAX_HEAD_DIM || nh % nkv || (page_size & (page_size - 1)))
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    const unsigned blocks = (unsigned)(((long long)N * nh + 3) / 4);
+    if (dtype == MV_DT_BF16)
+        attention_generic_kernel<<<blocks, 128, 0, stream>>>(
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_stride, page_table, table_stride,
+            page_shift, positions, seq_of, (__nv_bfloat16*)o, N, nh, nkv, hd, scale, window);
+    else
+        attention_generic_kernel<<<blocks, 128, 0, stream>>>(
+            (const float*)q, (const float*)pool, page_stride, page_table, table_stride, page_shift,
+            positions, seq_of, (float*)o, N, nh, nkv, hd, scale, window);
+    return mv_launch_status();
+}

@@ -1,0 +1,85 @@
+// Embedding gather, RMSNorm and SwiGLU: the memory-bound row kernels.
+//
+// Each is the device form of a loop of the reference engine: the embedding
+// row copy (crates/mivi-model/src/model.rs:355-366), rms_norm
+// (crates/mivi-core/src/simd/norm.rs:38-72) and swiglu
+// (crates/mivi-core/src/math.rs:94-98).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tok,
+                             float* __restrict__ x, int H) {
+    const int n = blockIdx.x;
+    const T* row = table + (size_t)tok[n] * H;
+    float* out = x + (size_t)n * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) out[h] = mv_to_f32(row[h]);
+}
+
+MV_API int mv_embed(const void* table, int table_dtype, const int* tok, float* x, int N, int H,
+                    cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == MV_DT_BF16)
+        embed_kernel<<<N, threads, 0, stream>>>((const __nv_bfloat16*)table, tok, x, H);
+    else
+        embed_kernel<<<N, threads, 0, stream>>>((const float*)table, tok, x, H);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------ rmsnorm
+// y[i, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w, r = rows ? rows[i] : i.
+// Statistics in 32-bit whatever the output type.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               TO* __restrict__ y, const int* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const float* xr = x + (size_t)r * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = xr[h];
+        ss = fmaf(v, v, ss);
+    }
+    ss = mv_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* yr = y + (size_t)i * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) yr[h] = mv_from_f32<TO>(xr[h] * scale * w[h]);
+}
+
+MV_API int mv_rmsnorm(const float* x, const float* w, void* y, int y_dtype, const int* rows,
+                      int n_rows, int H, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (y_dtype == MV_DT_BF16)
+        rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows, H, eps);
+    else
+        rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, w, (float*)y, rows, H, eps);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------- swiglu
+// h[n, f] = silu(gu[n, f]) * gu[n, F + f], silu(a) = a / (1 + e^-a).
+template <typename TO>
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ h, long long total, int F) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / F;
+    const int f = (int)(i - n * F);
+    const float a = gu[n * 2 * F + f];
+    const float b = gu[n * 2 * F + F + f];
+    h[i] = mv_from_f32<TO>(a / (1.0f + expf(-a)) * b);
+}
+
+MV_API int mv_swiglu(const float* gu, void* h, int h_dtype, int N, int F, cudaStream_t stream) {
+    const long long total = (long long)N * F;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (h_dtype == MV_DT_BF16)
+        swiglu_kernel<<<blocks, threads, 0, stream>>>(gu, (__nv_bfloat16*)h, total, F);
+    else
+        swiglu_kernel<<<blocks, threads, 0, stream>>>(gu, (float*)h, total, F);
+    return mv_launch_status();
+}

@@ -1,0 +1,337 @@
+// Sampling of one token for each row of logits, on the device, in the order of
+// the reference's sampler (crates/mivi-model/src/sampler.rs:92-136):
+// penalties over the recent tokens (222-260), greedy if temperature <= 0 (the
+// first maximum wins, 305-315), temperature (282-287), min-p (263-279), top-k
+// keeping ties at the k-th value (290-302), softmax, then the nucleus
+// (150-218) or the plain categorical draw (138-148).
+//
+// One block of 1024 threads per row; the row is copied to scratch first, so the
+// caller's logits stay as they are.
+//
+// Two things are this library's own.  (1) The uniform number: the reference
+// keeps one xorshift64* state for its single sequence (sampler.rs:70-76); a
+// batch needs draws that do not depend on what else is in the batch, so the
+// draw of a sequence at a decoding step is a splitmix64 hash of
+// (seed, stream, step), top 24 bits as in the reference.  (2) Probability mass
+// is summed as 40-bit fixed point in 64-bit integers: integer sums do not
+// depend on the order of the additions, so the result is the same in every
+// run and for every thread layout.  The nucleus is the shortest prefix in
+// descending probability (ties: lower index first) whose mass reaches top_p;
+// the draw walks the kept tokens in index order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+constexpr int RECENT_MAX = 64;
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ unsigned draw24(unsigned long long seed, unsigned long long stream,
+                                           unsigned long long step) {
+    unsigned long long z = mix64(seed);
+    z = mix64(z ^ (stream * 0xD1342543DE82EF95ull));
+    z = mix64(z ^ (step * 0xA24BAED4963EE407ull));
+    return (unsigned)(z >> 40);
+}
+// floats -> unsigned keys with the same order
+__device__ __forceinline__ unsigned order_key(float x) {
+    const unsigned u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long fixed40(float e) {
+    return (unsigned long long)(e * 1099511627776.0f);       // e in [0, 1]
+}
+
+struct Shared {
+    unsigned cnt[256];
+    unsigned long long mass[256];
+    float fred[33];
+    int ired[33];
+    unsigned long long wsum[33];
+    unsigned sel_prefix;
+    unsigned sel_remaining;
+    unsigned long long sel_mass_above;
+    int result;
+};
+
+__device__ float block_max(float v, Shared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = mv_warp_max(v);
+    __syncthreads();
+    if (lane == 0) sh.fred[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = sh.fred[lane];
+        t = mv_warp_max(t);
+        if (lane == 0) sh.fred[32] = t;
+    }
+    __syncthreads();
+    return sh.fred[32];
+}
+
+// exclusive prefix sum over the block in thread order; *total gets the sum
+__device__ unsigned long long block_excl_scan(unsigned long long v, Shared& sh, unsigned long long* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned long long inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    __syncthreads();
+    if (lane == 31) sh.wsum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long w = sh.wsum[lane];
+        unsigned long long winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
+        }
+        sh.wsum[lane] = winc - w;
+        if (lane == 31) sh.wsum[32] = winc;
+    }
+    __syncthreads();
+    *total = sh.wsum[32];
+    return sh.wsum[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
+              float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
+              float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
+              unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
+              int* __restrict__ out) {
+    __shared__ Shared sh;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const float* src = logits + (size_t)b * ld;
+    float* x = work + (size_t)b * V;
+
+    for (int i = tid; i < V; i += THREADS) x[i] = src[i];
+    __syncthreads();
+
+    // 1. penalties, once per distinct recent token
+    const int nr = n_recent ? min(n_recent[b], RECENT_MAX) : 0;
+    const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
+    if (pen && tid < nr) {
+        const int* rc = recent + (size_t)b * RECENT_MAX;
+        const int tok = rc[tid];
+        bool first = tok >= 0 && tok < V;
+        int count = 0;
+        for (int j = 0; j < nr; ++j) {
+            if (rc[j] == tok) {
+                if (j < tid) first = false;
+                ++count;
+            }
+        }
+        if (first) {
+            float v = x[tok];
+            if (rep_pen > 0.f && rep_pen != 1.f) v = v > 0.f ? v / rep_pen : v * rep_pen;
+            if (pres_pen != 0.f) v -= pres_pen;
+            if (freq_pen != 0.f) v -= freq_pen * (float)count;
+            x[tok] = v;
+        }
+    }
+    __syncthreads();
+
+    // 2. greedy: the first maximum wins
+    if (temperature <= 0.f) {
+        float best = -INFINITY;
+        int besti = 0x7fffffff;
+        for (int i = tid; i < V; i += THREADS) {
+            const float v = x[i];
+            if (v > best) { best = v; besti = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+        }
+        if ((tid & 31) == 0) { sh.fred[tid >> 5] = best; sh.ired[tid >> 5] = besti; }
+        __syncthreads();
+        if (tid < 32) {
+            best = sh.fred[tid]; besti = sh.ired[tid];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+                if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+            }
+            if (tid == 0) out[b] = besti == 0x7fffffff ? 0 : besti;
+        }
+        return;
+    }
+
+    // 3. temperature, maximum
+    const float inv_t = 1.0f / temperature;
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += THREADS) {
+        const float v = x[i] * inv_t;
+        x[i] = v;
+        mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, sh);
+
+    // 4. min-p
+    if (min_p > 0.f && min_p < 1.f) {
+        const float thr = mx + logf(min_p);
+        for (int i = tid; i < V; i += THREADS)
+            if (x[i] < thr) x[i] = -INFINITY;
+        __syncthreads();
+    }
+
+    // 5. top-k: radix select of the k-th largest value, ties at it are kept
+    if (top_k > 0 && top_k < V) {
+        if (tid == 0) { sh.sel_prefix = 0; sh.sel_remaining = (unsigned)top_k; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            if (tid < 256) sh.cnt[tid] = 0;
+            __syncthreads();
+            const unsigned prefix = sh.sel_prefix;
+            const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = tid; i < V; i += THREADS) {
+                const unsigned key = order_key(x[i]);
+                if ((key & himask) == prefix) atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned rem = sh.sel_remaining;
+                int bin = 255;
+                for (; bin > 0; --bin) {
+                    if (sh.cnt[bin] >= rem) break;
+                    rem -= sh.cnt[bin];
+                }
+                sh.sel_prefix = prefix | ((unsigned)bin << shift);
+                sh.sel_remaining = rem;
+            }
+            __syncthreads();
+        }
+        const unsigned cut = sh.sel_prefix;
+        for (int i = tid; i < V; i += THREADS)
+            if (order_key(x[i]) < cut) x[i] = -INFINITY;
+        __syncthreads();
+    }
+
+    // 6. softmax masses in fixed point; each thread owns a run of indices
+    const int seg = (V + THREADS - 1) / THREADS;
+    const int i0 = min(V, tid * seg), i1 = min(V, i0 + seg);
+    unsigned long long mine = 0;
+    for (int i = i0; i < i1; ++i) {
+        const float v = x[i];
+        const float e = v == -INFINITY ? 0.f : expf(v - mx);
+        x[i] = e;
+        mine += fixed40(e);
+    }
+    unsigned long long total;
+    block_excl_scan(mine, sh, &total);
+
+    // 7. nucleus: the value at which the descending mass reaches top_p
+    float cut_e = 0.f;                    // keep e > cut_e, and the first n_take of e == cut_e
+    unsigned long long n_take = ~0ull;
+    unsigned long long kept = total;
+    if (top_p < 1.0f) {
+        const unsigned long long target = (unsigned long long)((double)top_p * (double)total);
+        if (tid == 0) { sh.sel_prefix = 0; sh.sel_mass_above = 0; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            if (tid < 256) { sh.mass[tid] = 0; sh.cnt[tid] = 0; }
+            __syncthreads();
+            const unsigned prefix = sh.sel_prefix;
+            const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = i0; i < i1; ++i) {
+                const float e = x[i];
+                const unsigned key = __float_as_uint(e);          // e >= 0: bit order is value order
+                if (e > 0.f && (key & himask) == prefix) {
+                    atomicAdd(&sh.mass[(key >> shift) & 255u], fixed40(e));
+                    atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long above = sh.sel_mass_above;
+                int bin = 255;
+                for (; bin > 0; --bin) {
+                    if (sh.cnt[bin] && above + sh.mass[bin] >= target) break;
+                    above += sh.mass[bin];
+                }
+                sh.sel_prefix = prefix | ((unsigned)bin << shift);
+                sh.sel_mass_above = above;
+            }
+            __syncthreads();
+        }
+        cut_e = __uint_as_float(sh.sel_prefix);
+        const unsigned long long above = sh.sel_mass_above;
+        const unsigned long long qc = fixed40(cut_e);
+        if (qc == 0 || cut_e <= 0.f) {
+            n_take = ~0ull;               // nothing left to cut: keep all
+            cut_e = 0.f;
+        } else {
+            const unsigned long long need = target > above ? target - above : 1;
+            n_take = (need + qc - 1) / qc;
+            if (n_take == 0) n_take = 1;
+        }
+        // rank of this thread's first tie, in index order
+        unsigned long long ties = 0;
+        for (int i = i0; i < i1; ++i) ties += (x[i] == cut_e && cut_e > 0.f) ? 1 : 0;
+        unsigned long long tie_total;
+        unsigned long long tie_rank = block_excl_scan(ties, sh, &tie_total);
+        mine = 0;
+        for (int i = i0; i < i1; ++i) {
+            const float e = x[i];
+            bool keep = e > cut_e;
+            if (e == cut_e && cut_e > 0.f) { keep = tie_rank < n_take; ++tie_rank; }
+            if (!keep) x[i] = 0.f;
+            else mine += fixed40(e);
+        }
+        block_excl_scan(mine, sh, &kept);
+    }
+
+    // 8. the draw: first kept index whose running mass exceeds u * kept
+    const unsigned k24 = draw24(seed, (unsigned long long)(streams ? streams[b] : b),
+                                (unsigned long long)(steps ? steps[b] : 0));
+    const unsigned long long lo = kept * (unsigned long long)k24;
+    const unsigned long long hi = __umul64hi(kept, (unsigned long long)k24);
+    const unsigned long long r = (hi << 40) | (lo >> 24);
+    unsigned long long dummy;
+    const unsigned long long before = block_excl_scan(mine, sh, &dummy);
+    if (tid == 0) sh.result = -1;
+    __syncthreads();
+    if (mine > 0 && before <= r && r < before + mine) {
+        unsigned long long c = before;
+        for (int i = i0; i < i1; ++i) {
+            const unsigned long long qv = fixed40(x[i]);
+            if (qv == 0) continue;
+            c += qv;
+            if (r < c) { sh.result = i; break; }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int res = sh.result;
+        if (res < 0) {                    // all mass below the fixed-point resolution: fall back to the maximum
+            res = 0;
+            for (int i = 0; i < V; ++i)
+                if (src[i] * inv_t == mx) { res = i; break; }
+        }
+        out[b] = res;
+    }
+}
+
+}  // namespace
+
+MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int V, float temperature,
+                     int top_k, float top_p, float min_p, float rep_pen, float pres_pen, float freq_pen,
+                     const int* recent, const int* n_recent, unsigned long long seed, const int* streams,
+                     const int* steps, int* out, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    sample_kernel<<<B, THREADS, 0, stream>>>(logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
+                                             pres_pen, freq_pen, recent, n_recent, seed, streams, steps, out);
+    return mv_launch_status();
+}

@@ -1,0 +1,90 @@
+// The gated short convolution between its two projections, for any cut of the
+// token stream: prompts of unequal lengths, chunks of a prompt, single tokens.
+//
+// p[n, 0:H] = B, p[n, H:2H] = C, p[n, 2H:3H] = X (the order is fixed by the
+// reference: crates/mivi-model/src/ssm.rs:81-85); bx = B * X;
+// y_t[d] = sum_j w[d, j] * bx_{t-(k-1)+j}[d], tap k-1 on the current token
+// (ssm.rs:92-140); z = C * y (ssm.rs:110).  The reference keeps the last k
+// values of bx per channel and shifts them each token; here a sequence's
+// slot keeps the k-1 values BEFORE its next token, state[slot, j, d] =
+// bx at position len-(k-1)+j, zero at the start of a sequence, so a step
+// that begins in the middle of a sequence finds its left context there.
+#include "common.cuh"
+
+#define MV_MAX_CONV_K 16
+
+// One thread per (token, channel).  Reads the old state only.
+template <typename TO>
+__global__ void shortconv_fwd_kernel(const float* __restrict__ p, const float* __restrict__ w,
+                                     const float* __restrict__ bias, const float* __restrict__ state,
+                                     const int* __restrict__ positions, const int* __restrict__ seq_of,
+                                     const int* __restrict__ slots, const int* __restrict__ starts,
+                                     TO* __restrict__ z, int N, int H, int k) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)N * H) return;
+    const int n = (int)(i / H), d = (int)(i - (long long)n * H);
+    const int b = seq_of[n];
+    const int pos = positions[n], start = starts[b];
+    const float* st = state + (size_t)slots[b] * (k - 1) * H;
+    float y = bias ? bias[d] : 0.f;
+    for (int j = 0; j < k; ++j) {
+        const int src = pos - (k - 1) + j;
+        float bx;
+        if (src >= start) {
+            const float* row = p + (size_t)(n - (pos - src)) * 3 * H;
+            bx = row[d] * row[2 * H + d];
+        } else {
+            bx = st[(size_t)(src - start + (k - 1)) * H + d];
+        }
+        y = fmaf(w[d * k + j], bx, y);
+    }
+    z[i] = mv_from_f32<TO>(p[(size_t)n * 3 * H + H + d] * y);
+}
+
+// One thread per (sequence, channel): the state after this step's tokens.
+// New entry j holds position start+len-(k-1)+j: from this step's tokens if it
+// lies in them, else old entry len+j.  Going up in j, every old entry is read
+// before it is overwritten (len >= 1).
+__global__ void shortconv_state_kernel(const float* __restrict__ p, float* __restrict__ state,
+                                       const int* __restrict__ cu, const int* __restrict__ slots,
+                                       const int* __restrict__ lens, int B, int H, int k) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)B * H) return;
+    const int b = (int)(i / H), d = (int)(i - (long long)b * H);
+    const int len = lens[b];
+    if (len <= 0) return;
+    float* st = state + (size_t)slots[b] * (k - 1) * H;
+    const int first_row = cu[b];
+    for (int j = 0; j < k - 1; ++j) {
+        const int rel = len - (k - 1) + j;          // index among this step's tokens
+        float v;
+        if (rel >= 0) {
+            const float* row = p + (size_t)(first_row + rel) * 3 * H;
+            v = row[d] * row[2 * H + d];
+        } else {
+            v = st[(size_t)(len + j) * H + d];
+        }
+        st[(size_t)j * H + d] = v;
+    }
+}
+
+MV_API int mv_shortconv(const float* p, const float* w, const float* bias, float* state,
+                        const int* positions, const int* seq_of, const int* cu, const int* slots,
+                        const int* starts, const int* lens, void* z, int z_dtype, int N, int B, int H,
+                        int k, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (k < 1 || k > MV_MAX_CONV_K) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)(((long long)N * H + threads - 1) / threads);
+    if (z_dtype == MV_DT_BF16)
+        shortconv_fwd_kernel<<<blocks, threads, 0, stream>>>(p, w, bias, state, positions, seq_of, slots,
+                                                            starts, (__nv_bfloat16*)z, N, H, k);
+    else
+        shortconv_fwd_kernel<<<blocks, threads, 0, stream>>>(p, w, bias, state, positions, seq_of, slots,
+                                                            starts, (float*)z, N, H, k);
+    if (k > 1) {
+        const unsigned sblocks = (unsigned)(((long long)B * H + threads - 1) / threads);
+        shortconv_state_kernel<<<sblocks, threads, 0, stream>>>(p, state, cu, slots, lens, B, H, k);
+    }
+    return mv_launch_status();
+}

@@ -1,0 +1,96 @@
+"""A model put together from a description: embedding, blocks, the order in
+which the blocks run, final norm, head.  Nothing here is specific to an
+architecture; the architecture's file supplies the ``ModelSpec``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the architectures that ship with the package)
+from ..cache import CachePlan, plan_cache
+from ..config import architecture_for
+from ..parts import ModelSpec, ParamSpec, build
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, config=None):
+        self.spec, self.config = spec, config
+        self.hidden_size, self.vocab_size = spec.hidden_size, spec.vocab_size
+        self.embedding = build("embedding", spec.embedding)
+        self.blocks = [build("block", b) for b in spec.blocks]
+        self.final_norm = build("norm", spec.final_norm)
+        self.head = build("head", spec.head)
+        self.schedule = list(spec.schedule)
+        for pos, e in enumerate(self.schedule):
+            if not (0 <= e.block < len(self.blocks)):
+                raise ValueError(f"schedule position {pos} names block {e.block}; the model has "
+                                 f"{len(self.blocks)} blocks")
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+
+    # ---- parameters -------------------------------------------------------
+    def parts(self) -> List:
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def named_param_specs(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for p in self.parts():
+            for name, spec in p.named_param_specs().items():
+                if name in out:
+                    raise ValueError(f"two parts claim the tensor {name!r}")
+                out[name] = spec
+        return out
+
+    def load_params(self, named: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        for p in self.parts():
+            p.load_named(named)
+        self.dtype, self.device = dtype, torch.device(device)
+
+    def weight_bytes(self) -> int:
+        """Bytes of every tensor that one step reads (each counted once)."""
+        seen, total = set(), 0
+
+        def walk(p):
+            nonlocal total
+            for v in vars(p).values():
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    total += v.numel() * v.element_size()
+            for sub in p.nested().values():
+                walk(sub)
+        for p in self.parts():
+            walk(p)
+        return total
+
+    # ---- cache --------------------------------------------------------------
+    def cache_plan(self) -> CachePlan:
+        needs = [self.blocks[e.block].cache_need() for e in self.schedule]
+        return plan_cache(needs, [e.cache_of for e in self.schedule])
+
+    # ---- one step ---------------------------------------------------------------
+    def forward(self, step, cache) -> Optional[torch.Tensor]:
+        """Run the step's tokens through every scheduled block and return the
+        logits at ``step.out_rows`` (float32 [n_out, vocab]), or None if no
+        logits are wanted."""
+        x = self.embedding.forward(step)
+        for pos, entry in enumerate(self.schedule):
+            self.blocks[entry.block].forward(x, step, cache.view(pos, step.page_tables))
+        if step.n_out == 0:
+            return None
+        f = step.ws.get("final", (step.n_out, self.hidden_size), step.dtype)
+        self.final_norm.forward(x, f, rows=step.out_rows)
+        return self.head.forward(f, step, self.embedding)
+
+
+def describe_config(config_dict: dict):
+    arch = architecture_for(config_dict)
+    config = arch.config_from_dict(config_dict)
+    return config, arch.describe(config)
+
+
+def expected_tensors(config_dict: dict) -> Dict[str, ParamSpec]:
+    """The checkpoint's name table for this configuration."""
+    config, spec = describe_config(config_dict)
+    return Model(spec, config).named_param_specs()

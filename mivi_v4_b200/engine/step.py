@@ -1,0 +1,108 @@
+"""One step's batch as the kernels see it: the packed tokens of all sequences
+and the small integer arrays that say which token belongs where.
+
+The reference's step is one token of one sequence at one position
+(crates/mivi-model/src/model.rs:336-433) or a tile of consecutive tokens of
+that sequence (model.rs:670-831).  Here a step is any number of sequences,
+each with any number of next tokens, packed without padding: padding never
+enters a kernel, so it cannot change a result.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+class Workspace:
+    """Named device buffers that live as long as the engine and grow on demand,
+    so that steps allocate nothing once sizes have been seen."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+class StepContext:
+    """Host and device view of one step.
+
+    Device arrays (int32): tokens[N], positions[N] (absolute position of each
+    token in its sequence), seq_of[N] (index of its sequence in this step),
+    cu[B+1] (first packed row of each sequence), slots[B], starts[B] (length of
+    each sequence before the step), lens[B] (tokens it brings), out_rows[n_out]
+    (packed rows whose logits are wanted), page_tables[group] [B, P].
+    """
+
+    def __init__(self, *, slots: List[int], starts: List[int], token_lists: List[List[int]],
+                 out_rows: List[int], page_rows: Dict[int, List[List[int]]], dtype: torch.dtype,
+                 ws: Workspace):
+        device = ws.device
+        self.ws, self.dtype, self.device = ws, dtype, device
+        self.host_slots, self.host_starts = list(slots), list(starts)
+        self.host_lens = [len(t) for t in token_lists]
+        self.n_seqs = len(slots)
+        self.n_tokens = sum(self.host_lens)
+        self.n_out = len(out_rows)
+        self.is_decode = all(n == 1 for n in self.host_lens)
+        self.max_len = max(self.host_lens, default=0)
+        self.max_context = max((s + n for s, n in zip(starts, self.host_lens)), default=0)
+
+        flat: List[int] = []
+        spans: Dict[str, Tuple[int, int]] = {}
+
+        def put(name: str, values: List[int]) -> None:
+            spans[name] = (len(flat), len(values))
+            flat.extend(values)
+            flat.extend([0] * (-len(flat) % 4))          # 16-byte starts
+
+        tokens = [t for toks in token_lists for t in toks]
+        positions = [s + i for s, n in zip(starts, self.host_lens) for i in range(n)]
+        seq_of = [b for b, n in enumerate(self.host_lens) for _ in range(n)]
+        cu = [0]
+        for n in self.host_lens:
+            cu.append(cu[-1] + n)
+        put("tokens", tokens)
+        put("positions", positions)
+        put("seq_of", seq_of)
+        put("cu", cu)
+        put("slots", list(slots))
+        put("starts", list(starts))
+        put("lens", self.host_lens)
+        put("out_rows", list(out_rows))
+        widths: Dict[int, int] = {}
+        for g, rows in page_rows.items():
+            widths[g] = len(rows[0]) if rows else 1
+            put(f"pages{g}", [p for r in rows for p in r])
+
+        host = torch.tensor(flat, dtype=torch.int32)
+        if device.type == "cuda":
+            host = host.pin_memory()
+        arena = ws.get("step_meta", (len(flat),), torch.int32)
+        arena.copy_(host, non_blocking=True)
+        self._host_meta = host                            # keep the pinned buffer alive until the copy ran
+        self.h2d_bytes = host.numel() * 4
+
+        def view(name: str) -> torch.Tensor:
+            o, n = spans[name]
+            return arena[o:o + n]
+
+        self.tokens, self.positions, self.seq_of = view("tokens"), view("positions"), view("seq_of")
+        self.cu, self.slots, self.starts, self.lens = view("cu"), view("slots"), view("starts"), view("lens")
+        self.out_rows: Optional[torch.Tensor] = view("out_rows") if self.n_out else None
+        self.page_tables: Dict[int, torch.Tensor] = {
+            g: view(f"pages{g}").view(max(self.n_seqs, 1) if rows else 1, widths[g]) if rows else view(f"pages{g}")
+            for g, rows in page_rows.items()}

@@ -1,0 +1,261 @@
+"""Launch wrappers: one Python function per kernel entry point.
+
+Every wrapper checks what the kernel assumes (device, dtype, contiguity,
+shapes, size limits) and raises ``KernelError`` with the offending value
+instead of launching; the kernels themselves check nothing.  There is no CPU
+implementation behind these functions: a tensor that is not on a CUDA device
+is an error, and so is a library that cannot be built.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+MAX_HEAD_DIM = 256
+MAX_CONV_K = 16
+RECENT_MAX = 64
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_P, _I, _F, _Q, _UQ = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_ulonglong
+_SIGNATURES = {
+    "core": {
+        "mv_embed": [_P, _I, _P, _P, _I, _I, _P],
+        "mv_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+        "mv_swiglu": [_P, _P, _I, _I, _I, _P],
+        "mv_gemm_simt": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_qk_prepare": [_P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _P],
+        "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P],
+    },
+}
+_fns = {}
+
+
+def _fn(lib: str, name: str):
+    key = (lib, name)
+    f = _fns.get(key)
+    if f is None:
+        f = getattr(load_library(lib), name)
+        f.argtypes = _SIGNATURES[lib][name]
+        f.restype = ctypes.c_int
+        _fns[key] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}; the kernels take float32 and bfloat16")
+
+
+def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional=False):
+    if t is None:
+        if optional:
+            return None
+        raise KernelError(f"{name}: missing tensor")
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is on {t.device}; this library runs on CUDA devices only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor is not contiguous (strides {t.stride()})")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: dtype {t.dtype}, expected {dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
+            raise KernelError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+    return t.data_ptr()
+
+
+def _check(code: int, name: str) -> None:
+    if code != 0:
+        raise KernelError(f"{name}: launch failed with CUDA error {code}")
+
+
+# --------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, :] = table[tokens[n], :] widened to float32."""
+    N = tokens.numel()
+    V, H = table.shape
+    _check(_fn("core", "mv_embed")(
+        _need(table, "embedding table"), _dt(table), _need(tokens, "tokens", torch.int32),
+        _need(out, "embedding out", torch.float32, (N, H)), N, H, _stream()), "mv_embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = rmsnorm(x[rows[i]] or x[i]) * w, statistics in float32."""
+    H = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    _check(_fn("core", "mv_rmsnorm")(
+        _need(x, "rmsnorm x", torch.float32), _need(w, "rmsnorm weight", torch.float32, (H,)),
+        _need(out, "rmsnorm out", None, (n, H)), _dt(out),
+        _need(rows, "rmsnorm rows", torch.int32, optional=True), n, H, float(eps), _stream()), "mv_rmsnorm")
+    return out
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, f] = silu(gu[n, f]) * gu[n, F + f]."""
+    N, F2 = gu.shape
+    F = F2 // 2
+    _check(_fn("core", "mv_swiglu")(
+        _need(gu, "swiglu in", torch.float32), _need(out, "swiglu out", None, (N, F)), _dt(out), N, F,
+        _stream()), "mv_swiglu")
+    return out
+
+
+STORE, ACCUMULATE = "store", "accumulate"
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+              accumulate: bool = False) -> torch.Tensor:
+    """out = x @ w.T (+ bias), or out += ... when ``accumulate`` (out float32).
+    CUDA-core kernel, float32 accumulation, any sizes."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is [{N}, {K2}]")
+    if x.dtype != w.dtype:
+        raise KernelError(f"gemm: x is {x.dtype} but w is {w.dtype}")
+    if accumulate:
+        mode = 2
+        _need(out, "gemm out", torch.float32, (M, N))
+    else:
+        mode = 0 if out.dtype == torch.float32 else 1
+        _need(out, "gemm out", None, (M, N))
+        _dt(out)
+    _check(_fn("core", "mv_gemm_simt")(
+        _need(x, "gemm x"), _need(w, "gemm w"), _dt(x), _need(bias, "gemm bias", torch.float32, (N,), True),
+        out.data_ptr(), mode, M, N, K, N, _stream()), "mv_gemm_simt")
+    return out
+
+
+def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+              positions, seq_of, cu, slots, starts, lens, out: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    """Gated short convolution between its projections; updates ``state``
+    [n_slots, k-1, H] in place for the ``n_seqs`` sequences of the step."""
+    N, H3 = p.shape
+    H, k = w.shape
+    if H3 != 3 * H:
+        raise KernelError(f"shortconv: projection width {H3} is not 3 x {H}")
+    if not 1 <= k <= MAX_CONV_K:
+        raise KernelError(f"shortconv: convolution width {k} is outside 1..{MAX_CONV_K}")
+    _need(state, "shortconv state", torch.float32)
+    if state.dim() != 3 or state.shape[1] != k - 1 or state.shape[2] != H:
+        raise KernelError(f"shortconv: state shape {tuple(state.shape)}, expected [slots, {k - 1}, {H}]")
+    _check(_fn("core", "mv_shortconv")(
+        _need(p, "shortconv p", torch.float32), _need(w, "shortconv taps", torch.float32),
+        _need(bias, "shortconv bias", torch.float32, (H,), True), state.data_ptr(),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(cu, "cu", torch.int32), _need(slots, "slots", torch.int32),
+        _need(starts, "starts", torch.int32), _need(lens, "lens", torch.int32),
+        _need(out, "shortconv out", None, (N, H)), _dt(out), N, n_seqs, H, k, _stream()), "mv_shortconv")
+    return out
+
+
+def _check_kv(pool: torch.Tensor, nkv: int, hd: int, page_size: int, what: str):
+    if pool.dim() != 5 or tuple(pool.shape[1:]) != (2, nkv, page_size, hd):
+        raise KernelError(f"{what}: cache pool shape {tuple(pool.shape)}, expected "
+                          f"[pages, 2, {nkv}, {page_size}, {hd}]")
+    if page_size & (page_size - 1):
+        raise KernelError(f"{what}: page size {page_size} is not a power of two")
+
+
+def qk_prepare(qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+               inv_freq: Optional[torch.Tensor], half_split: bool, positions, seq_of, page_table,
+               pool: torch.Tensor, q_out: torch.Tensor, nh: int, nkv: int, hd: int,
+               append: bool = True) -> torch.Tensor:
+    """Per-head RMSNorm of q and k, rotation, and the write of k and v into
+    the paged cache; q comes out in the model's dtype."""
+    N = qkv.shape[0]
+    if hd % 2 or hd > MAX_HEAD_DIM:
+        raise KernelError(f"qk_prepare: head size {hd} must be even and at most {MAX_HEAD_DIM}")
+    page_size = pool.shape[3]
+    _check_kv(pool, nkv, hd, page_size, "qk_prepare")
+    if pool.dtype != q_out.dtype:
+        raise KernelError(f"qk_prepare: cache is {pool.dtype} but q is {q_out.dtype}")
+    _need(page_table, "page table", torch.int32)
+    _check(_fn("core", "mv_qk_prepare")(
+        _need(qkv, "qkv", torch.float32, (N, (nh + 2 * nkv) * hd)),
+        _need(wq, "q norm weight", torch.float32, (hd,), True),
+        _need(wk, "k norm weight", torch.float32, (hd,), True), float(eps),
+        _need(inv_freq, "inv_freq", torch.float32, (hd // 2,), True), int(half_split),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        page_table.data_ptr(), page_table.shape[1], page_size, _need(pool, "cache pool"),
+        pool.stride(0), int(append), _need(q_out, "q out", None, (N, nh * hd)), _dt(q_out), N, nh, nkv, hd,
+        _stream()), "mv_qk_prepare")
+    return q_out
+
+
+def qk_prepare_q_only(qkv: torch.Tensor, wq: Optional[torch.Tensor], eps: float,
+                      inv_freq: Optional[torch.Tensor], half_split: bool, positions, q_out: torch.Tensor,
+                      nh: int, hd: int) -> torch.Tensor:
+    """The same for a layer that has queries only (it reads another layer's cache)."""
+    N = qkv.shape[0]
+    if hd % 2 or hd > MAX_HEAD_DIM:
+        raise KernelError(f"qk_prepare: head size {hd} must be even and at most {MAX_HEAD_DIM}")
+    _check(_fn("core", "mv_qk_prepare")(
+        _need(qkv, "q", torch.float32, (N, nh * hd)), _need(wq, "q norm weight", torch.float32, (hd,), True),
+        None, float(eps), _need(inv_freq, "inv_freq", torch.float32, (hd // 2,), True), int(half_split),
+        _need(positions, "positions", torch.int32), None, None, 0, 1, None, 0, 0,
+        _need(q_out, "q out", None, (N, nh * hd)), _dt(q_out), N, nh, 0, hd, _stream()), "mv_qk_prepare")
+    return q_out
+
+
+def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table, positions, seq_of,
+                      out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: int = 0):
+    """Causal attention of every token of the step over its sequence's cache
+    (which already holds the step's own keys), optional sliding window."""
+    N = q.shape[0]
+    if hd % 8 or hd > MAX_HEAD_DIM:
+        raise KernelError(f"attention: head size {hd} must be a multiple of 8 and at most {MAX_HEAD_DIM}")
+    if nh % nkv:
+        raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
+    page_size = pool.shape[3]
+    _check_kv(pool, nkv, hd, page_size, "attention")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    _check(_fn("core", "mv_attention_generic")(
+        _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.stride(0),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(out, "attention out", None, (N, nh * hd)), _dt(q), N, nh, nkv, hd, float(scale), int(window),
+        _stream()), "mv_attention_generic")
+    return out
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, temperature: float,
+           top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
+           presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
+           recent: Optional[torch.Tensor] = None, n_recent: Optional[torch.Tensor] = None, seed: int = 0,
+           streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of ``logits`` [B, V] (float32, rows may be strided)."""
+    B, V = logits.shape
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 on a CUDA device with unit column stride")
+    if recent is not None and (recent.shape != (B, RECENT_MAX)):
+        raise KernelError(f"sample: recent tokens shape {tuple(recent.shape)}, expected [{B}, {RECENT_MAX}]")
+    _check(_fn("core", "mv_sample")(
+        logits.data_ptr(), logits.stride(0), _need(work, "sample scratch", torch.float32, (None, V)), B, V,
+        float(temperature), int(top_k), float(top_p), float(min_p), float(repetition_penalty),
+        float(presence_penalty), float(frequency_penalty),
+        _need(recent, "recent", torch.int32, optional=True),
+        _need(n_recent, "n_recent", torch.int32, (B,), True), int(seed) & ((1 << 64) - 1),
+        _need(streams, "streams", torch.int32, (B,), True), _need(steps, "steps", torch.int32, (B,), True),
+        _need(out, "sample out", torch.int32, (B,)), _stream()), "mv_sample")
+    return out

@@ -1,0 +1,26 @@
+"""The matrix product of a layer, y = x W^T: picks the kernel for the operands'
+dtype and shape.  All kernels are this library's own; none is a vendor library
+call.
+
+float32 operands always take the CUDA-core kernel (true 32-bit products and
+sums).  bfloat16 operands take the tensor-core kernels where their shape
+rules hold and the CUDA-core kernel otherwise.  A weight that the checkpoint
+stores in 32-bit stays so; a bfloat16 activation is widened for it.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import kernels as K
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+           accumulate: bool = False) -> torch.Tensor:
+    """out = x @ w.T (+ bias); with ``accumulate`` the product is added to
+    ``out`` (float32), which is how a layer's result joins the residual
+    stream without a separate pass."""
+    if w.dtype == torch.float32 and x.dtype != torch.float32:
+        x = x.float()
+    return K.gemm_simt(x, w, out, bias=bias, accumulate=accumulate)

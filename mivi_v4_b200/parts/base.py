@@ -1,0 +1,51 @@
+"""What every part is: a bag of named parameters with declared shapes, built
+from sizes and constants alone.  No part knows which model it is in.
+
+Interfaces by role (``step`` is an engine.step.StepContext, ``resid`` the
+32-bit residual stream [N, hidden] that a part adds its result to in place):
+
+norm          forward(x_f32[N, dim], out_dtype, step, rows=None) -> [n, dim]
+position      rotary() -> (inv_freq f32[hd/2], style) or None
+mixer         cache_need() -> KVNeed | StateNeed | None
+              forward(u[N, hidden], resid, step, cache_view) -> None
+feed_forward  forward(g[N, hidden], resid, step) -> None
+block         cache_need(); forward(resid, step, cache_view) -> None
+embedding     forward(step) -> resid f32[N, hidden]
+head          forward(f[n, hidden], step, embedding) -> logits f32[n, vocab]
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+from .spec import ParamSpec
+
+
+class Part:
+    kind = "?"
+    prefix = ""
+    nested_roles: Dict[str, str] = {}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        """Local tensor name (appended to ``prefix``) -> how the checkpoint stores it."""
+        return {}
+
+    def nested(self) -> Dict[str, "Part"]:
+        return {}
+
+    def named_param_specs(self) -> Dict[str, ParamSpec]:
+        out = {self.prefix + k: v for k, v in self.param_specs().items()}
+        for sub in self.nested().values():
+            out.update(sub.named_param_specs())
+        return out
+
+    def load(self, tensors: Dict[str, "object"]) -> None:
+        """Take this part's tensors (keyed by local name, already on the device
+        and in their run dtype) and lay them out as its kernels want them."""
+        for k, v in tensors.items():
+            setattr(self, k.replace(".", "_"), v)
+
+    def load_named(self, named: Dict[str, "object"]) -> None:
+        mine = {k: named[self.prefix + k] for k in self.param_specs()}
+        self.load(mine)
+        for sub in self.nested().values():
+            sub.load_named(named)

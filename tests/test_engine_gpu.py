@@ -1,0 +1,86 @@
+"""The engine against the plain implementation on a GPU, in 32-bit and in
+bfloat16: each request alone and whole; with the last tokens one by one; in
+batches of unequal lengths whose shorter requests end earlier, one batch after
+another so that slots are used again."""
+import pytest
+import torch
+
+from helpers import assert_close, plain_logits, write_model
+from tiny_configs import CONFIGS, prompts
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {k: write_model(root, cfg, seed) for k, (cfg, seed) in CONFIGS.items()}
+
+
+def make_engine(folder, dtype, max_tokens=4096, **kw):
+    from mivi_v4_b200 import Engine, load_model
+    return Engine(load_model(folder, dtype, "cuda:0"), max_tokens=max_tokens, **kw)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompt(folders, name, dtype):
+    eng = make_engine(folders[name], dtype)
+    V = CONFIGS[name][0]["vocab_size"]
+    for toks in prompts(V, [1, 2, 5, 33, 64, 65, 130], seed=3):
+        s = eng.open()
+        got = eng.step([(s, toks)], "all")
+        eng.close(s)
+        assert_close(got, plain_logits(folders[name], toks), dtype, f"{name} whole len {len(toks)}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_last_tokens_one_by_one(folders, name, dtype):
+    eng = make_engine(folders[name], dtype)
+    V = CONFIGS[name][0]["vocab_size"]
+    for toks in prompts(V, [33, 70, 100], seed=4):
+        want = plain_logits(folders[name], toks)
+        s = eng.open()
+        cut = max(1, len(toks) - 32)
+        rows = [eng.step([(s, toks[:cut])], "all")]
+        for t in toks[cut:]:
+            rows.append(eng.step([(s, [t])], "last"))
+        eng.close(s)
+        assert_close(torch.cat(rows), want, dtype, f"{name} last32 len {len(toks)}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_unequal_batches_slots_reused(folders, name, dtype):
+    """Two batches one after another through a cache that is just large
+    enough for one: prompts in one step, then one token each; shorter requests
+    end earlier."""
+    V = CONFIGS[name][0]["vocab_size"]
+    eng = make_engine(folders[name], dtype, max_tokens=4 * 128, max_batch=4)
+    for round_, lens in enumerate([[5, 11, 17, 40], [1, 7, 19, 32]]):
+        full = prompts(V, [n + d for n, d in zip(lens, [3, 9, 6, 12])], seed=10 + round_)
+        want = [plain_logits(folders[name], t) for t in full]
+        slots = [eng.open() for _ in full]
+        got = [[] for _ in full]
+        lg = eng.step([(s, t[:n]) for s, t, n in zip(slots, full, lens)], "all")
+        off = 0
+        for i, n in enumerate(lens):
+            got[i].append(lg[off:off + n])
+            off += n
+        pos = list(lens)
+        live = list(range(len(full)))
+        while live:
+            lg = eng.step([(slots[i], [full[i][pos[i]]]) for i in live], "last")
+            for j, i in enumerate(live):
+                got[i].append(lg[j:j + 1])
+                pos[i] += 1
+            for i in [i for i in live if pos[i] == len(full[i])]:
+                eng.close(slots[i])
+            live = [i for i in live if pos[i] < len(full[i])]
+        for i in range(len(full)):
+            assert_close(torch.cat(got[i]), want[i], dtype, f"{name} batch {round_} request {i}")
+        eng.cache.check()
+        assert eng.cache.slots.held_count == 0

@@ -1,0 +1,32 @@
+"""The tiny configurations that the tests run: two of the architecture that
+differ in every size and option, and helpers to draw prompts."""
+import torch
+
+ARCH = ["Lfm2ForCausalLM"]
+
+TINY_A = dict(
+    architectures=ARCH, model_type="lfm2", hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
+    num_key_value_heads=2, vocab_size=256, block_ff_dim=192, block_auto_adjust_ff_dim=False,
+    layer_types=["conv", "full_attention", "conv", "full_attention"], rope_theta=10000.0, norm_eps=1e-5,
+    conv_L_cache=3, conv_bias=False, tie_embedding=True)
+
+TINY_B = dict(
+    architectures=ARCH, model_type="lfm2", hidden_size=96, num_hidden_layers=6, num_attention_heads=3,
+    num_key_value_heads=1, vocab_size=384, block_ff_dim=384, block_auto_adjust_ff_dim=True,
+    block_multiple_of=64, block_ffn_dim_multiplier=1.0,
+    layer_types=["full_attention", "conv", "conv", "full_attention", "conv", "full_attention"],
+    rope_theta=1000000.0, norm_eps=1e-6, conv_L_cache=4, conv_bias=True, tie_embedding=False)
+
+# sizes that are no power of two anywhere: width 80 = 5 heads of 16, 5:1 groups... ff 144, vocab 301
+TINY_C = dict(
+    architectures=ARCH, model_type="lfm2", hidden_size=240, num_hidden_layers=3, num_attention_heads=5,
+    num_key_value_heads=5, vocab_size=301, block_ff_dim=200, block_auto_adjust_ff_dim=False,
+    layer_types=["full_attention", "conv", "full_attention"], rope_theta=50000.0, norm_eps=1e-5,
+    conv_L_cache=2, conv_bias=False, tie_embedding=True, rope_style="half_split")
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+
+
+def prompts(vocab: int, lengths, seed: int = 0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
