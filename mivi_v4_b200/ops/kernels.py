@@ -81,9 +81,21 @@ def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional
     return t.data_ptr()
 
 
+_launches = 0
+# kernels launched by one call of each entry point
+_KERNELS_PER_CALL = {"mv_shortconv": 2}
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far in this process."""
+    return _launches
+
+
 def _check(code: int, name: str) -> None:
+    global _launches
     if code != 0:
         raise KernelError(f"{name}: launch failed with CUDA error {code}")
+    _launches += _KERNELS_PER_CALL.get(name, 1)
 
 
 # --------------------------------------------------------------------------
