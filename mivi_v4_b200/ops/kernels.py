@@ -37,6 +37,9 @@ _SIGNATURES = {
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P],
     },
+    "bf16": {
+        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    },
 }
 _fns = {}
 
@@ -154,6 +157,34 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Opti
     _check(_fn("core", "mv_gemm_simt")(
         _need(x, "gemm x"), _need(w, "gemm w"), _dt(x), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, N, _stream()), "mv_gemm_simt")
+    return out
+
+
+SMALL_M_MAX = 64
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """out = x @ w.T for at most 64 rows of x, bfloat16 operands: the
+    weight-streaming tensor-core kernel of the decode step."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is [{N}, {K2}]")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_small_m: operands must be bfloat16, got {x.dtype} and {w.dtype}")
+    if not 1 <= M <= SMALL_M_MAX or K % 8:
+        raise KernelError(f"gemm_small_m: needs 1..{SMALL_M_MAX} rows and K a multiple of 8, got M={M}, K={K}")
+    if accumulate:
+        mode = 2
+        _need(out, "gemm out", torch.float32, (M, N))
+    else:
+        mode = 0 if out.dtype == torch.float32 else 1
+        _need(out, "gemm out", None, (M, N))
+        _dt(out)
+    _check(_fn("bf16", "mv_gemm_small_m")(
+        _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
+        out.data_ptr(), mode, M, N, K, N, _stream()), "mv_gemm_small_m")
     return out
 
 
