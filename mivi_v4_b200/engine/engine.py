@@ -28,7 +28,7 @@ class StepError(ValueError):
 
 class Engine:
     def __init__(self, model: Model, *, max_tokens: int, max_batch: Optional[int] = None,
-                 page_size: int = 64, max_step_tokens: int = 8192):
+                 page_size: int = 64, max_step_tokens: int = 8192, cuda_graphs: bool = True):
         if model.dtype is None:
             raise ValueError("the model has no weights yet; use load_model()")
         if model.device.type != "cuda":
@@ -49,12 +49,18 @@ class Engine:
         self.max_positions = model.spec.max_positions
         self.steps_run = 0
         self.h2d_bytes = 0
+        # decode steps (one token per sequence, last logits wanted) replay a captured CUDA graph;
+        # key: (sequences, page-table widths) -> (graph, private workspace, logits, kernels in the graph)
+        self.cuda_graphs = bool(cuda_graphs)
+        self._graphs: Dict[tuple, tuple] = {}
+        self.graph_replays = 0
 
     # ---- sequences ------------------------------------------------------------
     def open(self) -> int:
         """Start a sequence; returns its slot."""
         if self.cache.slots.free_count == 0 and self.cache.n_slots < self.total_pages:
             self.cache.grow_slots(min(self.total_pages, max(2 * self.cache.n_slots, 1)))
+            self._graphs.clear()                          # the state storage moved
         return self.cache.assign()
 
     def close(self, slot: int) -> None:
@@ -168,10 +174,44 @@ class Engine:
         for (_, toks), w in zip(items, places):
             out_rows.extend(row + i for i in w)
             row += len(toks)
-        page_rows = {g: self.cache.page_rows(g, slots) for g in self.cache.kv_groups}
-        ctx = StepContext(slots=slots, starts=starts, token_lists=[t for _, t in items], out_rows=out_rows,
-                          page_rows=page_rows, dtype=self.dtype, ws=self.ws)
-        logits = self.model.forward(ctx, self.cache)
+        decode = self.cuda_graphs and all(len(t) == 1 for _, t in items) and \
+            out_rows == list(range(len(items)))
+        # page tables of a decode step are padded to 8 pages so that one graph serves 512 tokens of growth
+        widths = {g: -(-max(len(self.cache._get(s).pages[g]) for s in slots) // 8) * 8 if decode else None
+                  for g in self.cache.kv_groups}
+        page_rows = {g: self.cache.page_rows(g, slots, widths[g]) for g in self.cache.kv_groups}
+        lists = [t for _, t in items]
+        if not decode:
+            ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
+                              page_rows=page_rows, dtype=self.dtype, ws=self.ws)
+            logits = self.model.forward(ctx, self.cache)
+        else:
+            key = (len(items), tuple(sorted(widths.items())))
+            entry = self._graphs.get(key)
+            if entry is None:
+                # first time: run the step for real on a workspace of its own (which sizes every
+                # buffer), then record the same launches for the steps to come
+                gws = Workspace(self.device)
+                ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
+                                  page_rows=page_rows, dtype=self.dtype, ws=gws)
+                logits = self.model.forward(ctx, self.cache)
+                from ..ops import kernels as K
+                n0 = K.launch_count()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    captured = self.model.forward(ctx, self.cache)
+                n_kernels = K.launch_count() - n0
+                K.add_launches(-n_kernels)                # recorded, not run
+                assert captured.data_ptr() == logits.data_ptr()
+                self._graphs[key] = (graph, gws, logits, n_kernels)
+            else:
+                graph, gws, logits, n_kernels = entry
+                ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
+                                  page_rows=page_rows, dtype=self.dtype, ws=gws)
+                graph.replay()
+                from ..ops import kernels as K
+                K.add_launches(n_kernels)
+                self.graph_replays += 1
         for s, toks in items:
             self.cache.advance(s, len(toks))
         self.steps_run += 1

@@ -36,6 +36,47 @@ class Workspace:
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 
+    def get_zeroed(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Like ``get``, but the buffer is zero when it is first handed out (and
+        after it had to grow).  For scratch that its kernels leave zeroed."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+    def stage(self, name: str, values: List[int]) -> torch.Tensor:
+        """Copy a list of integers to the device buffer ``name`` (int32) through
+        pinned host memory, one asynchronous copy.  A small ring of pinned
+        buffers is reused; a buffer is taken again only after the copy that
+        last read it has run."""
+        n = len(values)
+        dst = self.get(name, (n,), torch.int32)
+        if self.device.type != "cuda":
+            dst.copy_(torch.tensor(values, dtype=torch.int32))
+            return dst
+        ring = self.__dict__.setdefault("_ring", [])
+        if not ring:
+            ring.extend([None, None, None, None])
+            self._ring_at = 0
+        i = self._ring_at
+        self._ring_at = (i + 1) % len(ring)
+        slot = ring[i]
+        if slot is None or slot[0].numel() < n:
+            slot = (torch.empty(max(n, 256), dtype=torch.int32).pin_memory(), torch.cuda.Event())
+            ring[i] = slot
+        else:
+            slot[1].synchronize()
+        host, event = slot
+        host[:n] = torch.tensor(values, dtype=torch.int32)
+        dst.copy_(host[:n], non_blocking=True)
+        event.record()
+        return dst
+
 
 class StepContext:
     """Host and device view of one step.
@@ -88,13 +129,8 @@ class StepContext:
             widths[g] = len(rows[0]) if rows else 1
             put(f"pages{g}", [p for r in rows for p in r])
 
-        host = torch.tensor(flat, dtype=torch.int32)
-        if device.type == "cuda":
-            host = host.pin_memory()
-        arena = ws.get("step_meta", (len(flat),), torch.int32)
-        arena.copy_(host, non_blocking=True)
-        self._host_meta = host                            # keep the pinned buffer alive until the copy ran
-        self.h2d_bytes = host.numel() * 4
+        arena = ws.stage("step_meta", flat)
+        self.h2d_bytes = len(flat) * 4
 
         def view(name: str) -> torch.Tensor:
             o, n = spans[name]

@@ -26,7 +26,8 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 # library name -> sources.  ``core`` holds what every model and both dtypes
 # need; the tensor-core libraries serve bfloat16 only.
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["elementwise.cu", "gemm_simt.cu", "shortconv.cu", "attention.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "gemm_simt.cu", "shortconv.cu", "attention.cu", "attention_decode.cu",
+             "sampling.cu"],
     "bf16": ["gemm_small_m.cu"],
 }
 

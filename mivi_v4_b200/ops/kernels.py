@@ -35,6 +35,8 @@ _SIGNATURES = {
         "mv_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_qk_prepare": [_P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _P],
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "mv_attention_decode": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
+                                _I, _I, _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P],
     },
     "bf16": {
@@ -92,6 +94,12 @@ _KERNELS_PER_CALL = {"mv_shortconv": 2}
 def launch_count() -> int:
     """Kernels of this library launched so far in this process."""
     return _launches
+
+
+def add_launches(n: int) -> None:
+    """Kernels that ran without passing through a wrapper (a replayed CUDA graph)."""
+    global _launches
+    _launches += n
 
 
 def _check(code: int, name: str) -> None:
@@ -279,6 +287,49 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table, positions
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
         _need(out, "attention out", None, (N, nh * hd)), _dt(q), N, nh, nkv, hd, float(scale), int(window),
         _stream()), "mv_attention_generic")
+    return out
+
+
+N_SMS = 148
+DECODE_ATTENTION_MAX_TOKENS = 128      # steps with more query tokens split the work over the queries
+
+
+def attention_decode_plan(N: int, nh: int, nkv: int):
+    """(query heads per block, head tiles per kv head, key splits) for a step of N
+    query tokens: enough blocks to fill the GPU twice over."""
+    G = nh // nkv
+    gt = 1 if G <= 1 else (2 if G <= 2 else (4 if G <= 4 else 8))
+    head_tiles = -(-G // gt)
+    splits = max(1, min(32, -(-2 * N_SMS // max(1, N * nkv * head_tiles))))
+    return gt, head_tiles, splits
+
+
+def attention_decode(q: torch.Tensor, pool: torch.Tensor, page_table, positions, seq_of, out: torch.Tensor,
+                     nh: int, nkv: int, hd: int, scale: float, window: int, ws, splits: Optional[int] = None):
+    """The same contract as ``attention_generic``, for steps with few query
+    tokens: work is split over the keys, and the heads of a group share the
+    loads.  ``ws`` (a Workspace) supplies the scratch for the key splits."""
+    N = q.shape[0]
+    if hd % 8 or hd > MAX_HEAD_DIM:
+        raise KernelError(f"attention: head size {hd} must be a multiple of 8 and at most {MAX_HEAD_DIM}")
+    if nh % nkv:
+        raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
+    page_size = pool.shape[3]
+    _check_kv(pool, nkv, hd, page_size, "attention")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    gt, head_tiles, auto = attention_decode_plan(N, nh, nkv)
+    splits = auto if splits is None else int(splits)
+    part_o = ws.get("attn_part_o", (N * nh * splits * hd,), torch.float32)
+    part_ml = ws.get("attn_part_ml", (N * nh * splits * 2,), torch.float32)
+    tickets = ws.get_zeroed("attn_tickets", (N * nkv * head_tiles,), torch.int32)
+    _check(_fn("core", "mv_attention_decode")(
+        _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.stride(0),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(out, "attention out", None, (N, nh * hd)), _dt(q), part_o.data_ptr(), part_ml.data_ptr(),
+        tickets.data_ptr(), N, nh, nkv, hd, float(scale), int(window), splits, gt, head_tiles, _stream()),
+        "mv_attention_decode")
     return out
 
 

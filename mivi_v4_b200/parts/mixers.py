@@ -129,6 +129,10 @@ class GroupedQueryAttention(Part):
             K.qk_prepare(qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
                          step.seq_of, view.page_table, view.pool, q, nh, nkv, hd)
         o = step.ws.get("mix", (N, nh * hd), step.dtype)
-        K.attention_generic(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
-                            self.scale, self.window)
+        if N <= K.DECODE_ATTENTION_MAX_TOKENS:
+            K.attention_decode(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
+                               self.scale, self.window, step.ws)
+        else:
+            K.attention_generic(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
+                                self.scale, self.window)
         linear(o, self.w_o, resid, accumulate=True)

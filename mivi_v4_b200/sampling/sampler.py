@@ -25,6 +25,8 @@ class Sampler:
         self.seed = int(seed) & ((1 << 64) - 1)
         self._work = None
         self._out = None
+        from ..engine.step import Workspace
+        self._ws = Workspace(self.device)
 
     def sample(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
                recent: Sequence[Sequence[int]]) -> List[int]:
@@ -40,7 +42,7 @@ class Sampler:
             for r in recent:
                 r = list(r)[-RECENT_TOKENS_WINDOW:]
                 meta += r + [0] * (RECENT_TOKENS_WINDOW - len(r))
-        m = torch.tensor(meta, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        m = self._ws.stage("sample_meta", meta)
         streams_d, steps_d = m[:B], m[B:2 * B]
         n_recent_d = m[2 * B:3 * B] if use_pen else None
         recent_d = m[3 * B:].view(B, RECENT_TOKENS_WINDOW) if use_pen else None

@@ -110,3 +110,175 @@ def test_gemm_small_m_refuses_what_it_cannot_do():
                          torch.empty(2, 8, device=DEV))
     with pytest.raises(K().KernelError):
         K().gemm_simt(rnd(2, 8).cpu(), rnd(8, 8).cpu(), torch.empty(2, 8))
+
+
+# ---------------------------------------------------------------- attention
+def build_cache(lengths, nkv, hd, page_size, dtype, seed=0):
+    """Random keys and values of sequences with these lengths, laid into pages
+    handed out in a shuffled order; returns pool, page table, and the dense
+    copies [len, nkv, hd] for the plain expression."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-n // page_size) for n in lengths]
+    n_pages = sum(blocks) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    pool = torch.zeros(n_pages, 2, nkv, page_size, hd, dtype=dtype)
+    table = torch.zeros(len(lengths), max(blocks) + 2, dtype=torch.int32)
+    dense = []
+    for b, n in enumerate(lengths):
+        k = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        dense.append((k, v))
+        for blk in range(blocks[b]):
+            page = order.pop()
+            table[b, blk] = page
+            lo, hi = blk * page_size, min(n, (blk + 1) * page_size)
+            pool[page, 0, :, :hi - lo] = k[lo:hi].permute(1, 0, 2)
+            pool[page, 1, :, :hi - lo] = v[lo:hi].permute(1, 0, 2)
+    return pool.to(DEV), table.to(DEV), dense
+
+
+def plain_attend(q, k, v, pos, nh, nkv, scale, window):
+    """softmax(q.k / sqrt(hd)) v over keys t <= pos (and t > pos - window), float64."""
+    q, k, v = q.double(), k.double(), v.double()
+    hd = q.shape[-1]
+    out = torch.zeros(nh, hd, dtype=torch.float64)
+    lo = max(0, pos - window + 1) if window > 0 else 0
+    for h in range(nh):
+        g = h // (nh // nkv)
+        s = (k[lo:pos + 1, g] @ q[h]) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, g]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("kernel", ["generic", "decode", "decode_1split", "decode_7splits"])
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [
+    (4, 2, 16, 16, 0), (3, 1, 32, 64, 0), (5, 5, 48, 32, 0), (32, 8, 64, 64, 0), (12, 1, 128, 64, 0),
+    (2, 2, 256, 8, 0), (8, 2, 64, 64, 37), (6, 3, 80, 16, 64)])
+def test_attention_kernels(dtype, kernel, nh, nkv, hd, page, window):
+    from mivi_v4_b200.engine.step import Workspace
+    lengths = [1, 33, 300, 64, 129]
+    pool, table, dense = build_cache(lengths, nkv, hd, page, dtype, seed=nh + hd)
+    # query tokens: the last position of every sequence, and some in the middle (a step may
+    # bring several tokens of one sequence, each sees the keys up to its own position)
+    queries = [(b, n - 1) for b, n in enumerate(lengths)] + [(2, 0), (2, 31), (2, 32), (2, 255), (4, 64), (4, 63)]
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(len(queries), nh, hd, generator=g)
+    # make one far key of the longest sequence stand out for head 0, so that a kernel that
+    # loses it (a wrong page, a dropped run, a bad split) cannot pass
+    far = 5
+    k2 = dense[2][0]
+    q[2, 0] = (k2[far, 0].float() / k2[far, 0].float().norm()) * 6.0 * (hd ** 0.25)
+    q = q.to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    seq_of, positions = ints([b for b, _ in queries]), ints([p for _, p in queries])
+    qd = q.reshape(len(queries), nh * hd).contiguous().to(DEV)
+    out = torch.empty_like(qd)
+    if kernel == "generic":
+        K().attention_generic(qd, pool, table, positions, seq_of, out, nh, nkv, hd, scale, window)
+    else:
+        ws = Workspace(DEV)
+        splits = {"decode": None, "decode_1split": 1, "decode_7splits": 7}[kernel]
+        for _ in range(2):          # twice: the ticket counters must be back at zero
+            out.fill_(float("nan"))
+            K().attention_decode(qd, pool, table, positions, seq_of, out, nh, nkv, hd, scale, window, ws,
+                                 splits=splits)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    for i, (b, p) in enumerate(queries):
+        want = plain_attend(q[i], dense[b][0], dense[b][1], p, nh, nkv, scale, window)
+        got = out[i].reshape(nh, hd).double().cpu()
+        assert torch.allclose(got, want, rtol=tol, atol=tol), (kernel, i, b, p, (got - want).abs().max())
+    if window == 0:
+        w = torch.softmax((dense[2][0][:, 0].double() @ q[2, 0].double()) * scale, 0)
+        assert w[far] > 0.5          # the far key does dominate
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("style", ["interleaved", "half_split"])
+@pytest.mark.parametrize("nh,nkv,hd,eps,theta", [(4, 2, 16, 1e-5, 1e4), (3, 1, 32, 1e-6, 1e6), (5, 5, 48, 1e-5, 5e4)])
+def test_qk_prepare(dtype, style, nh, nkv, hd, eps, theta):
+    page = 16
+    lengths = [40, 7]
+    pool = torch.zeros(8, 2, nkv, page, hd, dtype=dtype, device=DEV)
+    table = ints([[3, 5, 1], [6, 0, 0]])
+    toks = [(0, p) for p in (0, 15, 16, 39)] + [(1, 6)]
+    qkv = rnd(len(toks), (nh + 2 * nkv) * hd, scale=2.0)
+    wq, wk = rnd(hd) + 1.0, rnd(hd, seed=1) + 1.0
+    inv = (1.0 / (torch.tensor(theta, dtype=torch.float64) ** (2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)))
+    q_out = torch.empty(len(toks), nh * hd, dtype=dtype, device=DEV)
+    K().qk_prepare(qkv, wq, wk, eps, inv.float().to(DEV), style == "half_split", ints([p for _, p in toks]),
+                   ints([b for b, _ in toks]), table, pool, q_out, nh, nkv, hd)
+    pos = torch.tensor([p for _, p in toks])
+    x = qkv.double().cpu()
+    qw = P.plain_rope(P.plain_rms_norm(x[:, :nh * hd].reshape(-1, nh, hd), wq.double().cpu(), eps), pos, theta, style)
+    kw = P.plain_rope(P.plain_rms_norm(x[:, nh * hd:(nh + nkv) * hd].reshape(-1, nkv, hd), wk.double().cpu(), eps),
+                      pos, theta, style)
+    vw = x[:, (nh + nkv) * hd:].reshape(-1, nkv, hd)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(q_out.double().cpu().reshape(-1, nh, hd), qw, rtol=tol, atol=tol)
+    tab = table.cpu()
+    for i, (b, p) in enumerate(toks):
+        pg = int(tab[b, p // page])
+        assert torch.allclose(pool[pg, 0, :, p % page].double().cpu(), kw[i], rtol=tol, atol=tol)
+        assert torch.allclose(pool[pg, 1, :, p % page].double().cpu(), vw[i], rtol=tol, atol=tol)
+    written = sum(1 for _ in toks) * 2 * nkv * hd
+    assert int((pool != 0).sum()) <= written     # nothing was written anywhere else
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("H,k,bias", [(8, 3, False), (200, 4, True), (64, 2, False), (16, 1, True), (24, 7, False)])
+def test_shortconv_any_cut(out_dtype, H, k, bias):
+    """Whole sequences against the plain loop, then the same sequences cut at
+    every place: the state carries the left context."""
+    T = [9, 4, 1]
+    g = torch.Generator().manual_seed(H + k)
+    p_all = [torch.randn(t, 3 * H, generator=g) for t in T]
+    w = torch.randn(H, k, generator=g)
+    b = torch.randn(H, generator=g) if bias else None
+
+    def plain(p):
+        bx = p[:, :H].double() * p[:, 2 * H:].double()
+        y = torch.zeros_like(bx)
+        for t in range(p.shape[0]):
+            for j in range(k):
+                src = t - (k - 1) + j
+                if src >= 0:
+                    y[t] += w[:, j].double() * bx[src]
+        if b is not None:
+            y = y + b.double()
+        return p[:, H:2 * H].double() * y
+
+    want = [plain(p) for p in p_all]
+    tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+    wd, bd = w.to(DEV), (b.to(DEV) if bias else None)
+
+    def run(cuts):
+        """cuts[b] = list of chunk lengths of sequence b; chunk i of every sequence runs in step i."""
+        state = torch.zeros(5, k - 1, H, device=DEV)
+        slots = [3, 0, 4]
+        done = [0, 0, 0]
+        got = [[] for _ in T]
+        for step in range(max(len(c) for c in cuts)):
+            live = [s for s in range(len(T)) if step < len(cuts[s])]
+            lens = [cuts[s][step] for s in live]
+            rows = torch.cat([p_all[s][done[s]:done[s] + n] for s, n in zip(live, lens)]).to(DEV).contiguous()
+            cu = [0]
+            for n in lens:
+                cu.append(cu[-1] + n)
+            out = torch.empty(rows.shape[0], H, dtype=out_dtype, device=DEV)
+            K().shortconv(rows, wd, bd, state, ints([done[s] + i for s, n in zip(live, lens) for i in range(n)]),
+                          ints([j for j, n in enumerate(lens) for _ in range(n)]), ints(cu),
+                          ints([slots[s] for s in live]), ints([done[s] for s in live]), ints(lens), out, len(live))
+            for j, (s, n) in enumerate(zip(live, lens)):
+                got[s].append(out[cu[j]:cu[j] + n])
+                done[s] += n
+        return [torch.cat(x).double().cpu() for x in got], state
+
+    whole, st_whole = run([[t] for t in T])
+    for a, b_ in zip(whole, want):
+        assert torch.allclose(a, b_, rtol=tol, atol=tol)
+    for cuts in ([[5, 4], [1, 3], [1]], [[1] * 9, [2, 2], [1]], [[8, 1], [4], [1]], [[2, 1, 6], [1, 1, 2], [1]]):
+        part, st = run(cuts)
+        for a, b_ in zip(part, want):
+            assert torch.allclose(a, b_, rtol=tol, atol=tol), cuts
+        assert torch.equal(st, st_whole), cuts       # the same state whatever the cut
