@@ -41,6 +41,7 @@ _SIGNATURES = {
     },
     "bf16": {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     },
 }
 _fns = {}
@@ -193,6 +194,53 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
     _check(_fn("bf16", "mv_gemm_small_m")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, N, _stream()), "mv_gemm_small_m")
+    return out
+
+
+_error_flags = {}
+
+
+def _error_flag(device) -> torch.Tensor:
+    """One int per device that a kernel sets when one of its bounded waits ran out."""
+    key = torch.device(device).index or 0
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel reported that a wait ran out (synchronises the device)."""
+    for key, flag in _error_flags.items():
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"code {code}")
+            raise KernelError(f"a tensor-core kernel on cuda:{key} gave up waiting on a barrier in {role}; "
+                              f"its output is not valid")
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+            accumulate: bool = False) -> torch.Tensor:
+    """out = x @ w.T, bfloat16 operands, on the tcgen05 tensor cores (TMA
+    loads, accumulator in tensor memory): the matrix product of prefill."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is [{N}, {K2}]")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tc: operands must be bfloat16, got {x.dtype} and {w.dtype}")
+    if K % 8 or K < 8:
+        raise KernelError(f"gemm_tc: K must be a multiple of 8 (16-byte rows for TMA), got {K}")
+    if accumulate:
+        mode = 2
+        _need(out, "gemm out", torch.float32, (M, N))
+    else:
+        mode = 0 if out.dtype == torch.float32 else 1
+        _need(out, "gemm out", None, (M, N))
+        _dt(out)
+    _check(_fn("bf16", "mv_gemm_tc")(
+        _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
+        out.data_ptr(), mode, M, N, K, N, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc")
     return out
 
 

@@ -23,7 +23,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
     stream without a separate pass."""
     if w.dtype == torch.float32 and x.dtype != torch.float32:
         x = x.float()
-    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= K.SMALL_M_MAX
-            and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
-        return K.gemm_small_m(x, w, out, bias=bias, accumulate=accumulate)
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        if x.shape[0] <= K.SMALL_M_MAX:
+            return K.gemm_small_m(x, w, out, bias=bias, accumulate=accumulate)
+        return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate)
     return K.gemm_simt(x, w, out, bias=bias, accumulate=accumulate)

@@ -282,3 +282,24 @@ def test_shortconv_any_cut(out_dtype, H, k, bias):
         for a, b_ in zip(part, want):
             assert torch.allclose(a, b_, rtol=tol, atol=tol), cuts
         assert torch.equal(st, st_whole), cuts       # the same state whatever the cut
+
+
+@pytest.mark.parametrize("M,N,Kd", [(65, 16, 8), (128, 128, 64), (129, 130, 72), (300, 301, 240), (256, 64, 200),
+                                    (1000, 2048, 2048), (2048, 512, 8192), (70, 9600, 96)])
+def test_gemm_tc(M, N, Kd):
+    x, w = rnd(M, Kd, dtype=torch.bfloat16), rnd(N, Kd, dtype=torch.bfloat16, seed=1)
+    bias = rnd(N, seed=2)
+    want = x.double() @ w.double().T
+    tol = dict(rtol=1e-4, atol=1e-3 * math.sqrt(Kd / 64))
+    out = torch.full((M, N), float("nan"), device=DEV)
+    K().gemm_tc(x, w, out)
+    K().check_device_errors()
+    assert torch.allclose(out.double(), want, **tol), (out.double() - want).abs().max()
+    base = rnd(M, N, seed=3)
+    acc = base.clone()
+    K().gemm_tc(x, w, acc, bias=bias, accumulate=True)
+    assert torch.allclose(acc.double(), want + base.double() + bias.double(), **tol)
+    ob = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    K().gemm_tc(x, w, ob)
+    assert torch.allclose(ob.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(Kd / 64))
+    K().check_device_errors()
