@@ -42,6 +42,7 @@ _SIGNATURES = {
     "bf16": {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     },
 }
 _fns = {}
@@ -378,6 +379,37 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, page_table, positions,
         _need(out, "attention out", None, (N, nh * hd)), _dt(q), part_o.data_ptr(), part_ml.data_ptr(),
         tickets.data_ptr(), N, nh, nkv, hd, float(scale), int(window), splits, gt, head_tiles, _stream()),
         "mv_attention_decode")
+    return out
+
+
+PREFILL_ATTENTION_MAX_HEAD_DIM = 128
+
+
+def attention_prefill_supported(dtype: torch.dtype, hd: int) -> bool:
+    return dtype == torch.bfloat16 and hd % 16 == 0 and hd <= PREFILL_ATTENTION_MAX_HEAD_DIM
+
+
+def attention_prefill(q: torch.Tensor, pool: torch.Tensor, page_table, cu, starts, out: torch.Tensor,
+                      n_seqs: int, nh: int, nkv: int, hd: int, scale: float, window: int = 0):
+    """Causal attention of a step with many query tokens on the tensor cores
+    (bfloat16, head sizes 16..128 in steps of 16).  The step's tokens are packed
+    sequence by sequence (``cu``), sequence b starting at position ``starts[b]``."""
+    N = q.shape[0]
+    if not attention_prefill_supported(q.dtype, hd):
+        raise KernelError(f"attention_prefill: needs bfloat16 and a head size 16..128 in steps of 16, "
+                          f"got {q.dtype}, {hd}")
+    if nh % nkv:
+        raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
+    page_size = pool.shape[3]
+    _check_kv(pool, nkv, hd, page_size, "attention")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    _check(_fn("bf16", "mv_attention_prefill")(
+        _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.stride(0),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
+        _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32),
+        _need(out, "attention out", None, (N, nh * hd)), N, n_seqs, nh, nkv, hd, float(scale), int(window),
+        _stream()), "mv_attention_prefill")
     return out
 
 

@@ -132,6 +132,9 @@ class GroupedQueryAttention(Part):
         if N <= K.DECODE_ATTENTION_MAX_TOKENS:
             K.attention_decode(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                self.scale, self.window, step.ws)
+        elif K.attention_prefill_supported(step.dtype, hd):
+            K.attention_prefill(q, view.pool, view.page_table, step.cu, step.starts, o, step.n_seqs, nh, nkv, hd,
+                                self.scale, self.window)
         else:
             K.attention_generic(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                 self.scale, self.window)

@@ -303,3 +303,37 @@ def test_gemm_tc(M, N, Kd):
     K().gemm_tc(x, w, ob)
     assert torch.allclose(ob.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(Kd / 64))
     K().check_device_errors()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [
+    (4, 2, 16, 16, 0), (3, 1, 32, 64, 0), (5, 5, 48, 32, 0), (8, 2, 64, 64, 0), (2, 1, 128, 64, 0),
+    (4, 4, 96, 128, 0), (8, 2, 64, 64, 37), (6, 3, 80, 16, 64), (2, 2, 112, 64, 100)])
+def test_attention_prefill(nh, nkv, hd, page, window):
+    """Chunks of several sequences in one step: (tokens already cached, tokens of this step)."""
+    dtype = torch.bfloat16
+    chunks = [(0, 1), (0, 200), (130, 70), (5, 64), (63, 66), (300, 3)]
+    lengths = [s + n for s, n in chunks]
+    pool, table, dense = build_cache(lengths, nkv, hd, page, dtype, seed=nh * hd)
+    N = sum(n for _, n in chunks)
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(N, nh, hd, generator=g)
+    # one far key stands out for the last token of the second sequence
+    row_last_b1 = chunks[0][1] + chunks[1][1] - 1
+    far = 3
+    kf = dense[1][0][far, 0].float()
+    q[row_last_b1, 0] = kf / kf.norm() * 6.0 * (hd ** 0.25)
+    q = q.to(dtype)
+    cu = [0]
+    for _, n in chunks:
+        cu.append(cu[-1] + n)
+    out = torch.full((N, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    K().attention_prefill(q.reshape(N, nh * hd).contiguous().to(DEV), pool, table, ints(cu),
+                          ints([s for s, _ in chunks]), out, len(chunks), nh, nkv, hd, scale, window)
+    tol = 1.5e-2
+    for b, (s, n) in enumerate(chunks):
+        for i in list(range(0, n, 7)) + [n - 1]:
+            want = plain_attend(q[cu[b] + i], dense[b][0], dense[b][1], s + i, nh, nkv, scale, window)
+            got = out[cu[b] + i].reshape(nh, hd).double().cpu()
+            assert torch.allclose(got, want, rtol=tol, atol=tol), (b, i, (got - want).abs().max())
+    assert not torch.isnan(out.float()).any()
