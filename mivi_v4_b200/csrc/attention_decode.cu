@@ -246,3 +246,84 @@ MV_API int mv_attention_decode(const void* q, const void* pool, long long page_s
                            o, part_o, part_ml, tickets, N, nh, nkv, hd, scale, window, splits, head_tiles,
                            stream);
 }
+
+// ---------------------------------------------------------------------------
+// mv_attention_decode_static: the same kernel for callers that cannot allocate.
+// Declared and documented in attention_decode_static.h.
+// ---------------------------------------------------------------------------
+#include "attention_decode_static.h"
+
+#include <stdio.h>
+
+namespace {
+
+// One array holds all three scratch regions.  It is part of the library's image:
+// every GPU that loads the library keeps these bytes until the process exits.
+constexpr size_t STATIC_TICKETS = MV_STATIC_ATTN_MAX_TICKETS;                  // ints, first
+constexpr size_t STATIC_FLOATS = MV_STATIC_ATTN_MAX_FLOATS;                    // part_ml and part_o share these
+static __device__ __align__(256) unsigned char g_static_attn_scratch[STATIC_TICKETS * sizeof(int) +
+                                                                     STATIC_FLOATS * sizeof(float)];
+
+constexpr int MAX_DEVICES = 64;
+unsigned char* g_static_attn_ptr[MAX_DEVICES] = {nullptr};
+
+int fail(char* errbuf, int errbuf_len, int code, const char* fmt, long long a = 0, long long b = 0) {
+    if (errbuf && errbuf_len > 0) snprintf(errbuf, (size_t)errbuf_len, fmt, a, b);
+    return code;
+}
+
+}  // namespace
+
+MV_API int mv_attention_decode_static(const void* q, const void* pool, long long page_stride,
+                                      const int* page_table, int table_stride, int page_size,
+                                      const int* positions, const int* seq_of, void* o, int dtype, int N, int nh,
+                                      int nkv, int hd, float scale, int window, int splits, cudaStream_t stream,
+                                      char* errbuf, int errbuf_len) {
+    if (errbuf && errbuf_len > 0) errbuf[0] = 0;
+    if (N <= 0) return 0;
+    if (nkv <= 0 || nh % nkv) return fail(errbuf, errbuf_len, 1, "%lld heads are not a multiple of %lld kv heads", nh, nkv);
+    if (splits < 1) return fail(errbuf, errbuf_len, 1, "splits must be at least 1, got %lld", splits);
+    const int G = nh / nkv;
+    const int gt = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
+    const int head_tiles = (G + gt - 1) / gt;
+    const size_t tickets = (size_t)N * nkv * head_tiles;
+    const size_t ml_floats = (size_t)N * nh * splits * 2;
+    const size_t o_floats = (size_t)N * nh * splits * hd;
+    if (tickets > STATIC_TICKETS)
+        return fail(errbuf, errbuf_len, 2,
+                    "the built-in scratch holds %lld (token, kv head) counters, this call needs %lld; "
+                    "use mv_attention_decode with scratch of your own", (long long)STATIC_TICKETS, (long long)tickets);
+    if (splits > 1 && ml_floats + o_floats > STATIC_FLOATS)
+        return fail(errbuf, errbuf_len, 2,
+                    "the built-in scratch holds %lld floats of partial results, this call needs %lld; "
+                    "use fewer splits or mv_attention_decode with scratch of your own",
+                    (long long)STATIC_FLOATS, (long long)(ml_floats + o_floats));
+
+    // Once per device, with that device current: the array's name is only a host-side stand-in
+    // here; the device address has to be asked for.
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        return fail(errbuf, errbuf_len, 3, "cudaGetDevice failed or device ordinal out of range (error %lld, device %lld)",
+                    (long long)e, dev);
+    if (g_static_attn_ptr[dev] == nullptr) {
+        unsigned char* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_attn_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(errbuf, errbuf_len, 3, "cudaGetSymbolAddress failed on device %lld with error %lld", dev,
+                        (long long)e);
+        g_static_attn_ptr[dev] = p;
+    }
+    unsigned char* base = g_static_attn_ptr[dev];
+    int* d_tickets = reinterpret_cast<int*>(base);
+    float* d_ml = reinterpret_cast<float*>(base + STATIC_TICKETS * sizeof(int));
+    float* d_o = d_ml + ml_floats;
+    // The counters must start at zero; the array still holds whatever the last call left.
+    e = cudaMemsetAsync(d_tickets, 0, tickets * sizeof(int), stream);
+    if (e != cudaSuccess) return fail(errbuf, errbuf_len, 3, "cudaMemsetAsync failed with error %lld", (long long)e);
+    const int rc = mv_attention_decode(q, pool, page_stride, page_table, table_stride, page_size, positions, seq_of,
+                                       o, dtype, d_o, d_ml, d_tickets, N, nh, nkv, hd, scale, window, splits, gt,
+                                       head_tiles, stream);
+    if (rc != 0) return fail(errbuf, errbuf_len, 4, "the kernel launch failed with CUDA error %lld", rc);
+    return 0;
+}
