@@ -1,0 +1,203 @@
+"""Command line in the manner of the reference's ``mivi`` binary
+(crates/mivi-cli/src/commands.rs:21-139): the same verbs where they make sense
+for a token-id library (generate in place of chat, info, doctor, bench) and
+the same option names and meanings where the reference has them:
+
+    -m/--model  -t/--temp  -p/--top-p  -k/--top-k  --min-p  -r/--rep-penalty
+    --seed  -n/--max-tokens  -c/--ctx-size
+
+with the chat command's defaults (commands.rs:86-99: temp 0.2, top-p 0.9,
+top-k 40, min-p 0.05, repetition penalty 1.1, 512 tokens).  The library has no
+tokenizer, so prompts are token ids.  ``random`` is the random-weights mode: it
+writes a model folder from a configuration and a seed.
+
+    python -m mivi_v4_b200 generate -m DIR --prompt-ids 1,2,3 --prompt-ids 4,5 -n 16 -t 0
+    python -m mivi_v4_b200 info -m DIR
+    python -m mivi_v4_b200 random --config cfg.json --seed 0 --out DIR
+    python -m mivi_v4_b200 doctor
+    python -m mivi_v4_b200 bench [-m DIR] [--bench-prompt-tokens 2048]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from typing import List
+
+
+def _ids(text: str) -> List[int]:
+    try:
+        return [int(t) for t in text.replace(",", " ").split()]
+    except ValueError:
+        raise argparse.ArgumentTypeError(f"not a list of token ids: {text!r}") from None
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="mivi_v4_b200", description="LFM2 / LFM2.5 generation on one B200")
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    g = sub.add_parser("generate", help="generate token ids for prompts of token ids")
+    g.add_argument("-m", "--model", required=True, help="folder with config.json and model.safetensors")
+    g.add_argument("--prompt-ids", type=_ids, action="append", default=[],
+                   help='one prompt as token ids, e.g. "1,2,3"; may be repeated')
+    g.add_argument("--prompts-file", help="file with one prompt per line (token ids), or a JSON list of lists")
+    g.add_argument("-t", "--temp", type=float, default=0.2, help="temperature; 0 is greedy")
+    g.add_argument("-p", "--top-p", type=float, default=0.9)
+    g.add_argument("-k", "--top-k", type=int, default=40)
+    g.add_argument("--min-p", type=float, default=0.05)
+    g.add_argument("-r", "--rep-penalty", type=float, default=1.1)
+    g.add_argument("--presence-penalty", type=float, default=0.0)
+    g.add_argument("--frequency-penalty", type=float, default=0.0)
+    g.add_argument("--seed", type=int, default=None)
+    g.add_argument("-n", "--max-tokens", type=int, default=512, help="most new tokens per prompt")
+    g.add_argument("-c", "--ctx-size", type=int, default=None, help="most tokens of one sequence (default: from the model, else 16384)")
+    g.add_argument("--stop-ids", type=_ids, default=None, help="token ids that end a sequence (default: the model's eos)")
+    g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--max-batch", type=int, default=64, help="most sequences that run together")
+    g.add_argument("--json", action="store_true", help="print one JSON object instead of lines of ids")
+
+    i = sub.add_parser("info", help="configuration and tensor table of a model folder")
+    i.add_argument("-m", "--model", required=True)
+
+    r = sub.add_parser("random", help="write a model folder with random weights")
+    r.add_argument("--config", required=True, help="config.json to build from")
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--out", required=True)
+    r.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+
+    sub.add_parser("doctor", help="GPU, compiler and kernel-library report")
+
+    b = sub.add_parser("bench", help="prefill and decode throughput of a model folder")
+    b.add_argument("-m", "--model", default=None, help="model folder (default: the LFM2.5-1.2B shape with random weights)")
+    b.add_argument("--bench-prompt-tokens", type=int, default=2048)
+    b.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    return ap
+
+
+def cmd_generate(a) -> int:
+    from . import Engine, SamplingParams, load_model
+    prompts = list(a.prompt_ids)
+    if a.prompts_file:
+        text = open(a.prompts_file).read().strip()
+        prompts += json.loads(text) if text.startswith("[") else [_ids(line) for line in text.splitlines() if line.strip()]
+    if not prompts:
+        print("generate: no prompts (use --prompt-ids or --prompts-file)", file=sys.stderr)
+        return 2
+    model = load_model(a.model, a.dtype, "cuda:0")
+    ctx = a.ctx_size or model.spec.max_positions or 16384
+    model.spec.max_positions = ctx
+    longest = max(len(p) for p in prompts) + a.max_tokens
+    batch = min(a.max_batch, len(prompts))
+    eng = Engine(model, max_tokens=batch * (min(ctx, longest) + 64), max_batch=batch)
+    sp = SamplingParams(temperature=a.temp, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p,
+                        repetition_penalty=a.rep_penalty, presence_penalty=a.presence_penalty,
+                        frequency_penalty=a.frequency_penalty, seed=a.seed)
+    t0 = time.perf_counter()
+    reqs = eng.generate(prompts, a.max_tokens, sp, stop_token_ids=a.stop_ids, return_requests=True)
+    dt = time.perf_counter() - t0
+    n_new = sum(len(r.output) for r in reqs)
+    if a.json:
+        print(json.dumps({"outputs": [r.output for r in reqs], "finish": [r.finish_reason for r in reqs],
+                          "seconds": dt, "new_tokens": n_new}))
+    else:
+        for r in reqs:
+            print(" ".join(str(t) for t in r.output))
+        print(f"[{n_new} tokens in {dt:.2f} s, {n_new / dt:.1f} tok/s]", file=sys.stderr)
+    return 0
+
+
+def cmd_info(a) -> int:
+    from .config import read_config_json
+    from .engine.model import describe_config
+    from .weights import read_model_headers
+    cfg = read_config_json(a.model)
+    config, spec = describe_config(cfg)
+    print(f"architecture: {cfg['architectures'][0]}")
+    for k, v in config.to_dict().items():
+        print(f"  {k}: {v}")
+    for k in ("head_dim", "kv_dim", "ff_dim", "attn_layer_ids", "conv_layer_ids"):
+        if hasattr(config, k):
+            print(f"  ({k}: {getattr(config, k)})")
+    entries = read_model_headers(a.model)
+    total = 0
+    print(f"tensors: {len(entries)}")
+    for name, e in entries.items():
+        n = 1
+        for s in e.shape:
+            n *= s
+        total += n
+        print(f"  {name:56s} {e.dtype:5s} {list(e.shape)}")
+    print(f"parameters: {total:,}")
+    return 0
+
+
+def cmd_random(a) -> int:
+    from . import write_random_model
+    with open(a.config) as f:
+        cfg = json.load(f)
+    print(write_random_model(a.out, cfg, a.seed, a.store_dtype))
+    return 0
+
+
+def cmd_doctor(a) -> int:
+    import torch
+    from .ops.build import LIBRARIES, build_dir, find_nvcc, library_path
+    import os
+    print(f"torch {torch.__version__}, CUDA available: {torch.cuda.is_available()}")
+    if torch.cuda.is_available():
+        p = torch.cuda.get_device_properties(0)
+        print(f"GPU 0: {p.name}, sm_{p.major}{p.minor}, {p.multi_processor_count} SMs, {p.total_memory / 2**30:.1f} GiB")
+        if (p.major, p.minor) != (10, 0):
+            print("  warning: the kernels are compiled for sm_100a only")
+    try:
+        print(f"nvcc: {find_nvcc()}")
+    except Exception as e:  # noqa: BLE001
+        print(f"nvcc: NOT FOUND ({e})")
+    print(f"build folder: {build_dir()}")
+    for name in LIBRARIES:
+        path = library_path(name)
+        print(f"  {name}: {'built' if os.path.isfile(path) else 'not built yet'} ({os.path.basename(path)})")
+    return 0
+
+
+def cmd_bench(a) -> int:
+    import statistics
+    import torch
+    from . import Engine, SamplingParams, load_model
+    if a.model is None:
+        import os
+        import runpy
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        sys.argv = [os.path.join(root, "bench.py")]
+        runpy.run_path(sys.argv[0], run_name="__main__")
+        return 0
+    model = load_model(a.model, a.dtype, "cuda:0")
+    T = a.bench_prompt_tokens
+    eng = Engine(model, max_tokens=2 * (T + 64), max_batch=2, max_step_tokens=max(T, 64))
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, model.vocab_size, (T,), generator=g).tolist()
+    times = []
+    for i in range(4):
+        s = eng.open()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.step([(s, prompt)], "last", copy=False)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+        eng.close(s)
+    pre = statistics.median(times[1:])
+    first = {}
+    t0 = time.perf_counter()
+    out = eng.generate([prompt], 25, SamplingParams.greedy(), stop_token_ids=[],
+                       on_token=lambda i, t: first.setdefault("t", time.perf_counter()))
+    dt = time.perf_counter() - first["t"]
+    print(json.dumps({"prompt_tokens": T, "prefill_tok_s": T / pre, "ttft_ms": (first["t"] - t0) * 1e3,
+                      "decode_tok_s": (len(out[0]) - 1) / dt, "generated": len(out[0])}))
+    return 0
+
+
+def main(argv=None) -> int:
+    a = build_parser().parse_args(argv)
+    return {"generate": cmd_generate, "info": cmd_info, "random": cmd_random, "doctor": cmd_doctor,
+            "bench": cmd_bench}[a.command](a)

@@ -143,7 +143,7 @@ def plain_short_conv(u: torch.Tensor, w_in: torch.Tensor, w_conv: torch.Tensor,
 
 def plain_attention(u: torch.Tensor, wq, wk, wv, wo, q_norm_w, k_norm_w, *, nh: int,
                     nkv: int, hd: int, eps: float, theta: float, style: str,
-                    window: int = 0) -> torch.Tensor:
+                    window: int = 0, kv=None, return_kv: bool = False):
     """Grouped-query attention over a whole sequence u [T, H] (already normed).
 
     q, k, v projections without bias; per-head RMSNorm of q and k with one
@@ -156,18 +156,24 @@ def plain_attention(u: torch.Tensor, wq, wk, wv, wo, q_norm_w, k_norm_w, *, nh: 
     293-298, 326-335; reference/reference_engine.py:130-169.
     ``window`` > 0 keeps only the last ``window`` keys (t > position - window);
     the reference has no window, this serves tests of the generic kernel.
+    ``kv`` = (k, v) as another layer stored them (after norm and rotation)
+    replaces this layer's own keys and values; ``return_kv`` also returns them.
+    Both serve tests of a layer that reads another layer's cache.
     """
     T = u.shape[0]
+    pos = torch.arange(T)
     q = (u @ wq.T).reshape(T, nh, hd)
-    k = (u @ wk.T).reshape(T, nkv, hd)
-    v = (u @ wv.T).reshape(T, nkv, hd)
     if q_norm_w is not None:
         q = plain_rms_norm(q, q_norm_w, eps)
-    if k_norm_w is not None:
-        k = plain_rms_norm(k, k_norm_w, eps)
-    pos = torch.arange(T)
     q = plain_rope(q, pos, theta, style)
-    k = plain_rope(k, pos, theta, style)
+    if kv is None:
+        k = (u @ wk.T).reshape(T, nkv, hd)
+        v = (u @ wv.T).reshape(T, nkv, hd)
+        if k_norm_w is not None:
+            k = plain_rms_norm(k, k_norm_w, eps)
+        k = plain_rope(k, pos, theta, style)
+    else:
+        k, v = kv
     group = nh // nkv
     scale = 1.0 / math.sqrt(hd)
     out = torch.zeros(T, nh, hd, dtype=u.dtype)
@@ -182,7 +188,8 @@ def plain_attention(u: torch.Tensor, wq, wk, wv, wo, q_norm_w, k_norm_w, *, nh: 
         s = s.masked_fill(~mask, float("-inf"))
         p = torch.softmax(s, dim=-1)
         out[:, h, :] = p @ v[:, g, :]
-    return out.reshape(T, nh * hd) @ wo.T
+    res = out.reshape(T, nh * hd) @ wo.T
+    return (res, (k, v)) if return_kv else res
 
 
 def plain_swiglu(g: torch.Tensor, w1, w3, w2) -> torch.Tensor:

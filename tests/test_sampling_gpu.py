@@ -1,0 +1,90 @@
+"""The sampling kernel against the plain sampler on the same logits."""
+import pytest
+import torch
+
+import plain_lfm2 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_kernel(logits, seed, streams, steps, recent, **kw):
+    from mivi_v4_b200.ops import kernels as K
+    B, V = logits.shape
+    lg = logits.to(DEV)
+    work = torch.empty(B, V, device=DEV)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    rec = torch.zeros(B, 64, dtype=torch.int32)
+    nrec = torch.zeros(B, dtype=torch.int32)
+    for b, r in enumerate(recent):
+        r = list(r)[-64:]
+        rec[b, :len(r)] = torch.tensor(r, dtype=torch.int32)
+        nrec[b] = len(r)
+    K.sample(lg, work, out, recent=rec.to(DEV), n_recent=nrec.to(DEV), seed=seed,
+             streams=torch.tensor(streams, dtype=torch.int32, device=DEV),
+             steps=torch.tensor(steps, dtype=torch.int32, device=DEV), **kw)
+    assert torch.equal(lg.cpu(), logits)              # the caller's logits are left alone
+    return out.tolist()
+
+
+CASES = [
+    dict(temperature=0.0),
+    dict(temperature=0.0, repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1),
+    dict(temperature=0.8),
+    dict(temperature=1.5, top_k=5),
+    dict(temperature=0.7, top_p=0.9),
+    dict(temperature=1.0, min_p=0.05),
+    dict(temperature=0.9, top_k=40, top_p=0.9, min_p=0.02, repetition_penalty=1.1),
+    dict(temperature=0.2, top_k=40, top_p=0.9, repetition_penalty=1.05),        # the reference's defaults
+    dict(temperature=2.0, top_p=0.3),
+]
+
+
+@pytest.mark.parametrize("kw", CASES, ids=[str(i) for i in range(len(CASES))])
+@pytest.mark.parametrize("V", [301, 4100])
+def test_sample_matches_plain(kw, V):
+    g = torch.Generator().manual_seed(V)
+    B = 6
+    logits = torch.randn(B, V, generator=g) * 3.0
+    logits[1, 7] = logits[1].max() + 0.0                 # a tie for the maximum: the first one wins
+    logits[1, 3] = logits[1, 7]
+    logits[2] = torch.round(logits[2])                   # many exact ties inside the distribution
+    seed, streams, steps = 1234, [0, 1, 2, 3, 70000, 5], [0, 5, 9, 2, 1, 63]
+    recent = [[], [3, 3, 7, 9], list(range(80)), [V - 1], [5] * 10, [1, 2, 3]]
+    got = run_kernel(logits, seed, streams, steps, recent, **kw)
+    for b in range(B):
+        want = P.plain_sample(logits[b], recent=recent[b][-64:], u=P.plain_uniform(seed, streams[b], steps[b]), **kw)
+        assert got[b] == want, (b, kw, got[b], want)
+
+
+def test_draw_depends_on_stream_and_step_not_on_the_batch():
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(1, 500, generator=g).repeat(8, 1)
+    a = run_kernel(logits, 9, [4] * 8, list(range(8)), [[]] * 8, temperature=1.0)
+    assert len(set(a)) > 3                                # different steps draw different tokens
+    b = run_kernel(logits[:3], 9, [4] * 3, [5, 6, 7], [[]] * 3, temperature=1.0)
+    assert b == a[5:8]                                    # the same (stream, step) in another batch
+    c = run_kernel(logits, 10, [4] * 8, list(range(8)), [[]] * 8, temperature=1.0)
+    assert c != a
+
+
+def test_distribution_of_draws():
+    p = torch.tensor([0.5, 0.25, 0.125, 0.125])
+    logits = p.log().repeat(4000, 1)
+    got = run_kernel(logits, 3, list(range(4000)), [0] * 4000, [[]] * 4000, temperature=1.0)
+    freq = torch.bincount(torch.tensor(got), minlength=4).double() / 4000
+    assert (freq - p.double()).abs().max() < 0.03
+    got = run_kernel(logits, 3, list(range(4000)), [0] * 4000, [[]] * 4000, temperature=1.0, top_p=0.7)
+    freq = torch.bincount(torch.tensor(got), minlength=4).double() / 4000
+    assert freq[2] == 0 and freq[3] == 0 and abs(freq[0] - 2 / 3) < 0.03
+
+
+def test_large_vocabulary():
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(2, 65536, generator=g) * 2
+    assert run_kernel(logits, 0, [0, 1], [0, 0], [[], []], temperature=0.0) == logits.argmax(1).tolist()
+    got = run_kernel(logits, 0, [0, 1], [0, 0], [[], []], temperature=1.0, top_k=3)
+    top3 = logits.topk(3, dim=1).indices.tolist()
+    assert got[0] in top3[0] and got[1] in top3[1]
+    want = [P.plain_sample(logits[b], temperature=1.0, top_k=3, u=P.plain_uniform(0, b, 0)) for b in range(2)]
+    assert got == want
