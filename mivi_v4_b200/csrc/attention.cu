@@ -29,6 +29,7 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
                                   const int* __restrict__ page_table, int table_stride, int page_shift,
                                   T* __restrict__ pool, long long page_stride, int append,
                                   T* __restrict__ q_out, int N, int nh, int nkv, int hd) {
+    mv_pdl_begin();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int slots_per_tok = nh + 2 * nkv;
@@ -91,11 +92,11 @@ MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, flo
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
     if (dtype == MV_DT_BF16)
-        qk_prepare_kernel<<<blocks, threads, 0, stream>>>(
+        mv_launch(qk_prepare_kernel<__nv_bfloat16>, blocks, threads, 0, stream, 
             qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
             page_shift, (__nv_bfloat16*)pool, page_stride, append, (__nv_bfloat16*)q_out, N, nh, nkv, hd);
     else
-        qk_prepare_kernel<<<blocks, threads, 0, stream>>>(
+        mv_launch(qk_prepare_kernel<float>, blocks, threads, 0, stream, 
             qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
             page_shift, (float*)pool, page_stride, append, (float*)q_out, N, nh, nkv, hd);
     return mv_launch_status();
@@ -112,6 +113,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ pool, lo
                          const int* __restrict__ page_table, int table_stride, int page_shift,
                          const int* __restrict__ positions, const int* __restrict__ seq_of,
                          T* __restrict__ o, int N, int nh, int nkv, int hd, float scale, int window) {
+    mv_pdl_begin();
     __shared__ float qs[4][MV_MAX_HEAD_DIM];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * 4 + wib;
@@ -189,11 +191,11 @@ MV_API int mv_attention_generic(const void* q, const void* pool, long long page_
     while ((1 << page_shift) < page_size) ++page_shift;
     const unsigned blocks = (unsigned)(((long long)N * nh + 3) / 4);
     if (dtype == MV_DT_BF16)
-        attention_generic_kernel<<<blocks, 128, 0, stream>>>(
+        mv_launch(attention_generic_kernel<__nv_bfloat16>, blocks, 128, 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_stride, page_table, table_stride,
             page_shift, positions, seq_of, (__nv_bfloat16*)o, N, nh, nkv, hd, scale, window);
     else
-        attention_generic_kernel<<<blocks, 128, 0, stream>>>(
+        mv_launch(attention_generic_kernel<float>, blocks, 128, 0, stream, 
             (const float*)q, (const float*)pool, page_stride, page_table, table_stride, page_shift,
             positions, seq_of, (float*)o, N, nh, nkv, hd, scale, window);
     return mv_launch_status();

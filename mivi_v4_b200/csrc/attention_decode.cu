@@ -32,6 +32,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pool, lon
                         const int* __restrict__ positions, const int* __restrict__ seq_of, T* __restrict__ o,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                         int nh, int nkv, int hd, float scale, int window, int splits, int head_tiles) {
+    mv_pdl_begin();
     extern __shared__ float sm[];
     // q heads [GT][hd] (scaled), then per warp: o [GT][hd], m [GT], l [GT]
     float* qs = sm;
@@ -75,29 +76,60 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pool, lon
     for (int run = run_begin + warp; run < run_end; run += WARPS) {
         const int t = lo + (run << 5) + lane;
         const bool valid = t <= pos;
-        const T* krow = nullptr;
+        const int cnt = min(32, pos - (lo + (run << 5)) + 1);
+        // the row of this lane's key; lanes past the last key point at the run's first row
+        const int tt = valid ? t : lo + (run << 5);
+        const T* krow = pool + (size_t)table[tt >> page_shift] * page_stride +
+                        ((size_t)g * page_size + (tt & (page_size - 1))) * hd;
+        const unsigned long long kaddr = (unsigned long long)krow;
         float s[GT];
+        constexpr int EPV = 16 / sizeof(T);                // elements per 16-byte load
+        constexpr int VG = R <= 2 ? 32 : (R == 4 ? 16 : 8);  // keys whose values are requested together
+        float vv[VG][R];
+        auto load_values = [&](int j0) {
 #pragma unroll
-        for (int hh = 0; hh < GT; ++hh) s[hh] = -INFINITY;
-        if (valid) {
-            const int page = table[t >> page_shift];
-            krow = pool + (size_t)page * page_stride + ((size_t)g * page_size + (t & (page_size - 1))) * hd;
+            for (int jj = 0; jj < VG; ++jj) {
+                const T* vrow = (const T*)__shfl_sync(0xffffffffu, kaddr, (j0 + jj) & 31) + v_off;
 #pragma unroll
-            for (int hh = 0; hh < GT; ++hh) s[hh] = 0.f;
-            for (int d = 0; d < hd; d += 8) {
-                float kv[8];
-                mv_load8(krow + d, kv);
+                for (int r = 0; r < R; ++r) {
+                    const int d = lane + 32 * r;
+                    vv[jj][r] = d < hd ? mv_to_f32(vrow[d]) : 0.f;
+                }
+            }
+        };
+        // Everything this run needs from memory is requested before any of it is used: a stretch of
+        // this lane's key and the values of the first VG keys.  A lane then waits once, not per load.
+        uint4 raw[8];
 #pragma unroll
-                for (int hh = 0; hh < GT; ++hh) {
-                    const float* qh = qs + hh * hd + d;
+        for (int v = 0; v < 8; ++v)
+            if (v * EPV < hd) raw[v] = *reinterpret_cast<const uint4*>(krow + v * EPV);
+        load_values(0);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) s[hh] = fmaf(qh[e], kv[e], s[hh]);
+        for (int hh = 0; hh < GT; ++hh) s[hh] = 0.f;
+        for (int d0 = 0; d0 < hd; d0 += 8 * EPV) {
+            if (d0 > 0) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    if (d0 + v * EPV < hd) raw[v] = *reinterpret_cast<const uint4*>(krow + d0 + v * EPV);
+            }
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                if (d0 + v * EPV < hd) {
+                    float kv[EPV];
+                    mv_unpack16(raw[v], kv, (const T*)nullptr);
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        const float* qh = qs + hh * hd + d0 + v * EPV;
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) s[hh] = fmaf(qh[e], kv[e], s[hh]);
+                    }
                 }
             }
         }
         float p[GT];
 #pragma unroll
         for (int hh = 0; hh < GT; ++hh) {
+            if (!valid) s[hh] = -INFINITY;
             const float m_new = fmaxf(m[hh], mv_warp_max(s[hh]));
             p[hh] = valid ? expf(s[hh] - m_new) : 0.f;
             const float corr = expf(m[hh] - m_new);
@@ -106,21 +138,17 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pool, lon
             for (int r = 0; r < R; ++r) acc[hh][r] *= corr;
             m[hh] = m_new;
         }
-        const int cnt = min(32, pos - (lo + (run << 5)) + 1);
-        const unsigned long long kaddr = (unsigned long long)krow;
-        for (int j = 0; j < cnt; ++j) {
-            const T* vrow = (const T*)__shfl_sync(0xffffffffu, kaddr, j) + v_off;
-            float vv[R];
+        // weighted sum of the values; lanes past the last key carry weight 0
+        for (int j0 = 0; j0 < cnt; j0 += VG) {
+            if (j0 > 0) load_values(j0);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int d = lane + 32 * r;
-                vv[r] = d < hd ? mv_to_f32(vrow[d]) : 0.f;
-            }
+            for (int jj = 0; jj < VG; ++jj) {
 #pragma unroll
-            for (int hh = 0; hh < GT; ++hh) {
-                const float pj = __shfl_sync(0xffffffffu, p[hh], j);
+                for (int hh = 0; hh < GT; ++hh) {
+                    const float pj = __shfl_sync(0xffffffffu, p[hh], (j0 + jj) & 31);
 #pragma unroll
-                for (int r = 0; r < R; ++r) acc[hh][r] = fmaf(pj, vv[r], acc[hh][r]);
+                    for (int r = 0; r < R; ++r) acc[hh][r] = fmaf(pj, vv[jj][r], acc[hh][r]);
+                }
             }
         }
     }
@@ -195,7 +223,7 @@ int launch(const void* q, const void* pool, long long page_stride, const int* pa
            cudaStream_t stream) {
     const size_t smem = (size_t)(GT * hd + WARPS * GT * hd + 2 * WARPS * GT) * sizeof(float);
     dim3 grid(N, nkv * head_tiles, splits);
-    attention_decode_kernel<T, GT, R><<<grid, WARPS * 32, smem, stream>>>(
+    mv_launch(attention_decode_kernel<T, GT, R>, grid, WARPS * 32, smem, stream, 
         (const T*)q, (const T*)pool, page_stride, page_table, table_stride, page_shift, positions, seq_of,
         (T*)o, part_o, part_ml, tickets, nh, nkv, hd, scale, window, splits, head_tiles);
     return mv_launch_status();

@@ -10,6 +10,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tok,
                              float* __restrict__ x, int H) {
+    mv_pdl_begin();
     const int n = blockIdx.x;
     const T* row = table + (size_t)tok[n] * H;
     float* out = x + (size_t)n * H;
@@ -21,9 +22,9 @@ MV_API int mv_embed(const void* table, int table_dtype, const int* tok, float* x
     if (N <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == MV_DT_BF16)
-        embed_kernel<<<N, threads, 0, stream>>>((const __nv_bfloat16*)table, tok, x, H);
+        mv_launch(embed_kernel<__nv_bfloat16>, N, threads, 0, stream, (const __nv_bfloat16*)table, tok, x, H);
     else
-        embed_kernel<<<N, threads, 0, stream>>>((const float*)table, tok, x, H);
+        mv_launch(embed_kernel<float>, N, threads, 0, stream, (const float*)table, tok, x, H);
     return mv_launch_status();
 }
 
@@ -33,6 +34,7 @@ MV_API int mv_embed(const void* table, int table_dtype, const int* tok, float* x
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ y, const int* __restrict__ rows, int H, float eps) {
+    mv_pdl_begin();
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -48,38 +50,90 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int h = threadIdx.x; h < H; h += blockDim.x) yr[h] = mv_from_f32<TO>(xr[h] * scale * w[h]);
 }
 
+// The same for rows that fit the registers of one block (H a multiple of 4, at most
+// 8192): each thread keeps its float4s, so the row is read once.
+template <typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_regs_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
+                    const int* __restrict__ rows, int H, float eps) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    constexpr int MAXV = 8192 / 4 / THREADS;
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * H);
+    const int nv = H >> 2;
+    float4 v[MAXV];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        const int c = threadIdx.x + j * THREADS;
+        if (c < nv) {
+            v[j] = xr[c];
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    ss = mv_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* yr = y + (size_t)i * H;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        const int c = threadIdx.x + j * THREADS;
+        if (c < nv) {
+            const float4 ww = reinterpret_cast<const float4*>(w)[c];
+            yr[4 * c + 0] = mv_from_f32<TO>(v[j].x * scale * ww.x);
+            yr[4 * c + 1] = mv_from_f32<TO>(v[j].y * scale * ww.y);
+            yr[4 * c + 2] = mv_from_f32<TO>(v[j].z * scale * ww.z);
+            yr[4 * c + 3] = mv_from_f32<TO>(v[j].w * scale * ww.w);
+        }
+    }
+}
+
 MV_API int mv_rmsnorm(const float* x, const float* w, void* y, int y_dtype, const int* rows,
                       int n_rows, int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (H % 4 == 0 && H <= 8192 && H >= 256 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+        if (y_dtype == MV_DT_BF16)
+            mv_launch(rmsnorm_regs_kernel<__nv_bfloat16, 256>, n_rows, 256, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
+        else
+            mv_launch(rmsnorm_regs_kernel<float, 256>, n_rows, 256, 0, stream, x, w, (float*)y, rows, H, eps);
+        return mv_launch_status();
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (y_dtype == MV_DT_BF16)
-        rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows, H, eps);
+        mv_launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
     else
-        rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, w, (float*)y, rows, H, eps);
+        mv_launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)y, rows, H, eps);
     return mv_launch_status();
 }
 
 // ------------------------------------------------------------------- swiglu
-// h[n, f] = silu(gu[n, f]) * gu[n, F + f], silu(a) = a / (1 + e^-a).
+// h[n, f] = silu(gate) * up, silu(a) = a / (1 + e^-a).  group == 0: gate = gu[n, f],
+// up = gu[n, F + f] (the two halves end to end).  group == 16: the columns come in
+// groups of 16 gate values followed by the 16 up values of the same features.
 template <typename TO>
-__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ h, long long total, int F) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ h, long long total, int F, int group) {
+    mv_pdl_begin();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long n = i / F;
     const int f = (int)(i - n * F);
-    const float a = gu[n * 2 * F + f];
-    const float b = gu[n * 2 * F + F + f];
+    const int ga = group ? (f / group) * 2 * group + f % group : f;
+    const int gb = group ? ga + group : F + f;
+    const float a = gu[n * 2 * F + ga];
+    const float b = gu[n * 2 * F + gb];
     h[i] = mv_from_f32<TO>(a / (1.0f + expf(-a)) * b);
 }
 
-MV_API int mv_swiglu(const float* gu, void* h, int h_dtype, int N, int F, cudaStream_t stream) {
+MV_API int mv_swiglu(const float* gu, void* h, int h_dtype, int N, int F, int group, cudaStream_t stream) {
     const long long total = (long long)N * F;
     if (total <= 0) return 0;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (h_dtype == MV_DT_BF16)
-        swiglu_kernel<<<blocks, threads, 0, stream>>>(gu, (__nv_bfloat16*)h, total, F);
+        mv_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, gu, (__nv_bfloat16*)h, total, F, group);
     else
-        swiglu_kernel<<<blocks, threads, 0, stream>>>(gu, (float*)h, total, F);
+        mv_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gu, (float*)h, total, F, group);
     return mv_launch_status();
 }

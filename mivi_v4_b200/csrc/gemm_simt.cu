@@ -19,6 +19,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const float* __restrict__ bias,
                  void* __restrict__ out, int mode, int M, int N, int K, int ldo) {
+    mv_pdl_begin();
     __shared__ float Xs[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -80,10 +81,10 @@ MV_API int mv_gemm_simt(const void* X, const void* W, int in_dtype, const float*
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (in_dtype == MV_DT_BF16)
-        gemm_simt_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
+        mv_launch(gemm_simt_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
                                                    bias, out, mode, M, N, K, ldo);
     else
-        gemm_simt_kernel<<<grid, 256, 0, stream>>>((const float*)X, (const float*)W, bias, out, mode,
+        mv_launch(gemm_simt_kernel<float>, grid, 256, 0, stream, (const float*)X, (const float*)W, bias, out, mode,
                                                    M, N, K, ldo);
     return mv_launch_status();
 }

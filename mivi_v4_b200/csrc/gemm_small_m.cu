@@ -12,15 +12,27 @@
 // one mma as those four k, the last 4 the next mma, and X is loaded with the
 // same rule, so no shuffle and no shared-memory staging of W is needed.
 //
-// The warps of a block split K and add their partial sums through shared
-// memory in warp order, so the result is the same in every run.
+// Work is cut small so that many blocks are resident on every SM and their
+// phases (load, multiply, reduce) overlap: a block is 4 warps on one tile of
+// rows and one slice of K.  The slices of a tile form a thread-block cluster
+// along K; each block adds its warps' partial sums in shared memory, then the
+// cluster's first block reads the others' sums through distributed shared
+// memory, adds them in rank order and runs the epilogue.  Every sum has a fixed
+// order, so the result is the same in every run.
+//
+// The first loads of W are issued before the kernel waits for its predecessor
+// (programmatic dependent launch): weights do not depend on it, and the stream
+// of weights from HBM then does not pause at the kernel boundary.
 //
 // What it replaces in the reference: quantized_matvec, one output row per
 // dot product over the input (crates/mivi-quant/src/lib.rs:75-135).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
-namespace {
+namespace cg = cooperative_groups;
 
+namespace {
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
@@ -37,17 +49,21 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 }
 
 // NT: n-tiles of 8 tokens; RT: tiles of 16 weight rows per warp; UNROLL: k-steps
-// of 32 whose W loads are issued together (bytes in flight per warp).
-template <int NT, int RT, int UNROLL>
-__global__ void __launch_bounds__(512)
+// of 32 whose W loads are issued together.  gridDim.x = K slices (= cluster
+// size), gridDim.y = row tiles.
+template <int NT, int RT, int UNROLL, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K,
                     int ldo) {
-    extern __shared__ float red[];                      // [warps][RT*16][NT*8 + 1]
     constexpr int ROWS = RT * 16, COLS = NT * 8, LDR = COLS + 1;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    extern __shared__ float sm[];
+    float* red = sm;                                   // [WARPS][ROWS][LDR] partial sums of the warps
+    float* csum = sm + WARPS * ROWS * LDR;             // [ROWS][LDR] their sum: this block's share
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * ROWS;
+    const int n0 = blockIdx.y * ROWS;
+    const int slices = gridDim.x, slice = blockIdx.x;
 
     float acc[RT][NT][4];
 #pragma unroll
@@ -72,13 +88,14 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         xrow[j] = X + (size_t)min(j * 8 + g, M - 1) * K;
     }
 
+    // k-steps of 32: first cut into the cluster's slices, then into this block's warps
     const int ksteps = (K + 31) >> 5;
-    // contiguous run of k-steps for this warp
-    const int per = (ksteps + nwarps - 1) / nwarps;
-    const int ks_begin = warp * per, ks_end = min(ksteps, ks_begin + per);
+    const int per_slice = (ksteps + slices - 1) / slices;
+    const int s_begin = slice * per_slice, s_end = min(ksteps, s_begin + per_slice);
+    const int per = (max(0, s_end - s_begin) + WARPS - 1) / WARPS;
+    const int ks_begin = s_begin + warp * per, ks_end = min(s_end, ks_begin + per);
 
-    for (int ks = ks_begin; ks < ks_end; ks += UNROLL) {
-        uint4 w[UNROLL][RT][2];
+    auto load_w = [&](uint4 (&w)[UNROLL][RT][2], int ks) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = ((ks + u) << 5) + 8 * t;
@@ -89,24 +106,37 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
                 for (int h = 0; h < 2; ++h)
                     w[u][r][h] = ok ? ld_stream16(wrow[r][h] + k) : make_uint4(0, 0, 0, 0);
         }
+    };
+    uint4 w[UNROLL][RT][2];
+    load_w(w, ks_begin);              // weights do not depend on the kernel before this one
+    mv_pdl_wait();
+    for (int ks = ks_begin; ks < ks_end; ks += UNROLL) {
+        uint4 x[UNROLL][NT];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = ((ks + u) << 5) + 8 * t;
             const bool ok = (ks + u) < ks_end && k < K;
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const uint4 x = (ok && xok[j]) ? *reinterpret_cast<const uint4*>(xrow[j] + k)
-                                               : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < NT; ++j)
+                x[u][j] = (ok && xok[j]) ? *reinterpret_cast<const uint4*>(xrow[j] + k) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
 #pragma unroll
                 for (int r = 0; r < RT; ++r) {
-                    mma_bf16(acc[r][j], w[u][r][0].x, w[u][r][1].x, w[u][r][0].y, w[u][r][1].y, x.x, x.y);
-                    mma_bf16(acc[r][j], w[u][r][0].z, w[u][r][1].z, w[u][r][0].w, w[u][r][1].w, x.z, x.w);
+                    mma_bf16(acc[r][j], w[u][r][0].x, w[u][r][1].x, w[u][r][0].y, w[u][r][1].y, x[u][j].x, x[u][j].y);
+                    mma_bf16(acc[r][j], w[u][r][0].z, w[u][r][1].z, w[u][r][0].w, w[u][r][1].w, x[u][j].z, x[u][j].w);
                 }
-            }
-        }
+        if (ks + UNROLL < ks_end) load_w(w, ks + UNROLL);
     }
+    // From here on this block only adds up and writes: the next kernel may start to launch and
+    // send out its own first loads.  (Earlier would let its blocks take the place of blocks of
+    // this kernel that have not started yet.)
+    mv_pdl_launch_dependents();
 
-    // partial sums of all warps -> shared memory
+    // the warps' partial sums -> shared memory -> their sum in warp order
     float* mine = red + (size_t)warp * ROWS * LDR;
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -119,56 +149,127 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
             mine[(row + 8) * LDR + col + 1] = acc[r][j][3];
         }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < ROWS * M; idx += blockDim.x) {
-        const int r = idx % ROWS, m = idx / ROWS;
-        const int n = n0 + r;
-        if (n >= N) continue;
+    for (int idx = threadIdx.x; idx < ROWS * COLS; idx += WARPS * 32) {
+        const int r = idx / COLS, c = idx - r * COLS;
         float v = 0.f;
-        for (int wp = 0; wp < nwarps; ++wp) v += red[(size_t)wp * ROWS * LDR + r * LDR + m];
-        if (bias) v += bias[n];
-        const size_t o = (size_t)m * ldo + n;
-        if (mode == 0) ((float*)out)[o] = v;
-        else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-        else ((float*)out)[o] += v;
+#pragma unroll
+        for (int wp = 0; wp < WARPS; ++wp) v += red[(size_t)wp * ROWS * LDR + r * LDR + c];
+        csum[r * LDR + c] = v;
     }
+
+    // the slices of this tile: the cluster's first block adds them in rank order
+    const float* share[8];
+    if (slices > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (slice == 0)
+            for (int s = 0; s < slices; ++s) share[s] = cluster.map_shared_rank(csum, s);
+    } else {
+        __syncthreads();
+        share[0] = csum;
+    }
+    if (slice == 0) {
+        auto total = [&](int r, int m) {
+            float v = 0.f;
+            for (int s = 0; s < slices; ++s) v += share[s][r * LDR + m];
+            return v;
+        };
+        if (mode == 3) {
+            // rows come in groups of 32: 16 gate rows, then the 16 up rows of the same features
+            // (RT == 2, so a block owns whole groups); out[m, f] = silu(gate) * up in bfloat16
+            constexpr int HALF = ROWS / 2;
+            for (int idx = threadIdx.x; idx < HALF * M; idx += WARPS * 32) {
+                const int r = idx % HALF, m = idx / HALF;
+                const int rg = (r >> 4) * 32 + (r & 15);           // gate row within the block
+                if (n0 + rg + 16 >= N) continue;
+                float a = total(rg, m), b = total(rg + 16, m);
+                if (bias) { a += bias[n0 + rg]; b += bias[n0 + rg + 16]; }
+                const int f = ((n0 + rg) >> 5) * 16 + (rg & 15);
+                ((__nv_bfloat16*)out)[(size_t)m * ldo + f] = __float2bfloat16_rn(a / (1.0f + expf(-a)) * b);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < ROWS * M; idx += WARPS * 32) {
+                const int r = idx % ROWS, m = idx / ROWS;
+                const int n = n0 + r;
+                if (n >= N) continue;
+                float v = total(r, m);
+                if (bias) v += bias[n];
+                const size_t o = (size_t)m * ldo + n;
+                if (mode == 0) ((float*)out)[o] = v;
+                else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+                else ((float*)out)[o] += v;
+            }
+        }
+    }
+    // nobody leaves while the first block may still read its shared memory
+    if (slices > 1) cg::this_cluster().sync();
 }
 
-template <int NT, int RT, int UNROLL>
+template <int NT, int RT, int UNROLL, int WARPS>
 int launch(const void* W, const void* X, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
            cudaStream_t stream) {
     constexpr int ROWS = RT * 16, LDR = NT * 8 + 1;
     const int ksteps = (K + 31) / 32;
-    int warps = ksteps / (2 * UNROLL);
-    warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
-    const size_t smem = (size_t)warps * ROWS * LDR * sizeof(float);
+    const int tiles = (N + ROWS - 1) / ROWS;
+    // slices of K: every warp should still have UNROLL k-steps, and there is no point in many
+    // more blocks than the GPU holds at once (about 8 per SM)
+    int slices = ksteps / (WARPS * UNROLL);
+    slices = slices < 1 ? 1 : (slices > 8 ? 8 : slices);
+    while (slices > 1 && (long long)tiles * slices > 148 * 8) slices >>= 1;
+    const size_t smem = (size_t)(WARPS + 1) * ROWS * LDR * sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(gemm_small_m_kernel<NT, RT, UNROLL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(gemm_small_m_kernel<NT, RT, UNROLL, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             160 * 1024);
         attr_set = true;
     }
-    const unsigned blocks = (unsigned)((N + ROWS - 1) / ROWS);
-    gemm_small_m_kernel<NT, RT, UNROLL><<<blocks, warps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)W, (const __nv_bfloat16*)X, bias, out, mode, M, N, K, ldo);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(slices, tiles);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (mv_pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (slices > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = slices;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaLaunchKernelEx(&cfg, gemm_small_m_kernel<NT, RT, UNROLL, WARPS>, (const __nv_bfloat16*)W, (const __nv_bfloat16*)X, bias,
+                       out, mode, M, N, K, ldo);
     return mv_launch_status();
 }
 
 }  // namespace
 
-// mode: 0 store float32, 1 store bfloat16, 2 add into float32.  Needs
+// mode: 0 store float32, 1 store bfloat16, 2 add into float32, 3 SwiGLU (W rows in
+// groups of 16 gate + 16 up; out is bfloat16 [M, N/2] with row stride ldo).  Needs
 // 1 <= M <= 64, K a multiple of 8, and 16-byte aligned operands.
 MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void* out, int mode, int M,
                            int N, int K, int ldo, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
     const int nt = (M + 7) / 8;
-    // 32 rows per warp halve the re-reads of X; 16 rows keep enough blocks for a narrow matrix
-    const bool wide = N >= 32 * 2 * 148;
-#define MV_GO(NT, RT, U) return launch<NT, RT, U>(W, X, bias, out, mode, M, N, K, ldo, stream)
+    // 32 rows per warp halve the re-reads of X and are what the SwiGLU epilogue needs;
+    // 16 rows keep more blocks for a narrow matrix
+    const bool wide = N >= 32 * 2 * 148 || mode == 3;
+#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, stream)
+    // few tokens: small blocks, many per SM; many tokens: large blocks, so that X is re-read less
     switch (nt) {
-        case 1: if (wide) MV_GO(1, 2, 4); else MV_GO(1, 1, 4);
-        case 2: if (wide) MV_GO(2, 2, 4); else MV_GO(2, 1, 4);
-        case 3: case 4: if (wide) MV_GO(4, 2, 4); else MV_GO(4, 1, 4);
-        default: if (wide) MV_GO(8, 2, 2); else MV_GO(8, 1, 4);
+        case 1: if (wide) MV_GO(1, 2, 2, 4); else MV_GO(1, 1, 4, 4);
+        case 2: if (wide) MV_GO(2, 2, 2, 4); else MV_GO(2, 1, 4, 4);
+        case 3: case 4: if (wide) MV_GO(4, 2, 2, 8); else MV_GO(4, 1, 4, 8);
+        default: if (wide) MV_GO(8, 2, 2, 16); else MV_GO(8, 1, 4, 16);
     }
 #undef MV_GO
 }

@@ -209,7 +209,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < M) {
                     const int n_base = n0 + c0;
-                    if (mode == 1) {
+                    if (mode == 3) {
+                        // columns n_base .. +15 are gate, +16 .. +31 the up values of the same features
+                        if (n_base + 32 <= N) {
+                            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + (n_base >> 1);
+                            unsigned packed[8];
+#pragma unroll
+                            for (int j = 0; j < 16; j += 2) {
+                                float a0 = __uint_as_float(r[j]), a1 = __uint_as_float(r[j + 1]);
+                                float b0 = __uint_as_float(r[j + 16]), b1 = __uint_as_float(r[j + 17]);
+                                if (bias) {
+                                    a0 += bias[n_base + j]; a1 += bias[n_base + j + 1];
+                                    b0 += bias[n_base + j + 16]; b1 += bias[n_base + j + 17];
+                                }
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(a0 / (1.0f + expf(-a0)) * b0,
+                                                                               a1 / (1.0f + expf(-a1)) * b1);
+                                packed[j >> 1] = *reinterpret_cast<const unsigned*>(&v);
+                            }
+                            if ((((uintptr_t)dst) & 15) == 0) {
+                                reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                                reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) reinterpret_cast<unsigned*>(dst)[j] = packed[j];
+                            }
+                        }
+                    } else if (mode == 1) {
                         __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + n_base;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
@@ -336,13 +361,15 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
 
 }  // namespace
 
-// mode: 0 store float32, 1 store bfloat16, 2 add into float32.  ``err`` points to a
+// mode: 0 store float32, 1 store bfloat16, 2 add into float32, 3 SwiGLU (W rows in groups
+// of 16 gate + 16 up; out is bfloat16 [M, N/2] with row stride ldo).  ``err`` points to a
 // device int that a block sets (1 producer, 2 MMA, 3 epilogue) if a wait ran out.
 // Needs K a multiple of 8 and 16-byte aligned operands.
 MV_API int mv_gemm_tc(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
                       int K, int ldo, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    if (mode == 3 && (N % 32 || ldo % 2)) return (int)cudaErrorInvalidValue;
     if (N <= 64) return launch<64, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
     return launch<128, 3>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
 }

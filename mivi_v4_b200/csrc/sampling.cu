@@ -108,6 +108,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
               float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
               unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
               int* __restrict__ out) {
+    mv_pdl_begin();
     __shared__ Shared sh;
     const int b = blockIdx.x, tid = threadIdx.x;
     const float* src = logits + (size_t)b * ld;
@@ -331,7 +332,7 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
                      const int* recent, const int* n_recent, unsigned long long seed, const int* streams,
                      const int* steps, int* out, cudaStream_t stream) {
     if (B <= 0) return 0;
-    sample_kernel<<<B, THREADS, 0, stream>>>(logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
+    mv_launch(sample_kernel, B, THREADS, 0, stream, logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
                                              pres_pen, freq_pen, recent, n_recent, seed, streams, steps, out);
     return mv_launch_status();
 }

@@ -20,6 +20,7 @@ __global__ void shortconv_fwd_kernel(const float* __restrict__ p, const float* _
                                      const int* __restrict__ positions, const int* __restrict__ seq_of,
                                      const int* __restrict__ slots, const int* __restrict__ starts,
                                      TO* __restrict__ z, int N, int H, int k) {
+    mv_pdl_begin();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)N * H) return;
     const int n = (int)(i / H), d = (int)(i - (long long)n * H);
@@ -48,6 +49,7 @@ __global__ void shortconv_fwd_kernel(const float* __restrict__ p, const float* _
 __global__ void shortconv_state_kernel(const float* __restrict__ p, float* __restrict__ state,
                                        const int* __restrict__ cu, const int* __restrict__ slots,
                                        const int* __restrict__ lens, int B, int H, int k) {
+    mv_pdl_begin();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)B * H) return;
     const int b = (int)(i / H), d = (int)(i - (long long)b * H);
@@ -68,6 +70,50 @@ __global__ void shortconv_state_kernel(const float* __restrict__ p, float* __res
     }
 }
 
+// A step in which every sequence brings one token (decoding): one thread per
+// (sequence, channel) does both, reading its k-1 state values once, writing z
+// and the shifted state.  Nobody else reads or writes that thread's column.
+template <typename TO>
+__global__ void shortconv_decode_kernel(const float* __restrict__ p, const float* __restrict__ w,
+                                        const float* __restrict__ bias, float* __restrict__ state,
+                                        const int* __restrict__ slots, TO* __restrict__ z, int B, int H, int k) {
+    mv_pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)B * H) return;
+    const int b = (int)(i / H), d = (int)(i - (long long)b * H);
+    float* st = state + (size_t)slots[b] * (k - 1) * H;
+    const float* row = p + (size_t)b * 3 * H;
+    const float bx = row[d] * row[2 * H + d];
+    float y = bias ? bias[d] : 0.f;
+    float prev = 0.f;
+    for (int j = 0; j < k - 1; ++j) {
+        const float v = st[(size_t)j * H + d];
+        y = fmaf(w[d * k + j], v, y);
+        if (j > 0) st[(size_t)(j - 1) * H + d] = v;         // shift towards the older end
+        prev = v;
+    }
+    (void)prev;
+    if (k > 1) st[(size_t)(k - 2) * H + d] = bx;
+    y = fmaf(w[d * k + (k - 1)], bx, y);
+    z[i] = mv_from_f32<TO>(row[H + d] * y);
+}
+
+MV_API int mv_shortconv_decode(const float* p, const float* w, const float* bias, float* state,
+                               const int* slots, void* z, int z_dtype, int B, int H, int k,
+                               cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (k < 1 || k > MV_MAX_CONV_K) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)(((long long)B * H + threads - 1) / threads);
+    if (z_dtype == MV_DT_BF16)
+        mv_launch(shortconv_decode_kernel<__nv_bfloat16>, blocks, threads, 0, stream, p, w, bias, state, slots,
+                  (__nv_bfloat16*)z, B, H, k);
+    else
+        mv_launch(shortconv_decode_kernel<float>, blocks, threads, 0, stream, p, w, bias, state, slots, (float*)z,
+                  B, H, k);
+    return mv_launch_status();
+}
+
 MV_API int mv_shortconv(const float* p, const float* w, const float* bias, float* state,
                         const int* positions, const int* seq_of, const int* cu, const int* slots,
                         const int* starts, const int* lens, void* z, int z_dtype, int N, int B, int H,
@@ -77,14 +123,14 @@ MV_API int mv_shortconv(const float* p, const float* w, const float* bias, float
     const int threads = 256;
     const unsigned blocks = (unsigned)(((long long)N * H + threads - 1) / threads);
     if (z_dtype == MV_DT_BF16)
-        shortconv_fwd_kernel<<<blocks, threads, 0, stream>>>(p, w, bias, state, positions, seq_of, slots,
+        mv_launch(shortconv_fwd_kernel<__nv_bfloat16>, blocks, threads, 0, stream, p, w, bias, state, positions, seq_of, slots,
                                                             starts, (__nv_bfloat16*)z, N, H, k);
     else
-        shortconv_fwd_kernel<<<blocks, threads, 0, stream>>>(p, w, bias, state, positions, seq_of, slots,
+        mv_launch(shortconv_fwd_kernel<float>, blocks, threads, 0, stream, p, w, bias, state, positions, seq_of, slots,
                                                             starts, (float*)z, N, H, k);
     if (k > 1) {
         const unsigned sblocks = (unsigned)(((long long)B * H + threads - 1) / threads);
-        shortconv_state_kernel<<<sblocks, threads, 0, stream>>>(p, state, cu, slots, lens, B, H, k);
+        mv_launch(shortconv_state_kernel, sblocks, threads, 0, stream, p, state, cu, slots, lens, B, H, k);
     }
     return mv_launch_status();
 }

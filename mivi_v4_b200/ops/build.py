@@ -143,6 +143,13 @@ def compile_library(name: str, verbose: bool = True) -> str:
                      f"link of {name}")
                 os.replace(part, out)
                 shutil.rmtree(tmp, ignore_errors=True)
+                for old in os.listdir(bdir):              # builds of older sources
+                    if old.startswith(f"libmivi_{name}_") and old.endswith(".so") and \
+                            os.path.join(bdir, old) != out:
+                        try:
+                            os.remove(os.path.join(bdir, old))
+                        except OSError:
+                            pass
             finally:
                 stop.set()
             if verbose:

@@ -30,9 +30,10 @@ _SIGNATURES = {
     "core": {
         "mv_embed": [_P, _I, _P, _P, _I, _I, _P],
         "mv_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
-        "mv_swiglu": [_P, _P, _I, _I, _I, _P],
+        "mv_swiglu": [_P, _P, _I, _I, _I, _I, _P],
         "mv_gemm_simt": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_shortconv_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "mv_qk_prepare": [_P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _P],
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
@@ -134,12 +135,18 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     return out
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[n, f] = silu(gu[n, f]) * gu[n, F + f]."""
+SWIGLU_GROUP = 16
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.Tensor:
+    """out[n, f] = silu(gate) * up.  ``group`` 0: gate and up are the two halves
+    of a row of ``gu``; 16: they alternate in groups of 16 columns."""
     N, F2 = gu.shape
     F = F2 // 2
+    if group and F % group:
+        raise KernelError(f"swiglu: width {F} is not a multiple of the group size {group}")
     _check(_fn("core", "mv_swiglu")(
-        _need(gu, "swiglu in", torch.float32), _need(out, "swiglu out", None, (N, F)), _dt(out), N, F,
+        _need(gu, "swiglu in", torch.float32), _need(out, "swiglu out", None, (N, F)), _dt(out), N, F, int(group),
         _stream()), "mv_swiglu")
     return out
 
@@ -174,7 +181,7 @@ SMALL_M_MAX = 64
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-                 accumulate: bool = False) -> torch.Tensor:
+                 accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
     """out = x @ w.T for at most 64 rows of x, bfloat16 operands: the
     weight-streaming tensor-core kernel of the decode step."""
     M, K = x.shape
@@ -185,7 +192,13 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
         raise KernelError(f"gemm_small_m: operands must be bfloat16, got {x.dtype} and {w.dtype}")
     if not 1 <= M <= SMALL_M_MAX or K % 8:
         raise KernelError(f"gemm_small_m: needs 1..{SMALL_M_MAX} rows and K a multiple of 8, got M={M}, K={K}")
-    if accumulate:
+    ldo = N
+    if swiglu:
+        if N % 32:
+            raise KernelError(f"gemm_small_m: the SwiGLU epilogue needs rows in groups of 32, got {N}")
+        mode, ldo = 3, N // 2
+        _need(out, "gemm out", torch.bfloat16, (M, N // 2))
+    elif accumulate:
         mode = 2
         _need(out, "gemm out", torch.float32, (M, N))
     else:
@@ -194,7 +207,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
         _dt(out)
     _check(_fn("bf16", "mv_gemm_small_m")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, N, _stream()), "mv_gemm_small_m")
+        out.data_ptr(), mode, M, N, K, ldo, _stream()), "mv_gemm_small_m")
     return out
 
 
@@ -221,7 +234,7 @@ def check_device_errors() -> None:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False) -> torch.Tensor:
+            accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
     """out = x @ w.T, bfloat16 operands, on the tcgen05 tensor cores (TMA
     loads, accumulator in tensor memory): the matrix product of prefill."""
     M, K = x.shape
@@ -232,7 +245,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
         raise KernelError(f"gemm_tc: operands must be bfloat16, got {x.dtype} and {w.dtype}")
     if K % 8 or K < 8:
         raise KernelError(f"gemm_tc: K must be a multiple of 8 (16-byte rows for TMA), got {K}")
-    if accumulate:
+    ldo = N
+    if swiglu:
+        if N % 32:
+            raise KernelError(f"gemm_tc: the SwiGLU epilogue needs rows in groups of 32, got {N}")
+        mode, ldo = 3, N // 2
+        _need(out, "gemm out", torch.bfloat16, (M, N // 2))
+    elif accumulate:
         mode = 2
         _need(out, "gemm out", torch.float32, (M, N))
     else:
@@ -241,14 +260,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
         _dt(out)
     _check(_fn("bf16", "mv_gemm_tc")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, N, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc")
+        out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc")
     return out
 
 
 def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
-              positions, seq_of, cu, slots, starts, lens, out: torch.Tensor, n_seqs: int) -> torch.Tensor:
+              positions, seq_of, cu, slots, starts, lens, out: torch.Tensor, n_seqs: int,
+              decode: bool = False) -> torch.Tensor:
     """Gated short convolution between its projections; updates ``state``
-    [n_slots, k-1, H] in place for the ``n_seqs`` sequences of the step."""
+    [n_slots, k-1, H] in place for the ``n_seqs`` sequences of the step.
+    ``decode``: every sequence brings exactly one token (one fused kernel)."""
     N, H3 = p.shape
     H, k = w.shape
     if H3 != 3 * H:
@@ -258,6 +279,13 @@ def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], st
     _need(state, "shortconv state", torch.float32)
     if state.dim() != 3 or state.shape[1] != k - 1 or state.shape[2] != H:
         raise KernelError(f"shortconv: state shape {tuple(state.shape)}, expected [slots, {k - 1}, {H}]")
+    if N == n_seqs and decode:
+        _check(_fn("core", "mv_shortconv_decode")(
+            _need(p, "shortconv p", torch.float32), _need(w, "shortconv taps", torch.float32),
+            _need(bias, "shortconv bias", torch.float32, (H,), True), state.data_ptr(),
+            _need(slots, "slots", torch.int32), _need(out, "shortconv out", None, (N, H)), _dt(out), N, H, k,
+            _stream()), "mv_shortconv_decode")
+        return out
     _check(_fn("core", "mv_shortconv")(
         _need(p, "shortconv p", torch.float32), _need(w, "shortconv taps", torch.float32),
         _need(bias, "shortconv bias", torch.float32, (H,), True), state.data_ptr(),

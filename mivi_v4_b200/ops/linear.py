@@ -16,6 +16,22 @@ import torch
 from . import kernels as K
 
 
+def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the bfloat16 tensor-core kernels take these operands."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate) * up where [gate | up] = x @ w_grouped.T and the rows of
+    ``w_grouped`` alternate in groups of 16 (gate rows, then the up rows of the
+    same features): the activation runs in the product's epilogue, so gate and
+    up never go to memory.  Needs ``tensor_core_ok``."""
+    if x.shape[0] <= K.SMALL_M_MAX:
+        return K.gemm_small_m(x, w_grouped, out, swiglu=True)
+    return K.gemm_tc(x, w_grouped, out, swiglu=True)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
            accumulate: bool = False) -> torch.Tensor:
     """out = x @ w.T (+ bias); with ``accumulate`` the product is added to

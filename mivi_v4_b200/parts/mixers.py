@@ -52,7 +52,7 @@ class ShortConv(Part):
         linear(u, self.w_in, p, bias=self.b_in)
         z = step.ws.get("mix", (N, H), step.dtype)
         K.shortconv(p, self.taps, self.b_conv, view.state, step.positions, step.seq_of, step.cu,
-                    step.slots, step.starts, step.lens, z, step.n_seqs)
+                    step.slots, step.starts, step.lens, z, step.n_seqs, decode=step.is_decode)
         linear(z, self.w_out, resid, bias=self.b_out, accumulate=True)
 
 

@@ -268,7 +268,8 @@ def test_shortconv_any_cut(out_dtype, H, k, bias):
             out = torch.empty(rows.shape[0], H, dtype=out_dtype, device=DEV)
             K().shortconv(rows, wd, bd, state, ints([done[s] + i for s, n in zip(live, lens) for i in range(n)]),
                           ints([j for j, n in enumerate(lens) for _ in range(n)]), ints(cu),
-                          ints([slots[s] for s in live]), ints([done[s] for s in live]), ints(lens), out, len(live))
+                          ints([slots[s] for s in live]), ints([done[s] for s in live]), ints(lens), out, len(live),
+                          decode=all(n == 1 for n in lens))       # one token each: the fused kernel
             for j, (s, n) in enumerate(zip(live, lens)):
                 got[s].append(out[cu[j]:cu[j] + n])
                 done[s] += n
@@ -337,3 +338,34 @@ def test_attention_prefill(nh, nkv, hd, page, window):
             got = out[cu[b] + i].reshape(nh, hd).double().cpu()
             assert torch.allclose(got, want, rtol=tol, atol=tol), (b, i, (got - want).abs().max())
     assert not torch.isnan(out.float()).any()
+
+
+def grouped(w1, w3, G=16):
+    F, H = w1.shape
+    return torch.stack([w1.view(F // G, G, H), w3.view(F // G, G, H)], dim=1).reshape(2 * F, H).contiguous()
+
+
+def test_swiglu_grouped_columns():
+    N, F = 5, 48
+    gu = rnd(N, 2 * F, scale=3.0)
+    out = torch.empty(N, F, device=DEV)
+    K().swiglu(gu, out, 16)
+    v = gu.view(N, F // 16, 2, 16).double()
+    a, b = v[:, :, 0].reshape(N, F), v[:, :, 1].reshape(N, F)
+    assert torch.allclose(out.double(), a / (1 + torch.exp(-a)) * b, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 33, 64, 65, 200, 1000])
+@pytest.mark.parametrize("F,Kd", [(16, 8), (48, 72), (256, 96), (8192, 2048), (1040, 200)])
+def test_gemm_swiglu_epilogue(M, F, Kd):
+    """gate and up never reach memory: the product's epilogue applies silu(gate) * up."""
+    x = rnd(M, Kd, dtype=torch.bfloat16)
+    w1, w3 = rnd(F, Kd, dtype=torch.bfloat16, scale=0.2, seed=1), rnd(F, Kd, dtype=torch.bfloat16, scale=0.2, seed=2)
+    a, b = x.double() @ w1.double().T, x.double() @ w3.double().T
+    want = a / (1 + torch.exp(-a)) * b
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fn = K().gemm_small_m if M <= 64 else K().gemm_tc
+    fn(x, grouped(w1, w3), out, swiglu=True)
+    K().check_device_errors()
+    scale = max(1.0, want.abs().max().item())
+    assert (out.double() - want).abs().max().item() <= 1e-2 * scale
