@@ -116,6 +116,11 @@ static inline void mv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 }
 #endif
 
+// A cluster barrier that orders nothing in memory: for "nobody leaves before everybody is here".
+__device__ __forceinline__ void mv_cluster_sync_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+
 // 16 bytes already in registers -> floats (4 of float32, 8 of bfloat16)
 __device__ __forceinline__ void mv_unpack16(const uint4& r, float* out, const float*) {
     out[0] = __uint_as_float(r.x); out[1] = __uint_as_float(r.y);

@@ -157,52 +157,43 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         csum[r * LDR + c] = v;
     }
 
-    // the slices of this tile: the cluster's first block adds them in rank order
+    // The slices of this tile are added in rank order.  The work of adding is dealt out to all blocks
+    // of the cluster: an item is the tile's rows for one token (one row per lane), item m belongs to
+    // block m mod slices.  A lane first requests its value from every slice, then adds.
     const float* share[8];
     if (slices > 1) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
-        if (slice == 0)
-            for (int s = 0; s < slices; ++s) share[s] = cluster.map_shared_rank(csum, s);
+        for (int s = 0; s < slices; ++s) share[s] = cluster.map_shared_rank(csum, s);
     } else {
         __syncthreads();
         share[0] = csum;
     }
-    if (slice == 0) {
-        auto total = [&](int r, int m) {
-            float v = 0.f;
-            for (int s = 0; s < slices; ++s) v += share[s][r * LDR + m];
-            return v;
-        };
+    for (int m = slice + slices * warp; m < M; m += slices * WARPS) {
+        const int r = lane;                         // ROWS is 16 or 32
+        const int n = n0 + r;
+        float part[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) part[s] = (s < slices && r < ROWS) ? share[s][r * LDR + m] : 0.f;
+        float v = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) v += part[s];
+        if (bias && r < ROWS && n < N) v += bias[n];
         if (mode == 3) {
-            // rows come in groups of 32: 16 gate rows, then the 16 up rows of the same features
-            // (RT == 2, so a block owns whole groups); out[m, f] = silu(gate) * up in bfloat16
-            constexpr int HALF = ROWS / 2;
-            for (int idx = threadIdx.x; idx < HALF * M; idx += WARPS * 32) {
-                const int r = idx % HALF, m = idx / HALF;
-                const int rg = (r >> 4) * 32 + (r & 15);           // gate row within the block
-                if (n0 + rg + 16 >= N) continue;
-                float a = total(rg, m), b = total(rg + 16, m);
-                if (bias) { a += bias[n0 + rg]; b += bias[n0 + rg + 16]; }
-                const int f = ((n0 + rg) >> 5) * 16 + (rg & 15);
-                ((__nv_bfloat16*)out)[(size_t)m * ldo + f] = __float2bfloat16_rn(a / (1.0f + expf(-a)) * b);
-            }
-        } else {
-            for (int idx = threadIdx.x; idx < ROWS * M; idx += WARPS * 32) {
-                const int r = idx % ROWS, m = idx / ROWS;
-                const int n = n0 + r;
-                if (n >= N) continue;
-                float v = total(r, m);
-                if (bias) v += bias[n];
-                const size_t o = (size_t)m * ldo + n;
-                if (mode == 0) ((float*)out)[o] = v;
-                else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-                else ((float*)out)[o] += v;
-            }
+            // ROWS == 32: lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same features
+            const float up = __shfl_down_sync(0xffffffffu, v, 16);
+            if (lane < 16 && n + 16 < N)
+                ((__nv_bfloat16*)out)[(size_t)m * ldo + (n >> 5) * 16 + lane] =
+                    __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+        } else if (r < ROWS && n < N) {
+            const size_t o = (size_t)m * ldo + n;
+            if (mode == 0) ((float*)out)[o] = v;
+            else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+            else ((float*)out)[o] += v;
         }
     }
-    // nobody leaves while the first block may still read its shared memory
-    if (slices > 1) cg::this_cluster().sync();
+    // nobody leaves while another block may still read its shared memory
+    if (slices > 1) mv_cluster_sync_relaxed();
 }
 
 template <int NT, int RT, int UNROLL, int WARPS>

@@ -28,95 +28,11 @@
 //
 // Reference counterpart: quantized_matmul_rows, out[b, n] = sum_d in[b, d] W[n, d]
 // (crates/mivi-quant/src/lib.rs:143-245).
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
-constexpr int BM = 128, BK = 64;
 constexpr int THREADS = 192;
-constexpr unsigned long long WAIT_NS = 2000000000ull;
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ unsigned long long globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false (and the error flag set) if the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* err, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer();
-    for (;;) {
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer() - t0 > WAIT_NS) {
-            atomicExch(err, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle; 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3ffffu) >> 4);          // start address
-    d |= (unsigned long long)1 << 16;                            // leading byte offset (unused with swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (unsigned long long)1 << 46;                            // descriptor version of sm_100
-    d |= (unsigned long long)2 << 61;                            // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor of kind::f16: bf16 x bf16 -> f32, both operands K-major.
-__device__ __forceinline__ unsigned instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
-__device__ __forceinline__ void mma_f16(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
-                                        unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void mma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -285,62 +201,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)BN)
                      : "memory");
     }
-}
-
-// ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encoder() {
-    static EncodeTiled fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^
-               ((size_t)k.box_rows << 20);
-    }
-};
-
-// A row-major [rows, cols] bfloat16 matrix read in boxes of box_rows x 64 with the 128-byte swizzle.
-bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const MapKey key{ptr, rows, cols, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return true; }
-    EncodeTiled enc = encoder();
-    if (!enc) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, m);
-    *out = m;
-    return true;
 }
 
 template <int BN, int STAGES>

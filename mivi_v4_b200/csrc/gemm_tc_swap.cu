@@ -1,0 +1,226 @@
+// Y[M, N] = X[M, K] . W[N, K]^T for a decode step (M <= 64 tokens) on the
+// fifth-generation tensor cores, with the roles of the operands swapped: a tile
+// of 128 rows of W is the MMA's M side, the tokens are its N side (16, 32 or 64
+// columns of tensor memory).  The cost of the step is reading W once, so the
+// kernel is a pipeline that keeps TMA loads of W in flight: one lane issues the
+// loads of 128 x 64 tiles into a ring of stages, one lane issues the MMAs and
+// hands the stages back, and nothing passes through registers until the end.
+//
+// A block owns one row tile and one slice of K; the slices of a tile form a
+// thread-block cluster.  Each block moves its accumulator from tensor memory to
+// shared memory; the cluster's first block adds the slices in rank order through
+// distributed shared memory and runs the epilogue (store float32 / bfloat16, add
+// into float32, or SwiGLU over rows grouped 16 gate + 16 up; optional bias).
+// Every sum has a fixed order.  Waits on mbarriers are bounded (see
+// tc_common.cuh); the cluster barrier is the hardware's.
+//
+// Reference counterpart: quantized_matvec (crates/mivi-quant/src/lib.rs:75-135).
+#include <cooperative_groups.h>
+
+#include "tc_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int THREADS = 192;
+
+template <int BN, int STAGES>
+struct SwapLayout {
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int LD = BN + 1;
+    static constexpr int CSUM_BYTES = BM * LD * 4;
+    static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 8;
+    static constexpr int TOTAL = (TILE_BYTES > CSUM_BYTES ? TILE_BYTES : CSUM_BYTES) + BAR_BYTES + 1024;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
+                    int* __restrict__ err) {
+    using L = SwapLayout<BN, STAGES>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int DATA_BYTES = L::TILE_BYTES > L::CSUM_BYTES ? L::TILE_BYTES : L::CSUM_BYTES;
+    unsigned long long* bars = (unsigned long long*)(smem + DATA_BYTES);
+    unsigned* tmem_holder = (unsigned*)(bars + 2 * STAGES + 1);
+    float* csum = reinterpret_cast<float*>(smem);       // reuses the ring once the MMAs are done
+    const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, acc_bar = full0 + 16 * STAGES;
+    const unsigned tiles0 = smem_u32(smem);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slices = gridDim.x, slice = blockIdx.x;
+    const int n0 = blockIdx.y * BM;
+    const int kblocks = (K + BK - 1) / BK;
+    const int per = (kblocks + slices - 1) / slices;
+    const int kb0 = slice * per;
+    const int nkb = max(0, min(kblocks, kb0 + per) - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_holder)), "r"((unsigned)L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = *tmem_holder;
+
+    bool acc_ok = nkb > 0;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const unsigned phase = (unsigned)(i / STAGES) & 1u;
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, err, 1)) break;
+                mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
+                const unsigned a_dst = tiles0 + s * L::STAGE_BYTES;
+                tma_load_2d(a_dst, &map_w, (kb0 + i) * BK, n0, full0 + 8 * s);
+                tma_load_2d(a_dst + L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && nkb > 0) {
+            const unsigned idesc = instr_desc(BM, BN);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const unsigned phase = (unsigned)(i / STAGES) & 1u;
+                if (!mbar_wait(full0 + 8 * s, phase, err, 2)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned a_addr = tiles0 + s * L::STAGE_BYTES;
+                const unsigned b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    mma_f16(tmem_base, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
+                            (i > 0 || k > 0) ? 1u : 0u);
+                mma_commit(empty0 + 8 * s);
+            }
+            mma_commit(acc_bar);
+        }
+    } else {
+        // this block's accumulator: tensor memory -> shared memory, rows = rows of W, columns = tokens
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        if (acc_ok) acc_ok = mbar_wait(acc_bar, 0, err, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            unsigned v[32];
+            if (acc_ok) {
+                tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (c0 + j < BN) csum[r * L::LD + c0 + j] = __uint_as_float(v[j]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+
+    // The slices of this tile are added in rank order.  The work of adding is dealt out to all blocks
+    // of the cluster: an item is 32 consecutive rows for one token (a warp, one row per lane), item i
+    // belongs to block i mod slices.  A lane first requests its value from every slice, then adds.
+    const float* share[8];
+    if (slices > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        for (int s = 0; s < slices; ++s) share[s] = cluster.map_shared_rank(csum, s);
+    } else {
+        __syncthreads();
+        share[0] = csum;
+    }
+    {
+        const int items = (BM / 32) * M;
+        for (int it = slice + slices * warp; it < items; it += slices * (THREADS / 32)) {
+            const int u = it % (BM / 32), m = it / (BM / 32);
+            const int r = u * 32 + lane, n = n0 + r;
+            float part[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) part[s] = s < slices ? share[s][r * L::LD + m] : 0.f;
+            float v = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) v += part[s];
+            if (bias && n < N) v += bias[n];
+            if (mode == 3) {
+                // lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same features
+                const float up = __shfl_down_sync(0xffffffffu, v, 16);
+                if (lane < 16 && n + 16 < N)
+                    ((__nv_bfloat16*)out)[(size_t)m * ldo + (n >> 5) * 16 + lane] =
+                        __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+            } else if (n < N) {
+                const size_t o = (size_t)m * ldo + n;
+                if (mode == 0) ((float*)out)[o] = v;
+                else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+                else ((float*)out)[o] += v;
+            }
+        }
+    }
+    // nobody leaves while another block may still read its shared memory
+    if (slices > 1) mv_cluster_sync_relaxed();
+    else __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((unsigned)L::TMEM_COLS) : "memory");
+    }
+}
+
+template <int BN, int STAGES>
+int launch(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
+           int* err, cudaStream_t stream) {
+    using L = SwapLayout<BN, STAGES>;
+    CUtensorMap mw, mx;
+    if (!tensor_map(W, N, K, BM, &mw) || !tensor_map(X, M, K, BN, &mx)) return (int)cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        attr_set = true;
+    }
+    const int tiles = (N + BM - 1) / BM;
+    const int kblocks = (K + BK - 1) / BK;
+    // slices of K: enough blocks to fill the GPU about twice over, each with at least four K blocks
+    int slices = 1;
+    while (slices < 8 && tiles * slices < 2 * 148 && kblocks / (slices * 2) >= 4) slices *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(slices, tiles);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = slices;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = slices > 1 ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, gemm_tc_swap_kernel<BN, STAGES>, mw, mx, bias, out, mode, M, N, K, ldo, err);
+    return mv_launch_status();
+}
+
+}  // namespace
+
+// Same contract as mv_gemm_small_m (modes 0-3, 1 <= M <= 64, K a multiple of 8,
+// 16-byte aligned operands), plus the error flag of the bounded waits.
+MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
+                           int K, int ldo, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
+    if (M <= 16) return launch<16, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    if (M <= 32) return launch<32, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    return launch<64, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+}

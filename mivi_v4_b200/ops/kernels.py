@@ -43,6 +43,7 @@ _SIGNATURES = {
     "bf16": {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     },
 }
@@ -261,6 +262,38 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
     _check(_fn("bf16", "mv_gemm_tc")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc")
+    return out
+
+
+def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+                 accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+    """out = x @ w.T for at most 64 rows of x on the tcgen05 tensor cores with the
+    operands' roles swapped (rows of w on the MMA's M side): a TMA pipeline that
+    streams w once.  Same contract as ``gemm_small_m``."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is [{N}, {K2}]")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tc_swap: operands must be bfloat16, got {x.dtype} and {w.dtype}")
+    if not 1 <= M <= SMALL_M_MAX or K % 8 or K < 8:
+        raise KernelError(f"gemm_tc_swap: needs 1..{SMALL_M_MAX} rows and K a multiple of 8, got M={M}, K={K}")
+    ldo = N
+    if swiglu:
+        if N % 32:
+            raise KernelError(f"gemm_tc_swap: the SwiGLU epilogue needs rows in groups of 32, got {N}")
+        mode, ldo = 3, N // 2
+        _need(out, "gemm out", torch.bfloat16, (M, N // 2))
+    elif accumulate:
+        mode = 2
+        _need(out, "gemm out", torch.float32, (M, N))
+    else:
+        mode = 0 if out.dtype == torch.float32 else 1
+        _need(out, "gemm out", None, (M, N))
+        _dt(out)
+    _check(_fn("bf16", "mv_gemm_tc_swap")(
+        _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
+        out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_swap")
     return out
 
 

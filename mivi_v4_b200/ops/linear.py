@@ -16,6 +16,19 @@ import torch
 from . import kernels as K
 
 
+import os
+
+_DECODE_GEMM = os.environ.get("MIVI_DECODE_GEMM", "mma")
+
+
+def _small_m(m: int):
+    """The kernel for at most 64 rows.  Two exist: the mma.sync kernel that streams
+    W through registers (``mma``, the default: faster at every batch size measured,
+    1 to 64, because a decode product is too short to repay a TMA pipeline's set-up)
+    and the tcgen05 kernel with swapped operands (``tc``, MIVI_DECODE_GEMM=tc)."""
+    return K.gemm_tc_swap if _DECODE_GEMM == "tc" else K.gemm_small_m
+
+
 def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the bfloat16 tensor-core kernels take these operands."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
@@ -28,7 +41,7 @@ def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor) -
     same features): the activation runs in the product's epilogue, so gate and
     up never go to memory.  Needs ``tensor_core_ok``."""
     if x.shape[0] <= K.SMALL_M_MAX:
-        return K.gemm_small_m(x, w_grouped, out, swiglu=True)
+        return _small_m(x.shape[0])(x, w_grouped, out, swiglu=True)
     return K.gemm_tc(x, w_grouped, out, swiglu=True)
 
 
@@ -42,6 +55,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         if x.shape[0] <= K.SMALL_M_MAX:
-            return K.gemm_small_m(x, w, out, bias=bias, accumulate=accumulate)
+            return _small_m(x.shape[0])(x, w, out, bias=bias, accumulate=accumulate)
         return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate)
     return K.gemm_simt(x, w, out, bias=bias, accumulate=accumulate)

@@ -82,23 +82,29 @@ def test_gemm_simt(dtype, M, N, Kd):
     assert torch.allclose(ob.double(), want, rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("kernel", ["gemm_small_m", "gemm_tc_swap"])
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 31, 33, 64])
 @pytest.mark.parametrize("N,Kd", [(16, 8), (1, 64), (50, 40), (301, 240), (2048, 2048), (300, 8200), (9600, 96)])
-def test_gemm_small_m(M, N, Kd):
+def test_gemm_small_m(kernel, M, N, Kd):
+    fn = getattr(K(), kernel)
     x, w = rnd(M, Kd, dtype=torch.bfloat16), rnd(N, Kd, dtype=torch.bfloat16, seed=1)
     bias = rnd(N, seed=2)
     want = x.double() @ w.double().T
     tol = dict(rtol=1e-4, atol=1e-3 * math.sqrt(Kd / 64))
     out = torch.full((M, N), float("nan"), device=DEV)
-    K().gemm_small_m(x, w, out)
+    fn(x, w, out)
     assert torch.allclose(out.double(), want, **tol)
     base = rnd(M, N, seed=3)
     acc = base.clone()
-    K().gemm_small_m(x, w, acc, bias=bias, accumulate=True)
+    fn(x, w, acc, bias=bias, accumulate=True)
     assert torch.allclose(acc.double(), want + base.double() + bias.double(), **tol)
     again = base.clone()
-    K().gemm_small_m(x, w, again, bias=bias, accumulate=True)
+    fn(x, w, again, bias=bias, accumulate=True)
     assert torch.equal(acc, again)               # the same bits in every run
+    ob = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    fn(x, w, ob)
+    assert torch.allclose(ob.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(Kd / 64))
+    K().check_device_errors()
 
 
 def test_gemm_small_m_refuses_what_it_cannot_do():
@@ -364,8 +370,9 @@ def test_gemm_swiglu_epilogue(M, F, Kd):
     a, b = x.double() @ w1.double().T, x.double() @ w3.double().T
     want = a / (1 + torch.exp(-a)) * b
     out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
-    fn = K().gemm_small_m if M <= 64 else K().gemm_tc
-    fn(x, grouped(w1, w3), out, swiglu=True)
-    K().check_device_errors()
     scale = max(1.0, want.abs().max().item())
-    assert (out.double() - want).abs().max().item() <= 1e-2 * scale
+    for fn in ([K().gemm_small_m, K().gemm_tc_swap] if M <= 64 else [K().gemm_tc]):
+        out.fill_(float("nan"))
+        fn(x, grouped(w1, w3), out, swiglu=True)
+        K().check_device_errors()
+        assert (out.double() - want).abs().max().item() <= 1e-2 * scale, fn.__name__
