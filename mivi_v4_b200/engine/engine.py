@@ -54,6 +54,7 @@ class Engine:
         self.cuda_graphs = bool(cuda_graphs)
         self._graphs: Dict[tuple, tuple] = {}
         self.graph_replays = 0
+        self._prepared: Optional[dict] = None             # a decode step laid out ahead of its tokens
 
     # ---- sequences ------------------------------------------------------------
     def open(self) -> int:
@@ -61,6 +62,7 @@ class Engine:
         if self.cache.slots.free_count == 0 and self.cache.n_slots < self.total_pages:
             self.cache.grow_slots(min(self.total_pages, max(2 * self.cache.n_slots, 1)))
             self._graphs.clear()                          # the state storage moved
+            self._prepared = None
         return self.cache.assign()
 
     def close(self, slot: int) -> None:
@@ -82,6 +84,16 @@ class Engine:
         """
         items = [(int(s), [int(t) for t in toks]) for s, toks in items]
         V = self.model.vocab_size
+        prepared, self._prepared = self._prepared, None
+        if (prepared is not None and want == "last" and len(items) == len(prepared["slots"])
+                and all(s == ps and len(t) == 1 for (s, t), ps in zip(items, prepared["slots"]))
+                and self._graphs.get(prepared["key"]) is not None):
+            tokens = [t[0] for _, t in items]
+            for (slot, _), t in zip(items, tokens):
+                if not 0 <= t < V:
+                    raise StepError(f"slot {slot}: token id {t} is outside the vocabulary of {V}")
+            logits = self._execute(prepared, tokens)
+            return logits.clone() if copy else logits
         seen = set()
         for slot, toks in items:
             if slot in seen:
@@ -165,6 +177,11 @@ class Engine:
         return out
 
     def _run(self, items, places) -> Optional[torch.Tensor]:
+        return self._execute(self._plan(items, places))
+
+    def _plan(self, items, places) -> dict:
+        """Everything of a step that the host can work out before the token ids matter: room in the
+        cache, positions, page tables, and for a decode-shaped step the arrays laid out for its graph."""
         slots = [s for s, _ in items]
         starts = [self.cache.length(s) for s in slots]
         for s, toks in items:
@@ -180,22 +197,47 @@ class Engine:
         widths = {g: -(-max(len(self.cache._get(s).pages[g]) for s in slots) // 8) * 8 if decode else None
                   for g in self.cache.kv_groups}
         page_rows = {g: self.cache.page_rows(g, slots, widths[g]) for g in self.cache.kv_groups}
-        lists = [t for _, t in items]
-        if not decode:
-            ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
-                              page_rows=page_rows, dtype=self.dtype, ws=self.ws)
+        plan = dict(slots=slots, starts=starts, lists=[list(t) for _, t in items], out_rows=out_rows,
+                    page_rows=page_rows, decode=decode, key=None, ctx=None)
+        if decode:
+            plan["key"] = (len(items), tuple(sorted(widths.items())))
+            entry = self._graphs.get(plan["key"])
+            if entry is not None:
+                plan["ctx"] = StepContext(slots=slots, starts=starts, token_lists=plan["lists"], out_rows=out_rows,
+                                          page_rows=page_rows, dtype=self.dtype, ws=entry[1], upload=False)
+        return plan
+
+    def _execute(self, plan: dict, tokens: Optional[List[int]] = None,
+                 device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Run a planned step.  ``tokens`` replaces the token ids of a decode-shaped plan;
+        ``device_tokens`` (int32 [B], on the device) does the same without the host ever seeing them:
+        they are copied into the step's token array on the stream, after the other arrays went up."""
+        slots, starts, lists = plan["slots"], plan["starts"], plan["lists"]
+        if tokens is not None:
+            lists = [[t] for t in tokens]
+
+        def context(ws, reuse=None):
+            ctx = reuse
+            if ctx is None or ctx.ws is not ws:
+                ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=plan["out_rows"],
+                                  page_rows=plan["page_rows"], dtype=self.dtype, ws=ws, upload=False)
+            ctx.upload([t for toks in lists for t in toks] if ctx is reuse else None)
+            if device_tokens is not None:
+                ctx.tokens.copy_(device_tokens, non_blocking=True)
+            return ctx
+
+        if not plan["decode"]:
+            ctx = context(self.ws)
             logits = self.model.forward(ctx, self.cache)
         else:
-            key = (len(items), tuple(sorted(widths.items())))
-            entry = self._graphs.get(key)
+            from ..ops import kernels as K
+            entry = self._graphs.get(plan["key"])
             if entry is None:
                 # first time: run the step for real on a workspace of its own (which sizes every
                 # buffer), then record the same launches for the steps to come
                 gws = Workspace(self.device)
-                ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
-                                  page_rows=page_rows, dtype=self.dtype, ws=gws)
+                ctx = context(gws)
                 logits = self.model.forward(ctx, self.cache)
-                from ..ops import kernels as K
                 n0 = K.launch_count()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
@@ -203,20 +245,61 @@ class Engine:
                 n_kernels = K.launch_count() - n0
                 K.add_launches(-n_kernels)                # recorded, not run
                 assert captured.data_ptr() == logits.data_ptr()
-                self._graphs[key] = (graph, gws, logits, n_kernels)
+                self._graphs[plan["key"]] = (graph, gws, logits, n_kernels)
             else:
                 graph, gws, logits, n_kernels = entry
-                ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
-                                  page_rows=page_rows, dtype=self.dtype, ws=gws)
+                ctx = context(gws, plan["ctx"])
                 graph.replay()
-                from ..ops import kernels as K
                 K.add_launches(n_kernels)
                 self.graph_replays += 1
-        for s, toks in items:
+        for s, toks in zip(slots, lists):
             self.cache.advance(s, len(toks))
         self.steps_run += 1
         self.h2d_bytes += ctx.h2d_bytes
         return logits
+
+    def decode_from_device(self, slots: Sequence[int], device_tokens: torch.Tensor) -> Optional[torch.Tensor]:
+        """One more token for each of ``slots``, the token ids being ``device_tokens`` (int32 [len(slots)],
+        on the device, e.g. what the sampling kernel just wrote): the step is enqueued without the host
+        waiting for them.  Returns the logits of all, or None if the step cannot run now (no room in the
+        cache, the context is full): the caller then waits for the tokens and calls ``step``."""
+        self._prepared = None
+        slots = [int(s) for s in slots]
+        if not slots or len(set(slots)) != len(slots) or device_tokens.numel() != len(slots) \
+                or device_tokens.dtype != torch.int32 or not device_tokens.is_cuda:
+            return None
+        try:
+            if self.max_positions is not None and any(self.cache.length(s) + 1 > self.max_positions for s in slots):
+                return None
+            for g in self.cache.kv_groups:
+                need = sum(max(0, -(-(self.cache.length(s) + 1) // self.page_size)
+                               - len(self.cache._get(s).pages[g])) for s in slots)
+                if need > self.cache.pages[g].free_count:
+                    return None
+            plan = self._plan([(s, [0]) for s in slots], [[0]] * len(slots))
+        except CacheError:
+            return None
+        return self._execute(plan, device_tokens=device_tokens)
+
+    def prepare_decode(self, slots: Sequence[int]) -> None:
+        """Lay out the next step - one more token for each of ``slots``, logits of all - while the GPU
+        is still busy with the current one.  ``step`` uses the layout if it is then called with
+        exactly these slots and one token each; otherwise the layout is dropped."""
+        self._prepared = None
+        if not self.cuda_graphs:
+            return
+        try:
+            slots = [int(s) for s in slots]
+            if self.max_positions is not None and any(self.cache.length(s) + 1 > self.max_positions for s in slots):
+                return
+            for g in self.cache.kv_groups:
+                need = sum(max(0, -(-(self.cache.length(s) + 1) // self.page_size)
+                               - len(self.cache._get(s).pages[g])) for s in slots)
+                if need > self.cache.pages[g].free_count:
+                    return
+            self._prepared = self._plan([(s, [0]) for s in slots], [[0]] * len(slots))
+        except CacheError:
+            self._prepared = None
 
     # ---- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 256,
@@ -238,14 +321,56 @@ class _EngineBackend:
         self.engine, self.sampler = engine, sampler
         self.max_batch, self.page_size = engine.max_batch, engine.page_size
         self.total_pages, self.max_positions = engine.total_pages, engine.max_positions
+        self._early = None            # the step after the current one, already enqueued
+        self._last = {}               # handle -> the token sampled for it in the last call
 
     def open(self) -> int:
+        self._early, self._last = None, {}        # a new sequence may get the slot of an old one
         return self.engine.open()
 
     def close(self, handle: int) -> None:
+        self._last.pop(handle, None)
         self.engine.close(handle)
 
     def forward_and_sample(self, requests: Sequence[Request], token_lists) -> List[int]:
-        logits = self.engine.step([(r.handle, t) for r, t in zip(requests, token_lists)], "last", copy=False)
-        return self.sampler.sample(logits, [r.index for r in requests], [len(r.output) for r in requests],
-                                   [r.output for r in requests])
+        """Forward the given tokens and sample the next one for every request.
+
+        Without penalties (which need the newest token on the host), the step AFTER this one is
+        enqueued before the host waits for this one's tokens: the sampling kernel's output is fed to
+        the next step on the device, for every request that can go on (it has tokens left to
+        generate).  If a request then turns out to have stopped, its row of the early step is simply
+        not used; the other rows do not depend on it.  The next call finds its work already running."""
+        sampler, eng = self.sampler, self.engine
+        handles = [r.handle for r in requests]
+        early = self._early
+        self._early = None
+        if (early is not None and set(handles) <= set(early["handles"])
+                and all(len(t) == 1 and self._last.get(h) == t[0] for h, t in zip(handles, token_lists))):
+            rows = [early["handles"].index(h) for h in handles]
+            out_dev, host, event = early["out"], early["host"], early["event"]
+        else:
+            logits = eng.step([(r.handle, t) for r, t in zip(requests, token_lists)], "last", copy=False)
+            out_dev = sampler.launch(logits, [r.index for r in requests], [len(r.output) for r in requests],
+                                     [r.output for r in requests])
+            host, event = sampler.read_async(out_dev)
+            rows = list(range(len(requests)))
+        # the step after this one, for the requests that will still have tokens to generate
+        if not sampler.params.uses_penalties and eng.cuda_graphs:
+            goers = [(i, r) for i, r in zip(rows, requests) if len(r.output) + 2 <= r.max_new_tokens]
+            if goers and len(goers) == len([r for r in requests if len(r.output) + 1 < r.max_new_tokens]):
+                src = out_dev if [i for i, _ in goers] == list(range(out_dev.numel())) else \
+                    out_dev[torch.tensor([i for i, _ in goers], device=out_dev.device)]
+                nxt = eng.decode_from_device([r.handle for _, r in goers], src)
+                if nxt is not None:
+                    out2 = sampler.launch(nxt, [r.index for _, r in goers], [len(r.output) + 1 for _, r in goers],
+                                          [[] for _ in goers], slot=1 - early["slot"] if early else 1)
+                    host2, event2 = sampler.read_async(out2, slot=1 - early["slot"] if early else 1)
+                    self._early = dict(handles=[r.handle for _, r in goers], out=out2, host=host2, event=event2,
+                                       slot=1 - early["slot"] if early else 1)
+        else:
+            eng.prepare_decode(handles)
+        event.synchronize()
+        tokens = host.tolist()
+        result = [tokens[i] for i in rows]
+        self._last = dict(zip(handles, result))
+        return result

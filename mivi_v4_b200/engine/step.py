@@ -90,7 +90,7 @@ class StepContext:
 
     def __init__(self, *, slots: List[int], starts: List[int], token_lists: List[List[int]],
                  out_rows: List[int], page_rows: Dict[int, List[List[int]]], dtype: torch.dtype,
-                 ws: Workspace):
+                 ws: Workspace, upload: bool = True):
         device = ws.device
         self.ws, self.dtype, self.device = ws, dtype, device
         self.host_slots, self.host_starts = list(slots), list(starts)
@@ -129,7 +129,10 @@ class StepContext:
             widths[g] = len(rows[0]) if rows else 1
             put(f"pages{g}", [p for r in rows for p in r])
 
-        arena = ws.stage("step_meta", flat)
+        # the arrays live in one device buffer whose place depends only on the workspace; they are
+        # filled by upload(), which may come later (a step can be laid out before its tokens are known)
+        arena = ws.get("step_meta", (len(flat),), torch.int32)
+        self._flat = flat
         self.h2d_bytes = len(flat) * 4
 
         def view(name: str) -> torch.Tensor:
@@ -139,6 +142,16 @@ class StepContext:
         self.tokens, self.positions, self.seq_of = view("tokens"), view("positions"), view("seq_of")
         self.cu, self.slots, self.starts, self.lens = view("cu"), view("slots"), view("starts"), view("lens")
         self.out_rows: Optional[torch.Tensor] = view("out_rows") if self.n_out else None
+        if upload:
+            self.upload()
         self.page_tables: Dict[int, torch.Tensor] = {
             g: view(f"pages{g}").view(max(self.n_seqs, 1) if rows else 1, widths[g]) if rows else view(f"pages{g}")
             for g, rows in page_rows.items()}
+
+    def upload(self, tokens: Optional[List[int]] = None) -> None:
+        """One host-to-device copy of the step's arrays; ``tokens`` replaces the token ids first."""
+        if tokens is not None:
+            if len(tokens) != self.n_tokens:
+                raise ValueError(f"{len(tokens)} token ids for a step of {self.n_tokens} tokens")
+            self._flat[:self.n_tokens] = tokens
+        self.ws.stage("step_meta", self._flat)

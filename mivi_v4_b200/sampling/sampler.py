@@ -23,18 +23,25 @@ class Sampler:
         if seed is None:
             seed = time.time_ns()
         self.seed = int(seed) & ((1 << 64) - 1)
-        self._work = None
-        self._out = None
+        self._bufs = {}
+        self._pinned = {}
+        self._events = {}
         from ..engine.step import Workspace
         self._ws = Workspace(self.device)
 
-    def sample(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
-               recent: Sequence[Sequence[int]]) -> List[int]:
+    def launch(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
+               recent: Sequence[Sequence[int]], slot: int = 0) -> torch.Tensor:
+        """Enqueue the sampling kernel; returns the device tensor (int32 [B]) that will hold the
+        tokens.  ``slot`` (0 or 1) picks one of two sets of buffers, so that two launches can be in
+        flight."""
         B, V = logits.shape
         p = self.params
-        if self._work is None or self._work.shape[0] < B:
-            self._work = torch.empty((max(B, 1), V), dtype=torch.float32, device=self.device)
-            self._out = torch.empty((max(B, 1),), dtype=torch.int32, device=self.device)
+        bufs = self._bufs.get(slot)
+        if bufs is None or bufs[0].shape[0] < B:
+            bufs = (torch.empty((max(B, 1), V), dtype=torch.float32, device=self.device),
+                    torch.empty((max(B, 1),), dtype=torch.int32, device=self.device))
+            self._bufs[slot] = bufs
+        work, out_all = bufs
         meta: List[int] = [int(s) & 0x7fffffff for s in streams] + [int(s) for s in steps]
         use_pen = p.uses_penalties and any(len(r) for r in recent)
         if use_pen:
@@ -42,13 +49,38 @@ class Sampler:
             for r in recent:
                 r = list(r)[-RECENT_TOKENS_WINDOW:]
                 meta += r + [0] * (RECENT_TOKENS_WINDOW - len(r))
-        m = self._ws.stage("sample_meta", meta)
+        m = self._ws.stage(f"sample_meta{slot}", meta)
         streams_d, steps_d = m[:B], m[B:2 * B]
         n_recent_d = m[2 * B:3 * B] if use_pen else None
         recent_d = m[3 * B:].view(B, RECENT_TOKENS_WINDOW) if use_pen else None
-        out = self._out[:B]
-        K.sample(logits, self._work, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
+        out = out_all[:B]
+        K.sample(logits, work, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                  min_p=p.min_p, repetition_penalty=p.repetition_penalty, presence_penalty=p.presence_penalty,
                  frequency_penalty=p.frequency_penalty, recent=recent_d, n_recent=n_recent_d, seed=self.seed,
                  streams=streams_d, steps=steps_d)
-        return out.tolist()
+        return out
+
+    def read_async(self, out: torch.Tensor, slot: int = 0):
+        """Start the copy of sampled tokens to pinned host memory; returns (host tensor, event).  The
+        tokens are there once the event has completed, whatever was enqueued after it."""
+        B = out.numel()
+        pinned = self._pinned.get(slot)
+        if pinned is None or pinned.numel() < B:
+            pinned = torch.empty(max(B, 64), dtype=torch.int32).pin_memory()
+            self._pinned[slot] = pinned
+        host = pinned[:B]
+        host.copy_(out, non_blocking=True)
+        event = self._events.setdefault(slot, torch.cuda.Event())
+        event.record()
+        return host, event
+
+    def sample(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
+               recent: Sequence[Sequence[int]], before_sync=None) -> List[int]:
+        """One token per row, on the host.  ``before_sync`` is called after the kernel is launched
+        and before the host waits for the tokens, for host work that can overlap with the GPU."""
+        out = self.launch(logits, streams, steps, recent)
+        host, event = self.read_async(out)
+        if before_sync is not None:
+            before_sync()
+        event.synchronize()
+        return host.tolist()

@@ -145,3 +145,27 @@ def test_command_line_generate(folders, capsys):
     assert rc == 0
     lines = [l for l in capsys.readouterr().out.strip().splitlines()]
     assert [[int(t) for t in l.split()] for l in lines] == [P.plain_generate(cfg, weights, p, 5) for p in ([5, 6, 7], [9])]
+
+
+@pytest.mark.parametrize("sp", ["greedy", "temperature", "penalties"])
+def test_early_enqueue_changes_nothing(folders, sp):
+    """The loop enqueues the next step before it has read the current step's tokens (when no penalty
+    needs them on the host).  The tokens must be those of the plain loop, stops and unequal lengths included."""
+    from mivi_v4_b200 import SamplingParams
+    cfg, weights = plain_view(folders["B"])
+    ps = prompts(cfg["vocab_size"], [3, 20, 9, 41, 1], seed=9)
+    params = {"greedy": SamplingParams.greedy(), "temperature": SamplingParams.plain_temperature(0.9, seed=5),
+              "penalties": SamplingParams(temperature=0.7, top_k=20, top_p=0.95, repetition_penalty=1.2, seed=5)}[sp]
+    new = [12, 3, 1, 9, 2]
+    base = engine(folders["B"], "float32", cuda_graphs=False).generate(ps, new, params, stop_token_ids=[])
+    stop = base[0][5]
+    want = engine(folders["B"], "float32", cuda_graphs=False).generate(ps, new, params, stop_token_ids=[stop])
+    eng = engine(folders["B"], "float32")
+    got = eng.generate(ps, new, params, stop_token_ids=[stop])
+    assert got == want
+    assert eng.graph_replays > 0
+    eng.cache.check()
+    assert eng.cache.slots.held_count == 0
+    if sp == "greedy":
+        kw = {k: v for k, v in vars(params).items() if k != "seed"}
+        assert want == [P.plain_generate(cfg, weights, p, n, stop_ids=[stop], **kw) for p, n in zip(ps, new)]
