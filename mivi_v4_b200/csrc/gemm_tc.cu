@@ -34,6 +34,79 @@ namespace {
 
 constexpr int THREADS = 192;
 
+// One row's 32 consecutive columns of the accumulator, from registers to Y, in the mode asked for.
+__device__ __forceinline__ void store_chunk(const unsigned (&r)[32], int row, int n_base, int N, int mode,
+                                            const float* __restrict__ bias, void* __restrict__ out, int ldo) {
+
+        if (mode == 3) {
+            // columns n_base .. +15 are gate, +16 .. +31 the up values of the same features
+            if (n_base + 32 <= N) {
+                __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + (n_base >> 1);
+                unsigned packed[8];
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    float a0 = __uint_as_float(r[j]), a1 = __uint_as_float(r[j + 1]);
+                    float b0 = __uint_as_float(r[j + 16]), b1 = __uint_as_float(r[j + 17]);
+                    if (bias) {
+                        a0 += bias[n_base + j]; a1 += bias[n_base + j + 1];
+                        b0 += bias[n_base + j + 16]; b1 += bias[n_base + j + 17];
+                    }
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(a0 / (1.0f + expf(-a0)) * b0,
+                                                                   a1 / (1.0f + expf(-a1)) * b1);
+                    packed[j >> 1] = *reinterpret_cast<const unsigned*>(&v);
+                }
+                if ((((uintptr_t)dst) & 15) == 0) {
+                    reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) reinterpret_cast<unsigned*>(dst)[j] = packed[j];
+                }
+            }
+        } else if (mode == 1) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + n_base;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (n_base + j < N) {
+                    float v = __uint_as_float(r[j]);
+                    if (bias) v += bias[n_base + j];
+                    dst[j] = __float2bfloat16_rn(v);
+                }
+            }
+        } else {
+            float* dst = (float*)out + (size_t)row * ldo + n_base;
+            const bool vec = n_base + 32 <= N && (((uintptr_t)dst) & 15) == 0;
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                           __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    if (bias) {
+                        const float4 bb = *reinterpret_cast<const float4*>(bias + n_base + j);
+                        v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+                    }
+                    float4* p = reinterpret_cast<float4*>(dst + j);
+                    if (mode == 2) {
+                        const float4 old = *p;
+                        v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                    }
+                    *p = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (n_base + j < N) {
+                        float v = __uint_as_float(r[j]);
+                        if (bias) v += bias[n_base + j];
+                        if (mode == 2) v += dst[j];
+                        dst[j] = v;
+                    }
+                }
+            }
+        }
+
+}
+
 template <int BN, int STAGES>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -123,75 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 unsigned r[32];
                 tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < M) {
-                    const int n_base = n0 + c0;
-                    if (mode == 3) {
-                        // columns n_base .. +15 are gate, +16 .. +31 the up values of the same features
-                        if (n_base + 32 <= N) {
-                            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + (n_base >> 1);
-                            unsigned packed[8];
-#pragma unroll
-                            for (int j = 0; j < 16; j += 2) {
-                                float a0 = __uint_as_float(r[j]), a1 = __uint_as_float(r[j + 1]);
-                                float b0 = __uint_as_float(r[j + 16]), b1 = __uint_as_float(r[j + 17]);
-                                if (bias) {
-                                    a0 += bias[n_base + j]; a1 += bias[n_base + j + 1];
-                                    b0 += bias[n_base + j + 16]; b1 += bias[n_base + j + 17];
-                                }
-                                const __nv_bfloat162 v = __floats2bfloat162_rn(a0 / (1.0f + expf(-a0)) * b0,
-                                                                               a1 / (1.0f + expf(-a1)) * b1);
-                                packed[j >> 1] = *reinterpret_cast<const unsigned*>(&v);
-                            }
-                            if ((((uintptr_t)dst) & 15) == 0) {
-                                reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                                reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) reinterpret_cast<unsigned*>(dst)[j] = packed[j];
-                            }
-                        }
-                    } else if (mode == 1) {
-                        __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + n_base;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (n_base + j < N) {
-                                float v = __uint_as_float(r[j]);
-                                if (bias) v += bias[n_base + j];
-                                dst[j] = __float2bfloat16_rn(v);
-                            }
-                        }
-                    } else {
-                        float* dst = (float*)out + (size_t)row * ldo + n_base;
-                        const bool vec = n_base + 32 <= N && (((uintptr_t)dst) & 15) == 0;
-                        if (vec) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                if (bias) {
-                                    const float4 bb = *reinterpret_cast<const float4*>(bias + n_base + j);
-                                    v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
-                                }
-                                float4* p = reinterpret_cast<float4*>(dst + j);
-                                if (mode == 2) {
-                                    const float4 old = *p;
-                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                                }
-                                *p = v;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (n_base + j < N) {
-                                    float v = __uint_as_float(r[j]);
-                                    if (bias) v += bias[n_base + j];
-                                    if (mode == 2) v += dst[j];
-                                    dst[j] = v;
-                                }
-                            }
-                        }
-                    }
-                }
+                if (row < M) store_chunk(r, row, n0 + c0, N, mode, bias, out, ldo);
             }
         }
     }
@@ -201,6 +206,174 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)BN)
                      : "memory");
     }
+}
+
+// ---------------------------------------------------------------------------
+// The same product for wide matrices: 128 x 256 tiles, one block per SM that
+// walks over tiles (consecutive blocks share a tile of W, so W comes from HBM
+// once and from L2 afterwards), and TWO accumulators of 256 columns in tensor
+// memory: while the epilogue warps drain one, the MMA warp fills the other, and
+// the TMA warp runs ahead across tile boundaries.  A 128 x 256 tile needs
+// 48 KB of operands per 128 x 256 x 64 of MMA work, 96 bytes per clock at full
+// tensor rate, which four stages of shared memory can keep in flight; the
+// 128 x 128 tile needs 128.
+// ---------------------------------------------------------------------------
+template <int STAGES>
+struct WideLayout {
+    static constexpr int BN = 256;
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 8;
+    static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;
+};
+
+template <int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
+                    int* __restrict__ err) {
+    using L = WideLayout<STAGES>;
+    constexpr int BN = L::BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned long long* bars = (unsigned long long*)(smem + L::TILE_BYTES);
+    unsigned* tmem_holder = (unsigned*)(bars + 2 * STAGES + 4);
+    const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+    const unsigned acc_full0 = full0 + 16 * STAGES, acc_empty0 = acc_full0 + 16;
+    const unsigned tiles0 = smem_u32(smem);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full0 + 8 * a, 1);
+            mbar_init(acc_empty0 + 8 * a, 4);             // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_holder)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                   // K blocks issued so far, over all tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const unsigned phase = (unsigned)(it / STAGES) & 1u;
+                    ok = mbar_wait(empty0 + 8 * s, phase ^ 1u, err, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
+                    const unsigned a_dst = tiles0 + s * L::STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_a, kb * BK, m0, full0 + 8 * s);
+                    tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, n0, full0 + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc = instr_desc(BM, BN);
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const unsigned acc_phase = (unsigned)(local >> 1) & 1u;
+                ok = mbar_wait(acc_empty0 + 8 * acc, acc_phase ^ 1u, err, 4);   // the epilogue has drained it
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const unsigned phase = (unsigned)(it / STAGES) & 1u;
+                    ok = mbar_wait(full0 + 8 * s, phase, err, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_addr = tiles0 + s * L::STAGE_BYTES;
+                    const unsigned b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        mma_f16(tmem_acc, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
+                                (kb > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(empty0 + 8 * s);
+                }
+                mma_commit(acc_full0 + 8 * acc);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+            const int acc = local & 1;
+            const unsigned acc_phase = (unsigned)(local >> 1) & 1u;
+            const int row = m0 + quarter * 32 + lane;
+            ok = mbar_wait(acc_full0 + 8 * acc, acc_phase, err, 3);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N) break;
+                unsigned r[32];
+                tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < M) store_chunk(r, row, n0 + c0, N, mode, bias, out, ldo);
+            }
+            // this warp has read its lanes of the accumulator: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * acc) : "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int STAGES>
+int launch_wide(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
+                int* err, cudaStream_t stream) {
+    using L = WideLayout<STAGES>;
+    CUtensorMap ma, mb;
+    if (!tensor_map(X, M, K, BM, &ma) || !tensor_map(W, N, K, L::BN, &mb)) return (int)cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(gemm_tc_wide_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        attr_set = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + L::BN - 1) / L::BN);
+    const int blocks = tiles < sm_count() ? tiles : sm_count();
+    gemm_tc_wide_kernel<STAGES><<<blocks, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, err);
+    return mv_launch_status();
 }
 
 template <int BN, int STAGES>
@@ -231,5 +404,8 @@ MV_API int mv_gemm_tc(const void* X, const void* W, const float* bias, void* out
     if (K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && (N % 32 || ldo % 2)) return (int)cudaErrorInvalidValue;
     if (N <= 64) return launch<64, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    // wide enough for 128 x 256 tiles to give every SM work: the persistent kernel
+    const long long wide_tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    if (N >= 256 && wide_tiles >= 96) return launch_wide<4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
     return launch<128, 3>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
 }

@@ -91,10 +91,60 @@ def decode_step(a) -> int:
     return 0
 
 
+def _kernel_table(events, title):
+    ev = [e for e in events if e.device_type == torch.autograd.DeviceType.CUDA
+          and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()]
+    ev.sort(key=lambda e: e.time_range.start)
+    agg = {}
+    for e in ev:
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+        t = agg.setdefault(name, [0.0, 0])
+        t[0] += e.time_range.end - e.time_range.start
+        t[1] += 1
+    span = ev[-1].time_range.end - ev[0].time_range.start
+    print(f"{title}: {len(ev)} kernels, {span:.0f} us from first start to last end")
+    for name, (t, c) in sorted(agg.items(), key=lambda kv: -kv[1][0]):
+        print(f"  {t:8.1f} us  {100 * t / span:5.1f} %  {c:3d} x {t / c:6.1f} us  {name}")
+
+
+def prefill_step(a) -> int:
+    import json
+    import os
+    import sys
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from .. import Engine, random_model
+    if a.config:
+        with open(a.config) as f:
+            cfg = json.load(f)
+    else:
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+        import bench
+        cfg = bench.BENCH_CONFIG
+    T = a.tokens
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+    eng = Engine(model, max_tokens=2 * T + 128, max_batch=2, max_step_tokens=T)
+    g = torch.Generator().manual_seed(0)
+    for i in range(3):
+        toks = torch.randint(0, model.vocab_size, (T,), generator=g).tolist()
+        s = eng.open()
+        if i == 2:
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                eng.step([(s, toks)], "last", copy=False)
+                torch.cuda.synchronize()
+        else:
+            eng.step([(s, toks)], "last", copy=False)
+        eng.close(s)
+    _kernel_table(prof.events(), f"prefill of one prompt of {T} tokens")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mivi_v4_b200.ops.probe")
     ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc_swap", "gemm_tc", "attention_decode", "attention_prefill",
-                                       "decode_step"])
+                                       "decode_step", "prefill_step"])
     ap.add_argument("--config", default=None, help="config.json for decode_step (default: bench.py's)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--m", type=int, default=8)
@@ -115,6 +165,8 @@ def main(argv=None) -> int:
 
     if a.kernel == "decode_step":
         return decode_step(a)
+    if a.kernel == "prefill_step":
+        return prefill_step(a)
 
     if a.kernel.startswith("gemm"):
         fn = getattr(K, a.kernel)

@@ -292,7 +292,10 @@ def test_shortconv_any_cut(out_dtype, H, k, bias):
 
 
 @pytest.mark.parametrize("M,N,Kd", [(65, 16, 8), (128, 128, 64), (129, 130, 72), (300, 301, 240), (256, 64, 200),
-                                    (1000, 2048, 2048), (2048, 512, 8192), (70, 9600, 96)])
+                                    (1000, 2048, 2048), (2048, 512, 8192), (70, 9600, 96),
+                                    # wide enough for the persistent 128 x 256 kernel, ragged in every dimension
+                                    (2048, 2048, 512), (1500, 4100, 264), (4096, 6144, 2048), (12300, 300, 72),
+                                    (2048, 2048, 8192)])
 def test_gemm_tc(M, N, Kd):
     x, w = rnd(M, Kd, dtype=torch.bfloat16), rnd(N, Kd, dtype=torch.bfloat16, seed=1)
     bias = rnd(N, seed=2)
@@ -361,7 +364,7 @@ def test_swiglu_grouped_columns():
     assert torch.allclose(out.double(), a / (1 + torch.exp(-a)) * b, rtol=1e-6, atol=1e-6)
 
 
-@pytest.mark.parametrize("M", [1, 8, 9, 33, 64, 65, 200, 1000])
+@pytest.mark.parametrize("M", [1, 8, 9, 33, 64, 65, 200, 1000, 3000])
 @pytest.mark.parametrize("F,Kd", [(16, 8), (48, 72), (256, 96), (8192, 2048), (1040, 200)])
 def test_gemm_swiglu_epilogue(M, F, Kd):
     """gate and up never reach memory: the product's epilogue applies silu(gate) * up."""
