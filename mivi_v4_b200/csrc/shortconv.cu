@@ -42,6 +42,46 @@ __global__ void shortconv_fwd_kernel(const float* __restrict__ p, const float* _
     z[i] = mv_from_f32<TO>(p[(size_t)n * 3 * H + H + d] * y);
 }
 
+// The same, four channels per thread with 16-byte loads (H a multiple of 4).
+template <typename TO>
+__global__ void shortconv_fwd_vec4_kernel(const float* __restrict__ p, const float* __restrict__ w,
+                                          const float* __restrict__ bias, const float* __restrict__ state,
+                                          const int* __restrict__ positions, const int* __restrict__ seq_of,
+                                          const int* __restrict__ slots, const int* __restrict__ starts,
+                                          TO* __restrict__ z, int N, int H, int k) {
+    mv_pdl_begin();
+    const int H4 = H >> 2;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)N * H4) return;
+    const int n = (int)(i / H4), d = (int)(i - (long long)n * H4) * 4;
+    const int b = seq_of[n];
+    const int pos = positions[n], start = starts[b];
+    const float* st = state + (size_t)slots[b] * (k - 1) * H;
+    float4 y = bias ? *reinterpret_cast<const float4*>(bias + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+        const int src = pos - (k - 1) + j;
+        float4 bx;
+        if (src >= start) {
+            const float* row = p + (size_t)(n - (pos - src)) * 3 * H;
+            const float4 bb = *reinterpret_cast<const float4*>(row + d);
+            const float4 xx = *reinterpret_cast<const float4*>(row + 2 * H + d);
+            bx = make_float4(bb.x * xx.x, bb.y * xx.y, bb.z * xx.z, bb.w * xx.w);
+        } else {
+            bx = *reinterpret_cast<const float4*>(st + (size_t)(src - start + (k - 1)) * H + d);
+        }
+        y.x = fmaf(w[(d + 0) * k + j], bx.x, y.x);
+        y.y = fmaf(w[(d + 1) * k + j], bx.y, y.y);
+        y.z = fmaf(w[(d + 2) * k + j], bx.z, y.z);
+        y.w = fmaf(w[(d + 3) * k + j], bx.w, y.w);
+    }
+    const float4 c = *reinterpret_cast<const float4*>(p + (size_t)n * 3 * H + H + d);
+    TO* dst = z + (size_t)n * H + d;
+    dst[0] = mv_from_f32<TO>(c.x * y.x);
+    dst[1] = mv_from_f32<TO>(c.y * y.y);
+    dst[2] = mv_from_f32<TO>(c.z * y.z);
+    dst[3] = mv_from_f32<TO>(c.w * y.w);
+}
+
 // One thread per (sequence, channel): the state after this step's tokens.
 // New entry j holds position start+len-(k-1)+j: from this step's tokens if it
 // lies in them, else old entry len+j.  Going up in j, every old entry is read
@@ -122,7 +162,15 @@ MV_API int mv_shortconv(const float* p, const float* w, const float* bias, float
     if (k < 1 || k > MV_MAX_CONV_K) return (int)cudaErrorInvalidValue;
     const int threads = 256;
     const unsigned blocks = (unsigned)(((long long)N * H + threads - 1) / threads);
-    if (z_dtype == MV_DT_BF16)
+    if (H % 4 == 0 && (((uintptr_t)p | (uintptr_t)state | (uintptr_t)bias) & 15) == 0) {
+        const unsigned vblocks = (unsigned)(((long long)N * (H / 4) + threads - 1) / threads);
+        if (z_dtype == MV_DT_BF16)
+            mv_launch(shortconv_fwd_vec4_kernel<__nv_bfloat16>, vblocks, threads, 0, stream, p, w, bias, state, positions,
+                      seq_of, slots, starts, (__nv_bfloat16*)z, N, H, k);
+        else
+            mv_launch(shortconv_fwd_vec4_kernel<float>, vblocks, threads, 0, stream, p, w, bias, state, positions, seq_of,
+                      slots, starts, (float*)z, N, H, k);
+    } else if (z_dtype == MV_DT_BF16)
         mv_launch(shortconv_fwd_kernel<__nv_bfloat16>, blocks, threads, 0, stream, p, w, bias, state, positions, seq_of, slots,
                                                             starts, (__nv_bfloat16*)z, N, H, k);
     else

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
+import numpy as np
 import torch
 
 from ..cache import CacheError, KVNeed, SequenceCache
@@ -82,13 +83,16 @@ class Engine:
         Returns float32 logits [wanted, vocab] in the order of the items and,
         within an item, of its places; None if nothing is wanted.
         """
-        items = [(int(s), [int(t) for t in toks]) for s, toks in items]
+        try:
+            items = [(int(s), np.asarray(toks, dtype=np.int64).ravel()) for s, toks in items]
+        except (TypeError, ValueError):
+            raise StepError("token ids must be integers") from None
         V = self.model.vocab_size
         prepared, self._prepared = self._prepared, None
         if (prepared is not None and want == "last" and len(items) == len(prepared["slots"])
                 and all(s == ps and len(t) == 1 for (s, t), ps in zip(items, prepared["slots"]))
                 and self._graphs.get(prepared["key"]) is not None):
-            tokens = [t[0] for _, t in items]
+            tokens = [int(t[0]) for _, t in items]
             for (slot, _), t in zip(items, tokens):
                 if not 0 <= t < V:
                     raise StepError(f"slot {slot}: token id {t} is outside the vocabulary of {V}")
@@ -99,11 +103,11 @@ class Engine:
             if slot in seen:
                 raise StepError(f"slot {slot} appears twice in one step")
             seen.add(slot)
-            if not toks:
+            if toks.size == 0:
                 raise StepError(f"slot {slot} brings no tokens")
-            bad = [t for t in toks if not 0 <= t < V]
-            if bad:
-                raise StepError(f"slot {slot}: token id {bad[0]} is outside the vocabulary of {V}")
+            if toks.min() < 0 or toks.max() >= V:
+                bad = toks[(toks < 0) | (toks >= V)]
+                raise StepError(f"slot {slot}: token id {int(bad[0])} is outside the vocabulary of {V}")
             try:
                 start = self.cache.length(slot)
             except CacheError as e:
@@ -197,7 +201,7 @@ class Engine:
         widths = {g: -(-max(len(self.cache._get(s).pages[g]) for s in slots) // 8) * 8 if decode else None
                   for g in self.cache.kv_groups}
         page_rows = {g: self.cache.page_rows(g, slots, widths[g]) for g in self.cache.kv_groups}
-        plan = dict(slots=slots, starts=starts, lists=[list(t) for _, t in items], out_rows=out_rows,
+        plan = dict(slots=slots, starts=starts, lists=[t for _, t in items], out_rows=out_rows,
                     page_rows=page_rows, decode=decode, key=None, ctx=None)
         if decode:
             plan["key"] = (len(items), tuple(sorted(widths.items())))
@@ -221,7 +225,7 @@ class Engine:
             if ctx is None or ctx.ws is not ws:
                 ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=plan["out_rows"],
                                   page_rows=plan["page_rows"], dtype=self.dtype, ws=ws, upload=False)
-            ctx.upload([t for toks in lists for t in toks] if ctx is reuse else None)
+            ctx.upload(np.concatenate([np.asarray(t).ravel() for t in lists]) if ctx is reuse else None)
             if device_tokens is not None:
                 ctx.tokens.copy_(device_tokens, non_blocking=True)
             return ctx

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -49,15 +50,15 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:n].view(*shape)
 
-    def stage(self, name: str, values: List[int]) -> torch.Tensor:
-        """Copy a list of integers to the device buffer ``name`` (int32) through
-        pinned host memory, one asynchronous copy.  A small ring of pinned
-        buffers is reused; a buffer is taken again only after the copy that
-        last read it has run."""
+    def stage(self, name: str, values) -> torch.Tensor:
+        """Copy integers (a list or a numpy array) to the device buffer ``name``
+        (int32) through pinned host memory, one asynchronous copy.  A small ring
+        of pinned buffers is reused; a buffer is taken again only after the copy
+        that last read it has run."""
         n = len(values)
         dst = self.get(name, (n,), torch.int32)
         if self.device.type != "cuda":
-            dst.copy_(torch.tensor(values, dtype=torch.int32))
+            dst.copy_(torch.from_numpy(np.asarray(values, dtype=np.int32)))
             return dst
         ring = self.__dict__.setdefault("_ring", [])
         if not ring:
@@ -72,7 +73,7 @@ class Workspace:
         else:
             slot[1].synchronize()
         host, event = slot
-        host[:n] = torch.tensor(values, dtype=torch.int32)
+        host.numpy()[:n] = values
         dst.copy_(host[:n], non_blocking=True)
         event.record()
         return dst
@@ -102,33 +103,43 @@ class StepContext:
         self.max_len = max(self.host_lens, default=0)
         self.max_context = max((s + n for s, n in zip(starts, self.host_lens)), default=0)
 
-        flat: List[int] = []
+        parts: List[np.ndarray] = []
         spans: Dict[str, Tuple[int, int]] = {}
+        total = 0
 
-        def put(name: str, values: List[int]) -> None:
-            spans[name] = (len(flat), len(values))
-            flat.extend(values)
-            flat.extend([0] * (-len(flat) % 4))          # 16-byte starts
+        def put(name: str, values) -> None:
+            nonlocal total
+            arr = np.asarray(values, dtype=np.int32).ravel()
+            spans[name] = (total, arr.size)
+            pad = -arr.size % 4                           # 16-byte starts
+            parts.append(arr)
+            if pad:
+                parts.append(np.zeros(pad, dtype=np.int32))
+            total += arr.size + pad
 
-        tokens = [t for toks in token_lists for t in toks]
-        positions = [s + i for s, n in zip(starts, self.host_lens) for i in range(n)]
-        seq_of = [b for b, n in enumerate(self.host_lens) for _ in range(n)]
-        cu = [0]
-        for n in self.host_lens:
-            cu.append(cu[-1] + n)
+        lens = np.asarray(self.host_lens, dtype=np.int64)
+        starts_a = np.asarray(starts, dtype=np.int64)
+        cu = np.zeros(self.n_seqs + 1, dtype=np.int64)
+        np.cumsum(lens, out=cu[1:])
+        seq_of = np.repeat(np.arange(self.n_seqs, dtype=np.int64), lens)
+        # position of a packed row = start of its sequence + its place in the sequence's run
+        positions = np.arange(self.n_tokens, dtype=np.int64) - cu[:-1][seq_of] + starts_a[seq_of] if self.n_tokens \
+            else np.zeros(0, dtype=np.int64)
+        tokens = np.concatenate([np.asarray(t, dtype=np.int64).ravel() for t in token_lists]) if token_lists \
+            else np.zeros(0, dtype=np.int64)
         put("tokens", tokens)
         put("positions", positions)
         put("seq_of", seq_of)
         put("cu", cu)
         put("slots", list(slots))
-        put("starts", list(starts))
-        put("lens", self.host_lens)
+        put("starts", starts_a)
+        put("lens", lens)
         put("out_rows", list(out_rows))
         widths: Dict[int, int] = {}
         for g, rows in page_rows.items():
             widths[g] = len(rows[0]) if rows else 1
-            put(f"pages{g}", [p for r in rows for p in r])
-
+            put(f"pages{g}", rows if rows else [])
+        flat = np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
         # the arrays live in one device buffer whose place depends only on the workspace; they are
         # filled by upload(), which may come later (a step can be laid out before its tokens are known)
         arena = ws.get("step_meta", (len(flat),), torch.int32)

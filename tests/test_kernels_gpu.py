@@ -379,3 +379,48 @@ def test_gemm_swiglu_epilogue(M, F, Kd):
         fn(x, grouped(w1, w3), out, swiglu=True)
         K().check_device_errors()
         assert (out.double() - want).abs().max().item() <= 1e-2 * scale, fn.__name__
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("H,k,bias", [(200, 3, False), (136, 4, True), (64, 1, False), (40, 6, True)])
+def test_shortconv_long_steps(out_dtype, H, k, bias):
+    """Steps with hundreds of tokens of several sequences (the vectorised kernel where the width allows);
+    sequences begin anywhere among the packed rows, and a prompt may arrive in two steps."""
+    T = [300, 77, 5, 130]
+    g = torch.Generator().manual_seed(H * k)
+    p_all = [torch.randn(t, 3 * H, generator=g) for t in T]
+    w = torch.randn(H, k, generator=g)
+    b = torch.randn(H, generator=g) if bias else None
+    wd, bd = w.to(DEV), (b.to(DEV) if bias else None)
+
+    def plain(p):
+        bx = (p[:, :H] * p[:, 2 * H:]).double()
+        y = torch.zeros_like(bx)
+        for j in range(k):
+            shift = k - 1 - j
+            y[shift:] += w[:, j].double() * bx[:bx.shape[0] - shift] if shift else w[:, j].double() * bx
+        if b is not None:
+            y = y + b.double()
+        return p[:, H:2 * H].double() * y
+
+    want = [plain(p) for p in p_all]
+    tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+    for cuts in ([[t] for t in T], [[260, 40], [77], [1, 4], [2, 128]]):
+        state = torch.zeros(6, k - 1, H, device=DEV)
+        slots, done, got = [5, 0, 3, 1], [0] * 4, [[] for _ in T]
+        for step in range(max(len(c) for c in cuts)):
+            live = [s for s in range(len(T)) if step < len(cuts[s])]
+            lens = [cuts[s][step] for s in live]
+            rows = torch.cat([p_all[s][done[s]:done[s] + n] for s, n in zip(live, lens)]).to(DEV).contiguous()
+            cu = [0]
+            for n in lens:
+                cu.append(cu[-1] + n)
+            out = torch.full((rows.shape[0], H), float("nan"), dtype=out_dtype, device=DEV)
+            K().shortconv(rows, wd, bd, state, ints([done[s] + i for s, n in zip(live, lens) for i in range(n)]),
+                          ints([j for j, n in enumerate(lens) for _ in range(n)]), ints(cu),
+                          ints([slots[s] for s in live]), ints([done[s] for s in live]), ints(lens), out, len(live))
+            for j, (s, n) in enumerate(zip(live, lens)):
+                got[s].append(out[cu[j]:cu[j] + n])
+                done[s] += n
+        for a, b_ in zip(got, want):
+            assert torch.allclose(torch.cat(a).double().cpu(), b_, rtol=tol, atol=tol), cuts
