@@ -84,7 +84,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pool, lon
         const unsigned long long kaddr = (unsigned long long)krow;
         float s[GT];
         constexpr int EPV = 16 / sizeof(T);                // elements per 16-byte load
-        constexpr int VG = R <= 2 ? 32 : (R == 4 ? 16 : 8);  // keys whose values are requested together
+        constexpr int VG = R <= 2 ? 16 : 8;                 // keys whose values are requested together
         float vv[VG][R];
         auto load_values = [&](int j0) {
 #pragma unroll

@@ -404,14 +404,19 @@ N_SMS = 148
 DECODE_ATTENTION_MAX_TOKENS = 128      # steps with more query tokens split the work over the queries
 
 
-def attention_decode_plan(N: int, nh: int, nkv: int):
+def attention_decode_plan(N: int, nh: int, nkv: int, context_cap: int = 0):
     """(query heads per block, head tiles per kv head, key splits) for a step of N
-    query tokens: enough blocks to fill the GPU twice over."""
+    query tokens.  Enough blocks to fill the GPU twice over; more when the cache
+    can be long (``context_cap`` tokens, the reach of the step's page table), so
+    that a warp has about eight runs of 32 keys.  The count depends on the page
+    table's width, not on the lengths: a decode step's launches are recorded once
+    per width and replayed as the cache grows."""
     G = nh // nkv
     gt = 1 if G <= 1 else (2 if G <= 2 else (4 if G <= 4 else 8))
     head_tiles = -(-G // gt)
-    splits = max(1, min(32, -(-2 * N_SMS // max(1, N * nkv * head_tiles))))
-    return gt, head_tiles, splits
+    splits = -(-2 * N_SMS // max(1, N * nkv * head_tiles))
+    splits = max(splits, -(-context_cap // (32 * 4 * 8)))
+    return gt, head_tiles, max(1, min(32, splits))
 
 
 def attention_decode(q: torch.Tensor, pool: torch.Tensor, page_table, positions, seq_of, out: torch.Tensor,
@@ -428,7 +433,7 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, page_table, positions,
     _check_kv(pool, nkv, hd, page_size, "attention")
     if q.dtype != pool.dtype or out.dtype != q.dtype:
         raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
-    gt, head_tiles, auto = attention_decode_plan(N, nh, nkv)
+    gt, head_tiles, auto = attention_decode_plan(N, nh, nkv, page_table.shape[1] * page_size)
     splits = auto if splits is None else int(splits)
     part_o = ws.get("attn_part_o", (N * nh * splits * hd,), torch.float32)
     part_ml = ws.get("attn_part_ml", (N * nh * splits * 2,), torch.float32)
