@@ -24,7 +24,22 @@ TINY_C = dict(
     layer_types=["full_attention", "conv", "full_attention"], rope_theta=50000.0, norm_eps=1e-5,
     conv_L_cache=2, conv_bias=False, tie_embedding=True, rope_style="half_split")
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# awkward sizes: a feed-forward width (100) and a vocabulary (131) that are multiples of nothing, as many kv
+# heads as heads, a wide convolution, one layer kind only at the start
+TINY_D = dict(
+    architectures=ARCH, model_type="lfm2", hidden_size=112, num_hidden_layers=3, num_attention_heads=7,
+    num_key_value_heads=7, vocab_size=131, block_ff_dim=100, block_auto_adjust_ff_dim=False,
+    layer_types=["conv", "conv", "full_attention"], rope_theta=777.0, norm_eps=3e-5,
+    conv_L_cache=5, conv_bias=True, tie_embedding=False)
+
+# a convolution of width 1 (no state at all), one kv head for five heads, the adjusted width rounded to 8
+TINY_E = dict(
+    architectures=ARCH, model_type="lfm2", hidden_size=160, num_hidden_layers=2, num_attention_heads=5,
+    num_key_value_heads=1, vocab_size=1000, block_ff_dim=301, block_auto_adjust_ff_dim=True, block_multiple_of=8,
+    block_ffn_dim_multiplier=1.3, layer_types=["full_attention", "conv"], rope_theta=1000000.0, norm_eps=1e-5,
+    conv_L_cache=1, conv_bias=False, tie_embedding=True)
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
 def prompts(vocab: int, lengths, seed: int = 0):
