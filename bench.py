@@ -5,6 +5,7 @@ weights on one B200, in the manner of the reference's ``bench`` command
 prefill, then generation timed without its first token).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16]
+    python bench.py --workload unequal32 | long32k      (the two further workloads, one JSON line each)
 
 One "step" is one decode step of the whole batch.  Prints ONE JSON line:
 ``value`` is decoded tokens per second timed on the device over exactly K
@@ -211,6 +212,47 @@ def time_prefill(model, reps, warmup, seed=2):
     return statistics.median(times)
 
 
+def further_workload(which: str) -> int:
+    """The two further workloads of the benchmark set, through ``Engine.generate``:
+    ``unequal32``: LFM2-700M shape, 32 prompts of 64..2,048 tokens in one unequal prefill step, 256 new tokens;
+    ``long32k``: LFM2-350M shape, 8 prompts of 32,768 tokens, 128 new tokens (keys and values only for the six
+    attention layers, convolution state for the ten others).  Prefill is timed to the first token, decoding
+    from the first token to the end."""
+    import torch
+    from mivi_v4_b200 import Engine, SamplingParams, random_model
+    cfg = dict(BENCH_CONFIG)
+    if which == "long32k":
+        cfg.update(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, block_ff_dim=6656)
+        lens, new = [32768] * 8, 128
+    else:
+        cfg.update(hidden_size=1536, num_attention_heads=24, num_key_value_heads=8, block_ff_dim=10240)
+        g = torch.Generator().manual_seed(0)
+        lens, new = torch.randint(64, 2049, (32,), generator=g).tolist(), 256
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+    eng = Engine(model, max_tokens=sum(-(-(n + new) // 64) * 64 for n in lens), max_batch=len(lens))
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, model.vocab_size, (n,), generator=g).tolist() for n in lens]
+    eng.generate([p[:64] for p in prompts[:2]], 4, SamplingParams.greedy(), stop_token_ids=[])       # warm-up
+    first = {}
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = eng.generate(prompts, new, SamplingParams.greedy(), stop_token_ids=[],
+                       on_token=lambda i, t: first.setdefault("t", time.perf_counter()))
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    assert all(len(o) == new for o in out)
+    c = model.config
+    print(json.dumps({
+        "workload": which, "impl": "ours", "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)",
+        "prompt_tokens": sum(lens), "prefill_tokens_per_s": sum(lens) / (first["t"] - t0),
+        "decode_tokens_per_s": len(lens) * (new - 1) / (t1 - first["t"]), "new_tokens_each": new,
+        "peak_memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30, "cache_gib": eng.cache.bytes() / 2 ** 30,
+        "config": {"hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
+                   "ff": c.ff_dim, "layers": c.num_hidden_layers, "vocab": c.vocab_size, "batch": len(lens),
+                   "longest_prompt": max(lens), "shortest_prompt": min(lens)}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -221,6 +263,8 @@ def main() -> int:
                     help="run the first LAYERS layers of the 16 (sizes unchanged); both numbers go into config")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the end-to-end run")
+    ap.add_argument("--workload", default=None, choices=["unequal32", "long32k"],
+                    help="run one of the two further workloads instead of the default benchmark")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -233,6 +277,8 @@ def main() -> int:
                           "n_gpus": args.gpus}))
         return 2
     warmup = max(3, args.warmup)
+    if args.workload:
+        return further_workload(args.workload)
 
     import torch
     from mivi_v4_b200 import random_model

@@ -16,6 +16,7 @@ writes a model folder from a configuration and a seed.
     python -m mivi_v4_b200 random --config cfg.json --seed 0 --out DIR
     python -m mivi_v4_b200 doctor
     python -m mivi_v4_b200 bench [-m DIR] [--bench-prompt-tokens 2048]
+    python -m mivi_v4_b200 replay --model DIR --dtype bfloat16 --out DIR --max-tokens N < steps.jsonl
 """
 from __future__ import annotations
 
@@ -67,6 +68,12 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"])
 
     sub.add_parser("doctor", help="GPU, compiler and kernel-library report")
+
+    rp = sub.add_parser("replay", help="feed given token ids step by step and write logits (bin/trace_run)")
+    rp.add_argument("--model", required=True)
+    rp.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    rp.add_argument("--out", required=True)
+    rp.add_argument("--max-tokens", type=int, required=True)
 
     b = sub.add_parser("bench", help="prefill and decode throughput of a model folder")
     b.add_argument("-m", "--model", default=None, help="model folder (default: the LFM2.5-1.2B shape with random weights)")
@@ -197,7 +204,19 @@ def cmd_bench(a) -> int:
     return 0
 
 
+def cmd_replay(a) -> int:
+    import os
+    import runpy
+    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
+    sys.argv = [script, "--model", a.model, "--dtype", a.dtype, "--out", a.out, "--max-tokens", str(a.max_tokens)]
+    try:
+        runpy.run_path(script, run_name="__main__")
+    except SystemExit as e:
+        return int(e.code or 0)
+    return 0
+
+
 def main(argv=None) -> int:
     a = build_parser().parse_args(argv)
-    return {"generate": cmd_generate, "info": cmd_info, "random": cmd_random, "doctor": cmd_doctor,
+    return {"replay": cmd_replay, "generate": cmd_generate, "info": cmd_info, "random": cmd_random, "doctor": cmd_doctor,
             "bench": cmd_bench}[a.command](a)

@@ -84,3 +84,29 @@ def test_unequal_batches_slots_reused(folders, name, dtype):
             assert_close(torch.cat(got[i]), want[i], dtype, f"{name} batch {round_} request {i}")
         eng.cache.check()
         assert eng.cache.slots.held_count == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_cache_contents_do_not_depend_on_the_cut(folders, name, dtype):
+    """Not only the logits: the keys, values and convolution state that a sequence leaves in the cache are
+    the same whether it came whole, token by token or in uneven pieces (the reference checks the same for
+    its token and tile paths: crates/mivi-model/src/ssm.rs:455-541, transformer.rs:612-753)."""
+    eng = make_engine(folders[name], dtype, page_size=16)
+    V = CONFIGS[name][0]["vocab_size"]
+    toks = prompts(V, [53], seed=12)[0]
+    dumps = []
+    for cuts in ([53], [1] * 53, [7, 30, 1, 15], [16, 16, 21]):
+        s = eng.open()
+        done = 0
+        for n in cuts:
+            eng.step([(s, toks[done:done + n])], None)
+            done += n
+        dumps.append({g: t.float().cpu() for g, t in eng.cache.dump_slot(s).items()})
+        eng.close(s)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for other in dumps[1:]:
+        for g, ref in dumps[0].items():
+            scale = max(1.0, ref.abs().max().item())
+            assert ref.shape == other[g].shape
+            assert (ref - other[g]).abs().max().item() <= tol * scale, (name, g)
