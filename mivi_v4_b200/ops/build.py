@@ -28,7 +28,8 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "gemm_simt.cu", "shortconv.cu", "attention.cu", "attention_decode.cu",
              "sampling.cu"],
-    "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_swap.cu", "attention_prefill.cu"],
+    "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_swap.cu", "attention_prefill.cu",
+             "attention_prefill_tc.cu"],
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -45,6 +45,7 @@ _SIGNATURES = {
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
     },
 }
 _fns = {}
@@ -476,6 +477,38 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, page_table, cu, start
         _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32),
         _need(out, "attention out", None, (N, nh * hd)), N, n_seqs, nh, nkv, hd, float(scale), int(window),
         _stream()), "mv_attention_prefill")
+    return out
+
+
+def attention_prefill_tc_supported(dtype: torch.dtype, hd: int, pool: torch.Tensor, window: int) -> bool:
+    """What the tcgen05 prefill attention takes: bfloat16, head size 64, no window, and a
+    dense cache pool [pages, 2, kv heads, 64, 64] that a 2-D tensor map can describe."""
+    if dtype != torch.bfloat16 or hd != 64 or window != 0 or pool.dim() != 5 or pool.shape[3] != 64:
+        return False
+    rows = pool.shape[0] * 2 * pool.shape[2] * 64
+    return pool.is_contiguous() and rows < 2 ** 31 and pool.data_ptr() % 16 == 0
+
+
+def attention_prefill_tc(q: torch.Tensor, pool: torch.Tensor, page_table, cu, starts, out: torch.Tensor,
+                         n_seqs: int, nh: int, nkv: int, hd: int, scale: float):
+    """Causal attention of a step with many query tokens, both products on tcgen05
+    (bfloat16, head size 64, pages of 64 tokens, no window).  Same arguments and
+    result as :func:`attention_prefill`."""
+    N = q.shape[0]
+    if not attention_prefill_tc_supported(q.dtype, hd, pool, 0):
+        raise KernelError(f"attention_prefill_tc: needs bfloat16, head size 64 and a dense pool of 64-token pages, "
+                          f"got {q.dtype}, {hd}, pool {tuple(pool.shape)}")
+    if nh % nkv:
+        raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
+    _check_kv(pool, nkv, hd, 64, "attention")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    _check(_fn("bf16", "mv_attention_prefill_tc")(
+        _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.shape[0] * 2 * nkv * 64,
+        _need(page_table, "page table", torch.int32), page_table.shape[1],
+        _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32),
+        _need(out, "attention out", None, (N, nh * hd)), N, n_seqs, nh, nkv, float(scale),
+        _error_flag(q.device).data_ptr(), _stream()), "mv_attention_prefill_tc")
     return out
 
 

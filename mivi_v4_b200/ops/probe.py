@@ -144,6 +144,7 @@ def prefill_step(a) -> int:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mivi_v4_b200.ops.probe")
     ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc_swap", "gemm_tc", "attention_decode", "attention_prefill",
+                                      "attention_prefill_tc",
                                        "decode_step", "prefill_step"])
     ap.add_argument("--config", default=None, help="config.json for decode_step (default: bench.py's)")
     ap.add_argument("--prompt", type=int, default=512)
@@ -231,11 +232,15 @@ def main(argv=None) -> int:
         q = torch.randn(T, nh * hd, device=dev).to(torch.bfloat16)
         out = torch.empty_like(q)
         cu, starts = ints([0, T]), ints([0])
-        run = lambda: K.attention_prefill(q, pool, table, cu, starts, out, 1, nh, nkv, hd, scale, 0)
+        if a.kernel == "attention_prefill_tc":
+            run = lambda: K.attention_prefill_tc(q, pool, table, cu, starts, out, 1, nh, nkv, hd, scale)
+        else:
+            run = lambda: K.attention_prefill(q, pool, table, cu, starts, out, 1, nh, nkv, hd, scale, 0)
         run()
         us = _timed([run], a.reps)
+        K.check_device_errors()
         flops = 4.0 * nh * hd * T * (T + 1) / 2
-        print(f"attention_prefill tokens={T}: {us:.2f} us, {flops / us / 1e6:.1f} TFLOP/s")
+        print(f"{a.kernel} tokens={T}: {us:.2f} us, {flops / us / 1e6:.1f} TFLOP/s")
     torch.cuda.profiler.start()
     run()
     torch.cuda.synchronize()

@@ -132,6 +132,10 @@ class GroupedQueryAttention(Part):
         if N <= K.DECODE_ATTENTION_MAX_TOKENS:
             K.attention_decode(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                self.scale, self.window, step.ws)
+        elif (N >= 128 * step.n_seqs and K.attention_prefill_tc_supported(step.dtype, hd, view.pool, self.window)):
+            # long chunks: 256 query rows a block, both products on tcgen05
+            K.attention_prefill_tc(q, view.pool, view.page_table, step.cu, step.starts, o, step.n_seqs, nh, nkv,
+                                   hd, self.scale)
         elif K.attention_prefill_supported(step.dtype, hd):
             K.attention_prefill(q, view.pool, view.page_table, step.cu, step.starts, o, step.n_seqs, nh, nkv, hd,
                                 self.scale, self.window)

@@ -110,3 +110,26 @@ def test_cache_contents_do_not_depend_on_the_cut(folders, name, dtype):
             scale = max(1.0, ref.abs().max().item())
             assert ref.shape == other[g].shape
             assert (ref - other[g]).abs().max().item() <= tol * scale, (name, g)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_long_prompts_in_chunks(folders, dtype):
+    """Prompts of hundreds of tokens with heads of 64 (in bfloat16 the tcgen05 attention
+    kernel runs them): two unequal prompts in one step, and one prompt in two chunks, the
+    second of which starts in the middle of a page."""
+    name = "F"
+    eng = make_engine(folders[name], dtype, max_tokens=4096)
+    V = CONFIGS[name][0]["vocab_size"]
+    a, b = prompts(V, [700, 300], seed=11)
+    want_a, want_b = plain_logits(folders[name], a), plain_logits(folders[name], b)
+    sa, sb = eng.open(), eng.open()
+    got = eng.step([(sa, a), (sb, b)], "all")
+    eng.close(sa), eng.close(sb)
+    assert_close(got[:700], want_a, dtype, "two prompts, the longer")
+    assert_close(got[700:], want_b, dtype, "two prompts, the shorter")
+    s = eng.open()
+    first = eng.step([(s, a[:230])], "all")
+    second = eng.step([(s, a[230:])], "all")
+    eng.close(s)
+    assert_close(torch.cat([first, second]), want_a, dtype, "one prompt in chunks of 230 and 470")
+    eng.cache.check()

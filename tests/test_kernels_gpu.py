@@ -349,6 +349,39 @@ def test_attention_prefill(nh, nkv, hd, page, window):
     assert not torch.isnan(out.float()).any()
 
 
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (3, 1), (5, 5)])
+def test_attention_prefill_tc(nh, nkv):
+    """The tcgen05 kernel (head size 64, pages of 64): chunks that start anywhere, span several
+    query tiles and key blocks, and end in the middle of a page."""
+    dtype, hd, page = torch.bfloat16, 64, 64
+    chunks = [(0, 1), (0, 700), (130, 270), (5, 64), (63, 66), (1000, 300), (64, 128), (0, 128)]
+    lengths = [s + n for s, n in chunks]
+    pool, table, dense = build_cache(lengths, nkv, hd, page, dtype, seed=nh)
+    N = sum(n for _, n in chunks)
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(N, nh, hd, generator=g)
+    cu = [0]
+    for _, n in chunks:
+        cu.append(cu[-1] + n)
+    # one far key stands out for the last token of the second and of the sixth sequence
+    for b, far in ((1, 3), (5, 200)):
+        kf = dense[b][0][far, 0].float()
+        q[cu[b + 1] - 1, 0] = kf / kf.norm() * 6.0 * (hd ** 0.25)
+    q = q.to(dtype)
+    out = torch.full((N, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    K().attention_prefill_tc(q.reshape(N, nh * hd).contiguous().to(DEV), pool, table, ints(cu),
+                             ints([s for s, _ in chunks]), out, len(chunks), nh, nkv, hd, scale)
+    K().check_device_errors()
+    tol = 1.5e-2
+    for b, (s, n) in enumerate(chunks):
+        for i in sorted(set(list(range(0, n, 7)) + [n - 1] + [x for x in (63, 64, 127, 128, 129) if x < n])):
+            want = plain_attend(q[cu[b] + i], dense[b][0], dense[b][1], s + i, nh, nkv, scale, 0)
+            got = out[cu[b] + i].reshape(nh, hd).double().cpu()
+            assert torch.allclose(got, want, rtol=tol, atol=tol), (b, i, (got - want).abs().max())
+    assert not torch.isnan(out.float()).any()
+
+
 def grouped(w1, w3, G=16):
     F, H = w1.shape
     return torch.stack([w1.view(F // G, G, H), w3.view(F // G, G, H)], dim=1).reshape(2 * F, H).contiguous()

@@ -39,7 +39,15 @@ TINY_E = dict(
     block_ffn_dim_multiplier=1.3, layer_types=["full_attention", "conv"], rope_theta=1000000.0, norm_eps=1e-5,
     conv_L_cache=1, conv_bias=False, tie_embedding=True)
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
+# heads of 64, the size that the tcgen05 attention kernel of long prompts takes; 3 heads on one kv head
+TINY_F = dict(
+    architectures=ARCH, model_type="lfm2", hidden_size=192, num_hidden_layers=3, num_attention_heads=3,
+    num_key_value_heads=1, vocab_size=500, block_ff_dim=256, block_auto_adjust_ff_dim=False,
+    layer_types=["full_attention", "conv", "full_attention"], rope_theta=10000.0, norm_eps=1e-5,
+    conv_L_cache=3, conv_bias=False, tie_embedding=False)
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4),
+           "F": (TINY_F, 5)}
 
 
 def prompts(vocab: int, lengths, seed: int = 0):
