@@ -52,7 +52,7 @@ class Engine:
         self.h2d_bytes = 0
         # decode steps (one token per sequence, last logits wanted) replay a captured CUDA graph;
         # key: (sequences, page-table widths) -> (graph, private workspace, logits, kernels in the graph)
-        self.cuda_graphs = bool(cuda_graphs)
+        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
         self._graphs: Dict[tuple, tuple] = {}
         self.graph_replays = 0
         self._prepared: Optional[dict] = None             # a decode step laid out ahead of its tokens

@@ -34,6 +34,13 @@ class Model:
     def parts(self) -> List:
         return [self.embedding, *self.blocks, self.final_norm, self.head]
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a step's launches may be recorded once and replayed: every part says so."""
+        def walk(p):
+            return getattr(p, "graph_safe", True) and all(walk(sub) for sub in p.nested().values())
+        return all(walk(p) for p in self.parts())
+
     def named_param_specs(self) -> Dict[str, ParamSpec]:
         out: Dict[str, ParamSpec] = {}
         for p in self.parts():

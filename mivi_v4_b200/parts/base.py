@@ -24,6 +24,10 @@ class Part:
     kind = "?"
     prefix = ""
     nested_roles: Dict[str, str] = {}
+    # False for a part whose forward reads device values on the host or launches work that depends
+    # on the step's host-side lists: a model with such a part runs its decode steps launch by launch
+    # instead of replaying a recorded CUDA graph.
+    graph_safe = True
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         """Local tensor name (appended to ``prefix``) -> how the checkpoint stores it."""

@@ -141,6 +141,8 @@ def register_toy_parts():
 
     @register("mixer", "toy_running_sum", replace=True)
     class RunningSum(Part):
+        graph_safe = False                      # its forward loops over the step's slots on the host
+
         def __init__(self, hidden: int, decay: float):
             self.hidden, self.decay = hidden, decay
 
@@ -166,6 +168,56 @@ def register_toy_parts():
                 row += n
             linear(s_all.to(step.dtype), self.w, resid, accumulate=True)
 
+    @register("feed_forward", "toy_top1_experts", replace=True)
+    class Top1Experts(Part):
+        """A feed-forward with routing: every token goes to the one expert whose router logit is
+        largest and gets relu(g Wup^T) Wdown^T times that expert's softmax weight."""
+        graph_safe = False                      # which rows an expert gets is decided on the host
+
+        def __init__(self, hidden: int, ff: int, experts: int):
+            self.hidden, self.ff, self.experts = hidden, ff, experts
+
+        def param_specs(self):
+            H, F = self.hidden, self.ff
+            out = {"router.weight": ParamSpec((self.experts, H), "vector", "conv")}
+            for e in range(self.experts):
+                out[f"experts.{e}.up.weight"] = ParamSpec((F, H))
+                out[f"experts.{e}.down.weight"] = ParamSpec((H, F))
+            return out
+
+        def load(self, t):
+            self.router = t["router.weight"]
+            self.up = [t[f"experts.{e}.up.weight"] for e in range(self.experts)]
+            self.down = [t[f"experts.{e}.down.weight"] for e in range(self.experts)]
+
+        def forward(self, g, resid, step):
+            logits = g.float() @ self.router.float().T                    # router logits in 32-bit
+            prob = torch.softmax(logits, dim=-1)
+            top = logits.argmax(dim=-1)
+            for e in range(self.experts):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                h = torch.empty(rows.numel(), self.ff, dtype=torch.float32, device=g.device)
+                linear(g[rows].contiguous(), self.up[e], h)
+                y = torch.empty(rows.numel(), self.hidden, dtype=torch.float32, device=g.device)
+                linear(torch.relu(h).to(step.dtype), self.down[e], y)
+                resid.index_add_(0, rows, y * prob[rows, e, None])
+
+    @register("position", "toy_stretched_rope", replace=True)
+    class StretchedRope(Part):
+        """Another position encoding: a rotation whose pair i turns by pos / factor^(i / pairs) * theta^(-2i/hd),
+        so that the slow pairs are stretched more than the fast ones."""
+
+        def __init__(self, head_dim: int, theta: float, factor: float):
+            self.head_dim, self.theta, self.factor = head_dim, theta, factor
+            self.table = None
+
+        def rotary(self, device):
+            if self.table is None:              # made once: a recorded step may not copy from the host
+                self.table = stretched_inv_freq(self.head_dim, self.theta, self.factor).to(torch.float32).to(device)
+            return self.table, False
+
     @dataclass
     class ToyConfig:
         hidden_size: int
@@ -178,6 +230,8 @@ def register_toy_parts():
         heads: int = 2
         kv_heads: int = 1
         window: int = 0
+        experts: int = 3
+        stretch: float = 4.0
 
         @classmethod
         def from_dict(cls, d):
@@ -189,8 +243,17 @@ def register_toy_parts():
         blocks = []
         for i, kind in enumerate(c.layer_types):
             pre = f"toy.{i}."
+            ffn = PartSpec("swiglu", dict(hidden=H, ff=c.ff), prefix=pre + "ff.")
+            if kind.endswith("+routed"):
+                kind = kind[:-len("+routed")]
+                ffn = PartSpec("toy_top1_experts", dict(hidden=H, ff=c.ff, experts=c.experts), prefix=pre + "moe.")
             if kind == "sum":
                 mixer = PartSpec("toy_running_sum", dict(hidden=H, decay=c.decay), prefix=pre + "sum.")
+            elif kind == "attn_stretched":
+                mixer = PartSpec("gqa", dict(hidden=H, n_heads=c.heads, n_kv_heads=c.kv_heads, head_dim=hd,
+                                             qk_norm_eps=None, window=0, shared_kv=False), prefix=pre + "attn.",
+                                 parts={"position": PartSpec("toy_stretched_rope",
+                                                             dict(head_dim=hd, theta=1e4, factor=c.stretch))})
             elif kind in ("attn", "attn_shared"):
                 mixer = PartSpec("gqa", dict(hidden=H, n_heads=c.heads, n_kv_heads=c.kv_heads, head_dim=hd,
                                              qk_norm_eps=None, window=c.window, shared_kv=kind == "attn_shared"),
@@ -201,7 +264,7 @@ def register_toy_parts():
             blocks.append(PartSpec("prenorm", prefix=pre, parts={
                 "mixer_norm": PartSpec("rmsnorm", dict(dim=H, eps=c.eps), prefix=pre + "n1."), "mixer": mixer,
                 "ffn_norm": PartSpec("rmsnorm", dict(dim=H, eps=c.eps), prefix=pre + "n2."),
-                "ffn": PartSpec("swiglu", dict(hidden=H, ff=c.ff), prefix=pre + "ff.")}))
+                "ffn": ffn}))
         return ModelSpec(hidden_size=H, vocab_size=c.vocab_size,
                          embedding=PartSpec("table", dict(vocab=c.vocab_size, hidden=H), prefix="toy.embed."),
                          blocks=blocks, schedule=[ScheduleEntry(b, src) for b, src in c.schedule],
@@ -211,16 +274,52 @@ def register_toy_parts():
     register_architecture("ToyForCausalLM", ToyConfig.from_dict, describe, replace=True)
 
 
-def toy_plain(cfg, w, tokens):
-    """The toy architecture, whole sequence, with the plain functions."""
+def stretched_inv_freq(hd, theta, factor):
+    i = torch.arange(hd // 2, dtype=torch.float64)
+    return 1.0 / (torch.tensor(theta, dtype=torch.float64) ** (2.0 * i / hd)) / factor ** (i / (hd // 2))
+
+
+def plain_stretched_attention(u, wq, wk, wv, wo, nh, nkv, hd, theta, factor):
+    """Causal grouped-query attention whose rotation uses stretched_inv_freq (pairs (2i, 2i+1))."""
+    T = u.shape[0]
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * stretched_inv_freq(hd, theta, factor)[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rot(v):
+        out = torch.empty_like(v)
+        a, b = v[..., 0::2], v[..., 1::2]
+        out[..., 0::2], out[..., 1::2] = a * c - b * s, a * s + b * c
+        return out
+
+    q, k, v = rot((u @ wq.T).view(T, nh, hd)), rot((u @ wk.T).view(T, nkv, hd)), (u @ wv.T).view(T, nkv, hd)
+    out = torch.zeros(T, nh, hd, dtype=torch.float64)
+    for h in range(nh):
+        g = h // (nh // nkv)
+        sc = (q[:, h] @ k[:, g].T) / hd ** 0.5
+        sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        out[:, h] = torch.softmax(sc, -1) @ v[:, g]
+    return out.reshape(T, nh * hd) @ wo.T
+
+
+def toy_plain(cfg, w, tokens, margins=None):
+    """The toy architecture, whole sequence, with the plain functions.  ``margins``: a list that
+    receives, per token, the smallest gap between the two largest router logits it met."""
     f = lambda n: w[n].double()
     H, hd = cfg["hidden_size"], cfg["hidden_size"] // cfg.get("heads", 2)
     x = f("toy.embed.weight")[torch.tensor(tokens)]
     kvs = {}
+    gap = torch.full((len(tokens),), float("inf"), dtype=torch.float64)
     for pos, (b, src) in enumerate(cfg["schedule"]):
         kind, pre = cfg["layer_types"][b], f"toy.{b}."
+        routed = kind.endswith("+routed")
+        kind = kind[:-len("+routed")] if routed else kind
         u = P.plain_rms_norm(x, f(pre + "n1.weight"), 1e-5)
-        if kind == "sum":
+        if kind == "attn_stretched":
+            x = x + plain_stretched_attention(u, f(pre + "attn.q_proj.weight"), f(pre + "attn.k_proj.weight"),
+                                              f(pre + "attn.v_proj.weight"), f(pre + "attn.out_proj.weight"),
+                                              cfg.get("heads", 2), cfg.get("kv_heads", 1), hd, 1e4,
+                                              cfg.get("stretch", 4.0))
+        elif kind == "sum":
             s, rows = torch.zeros(H, dtype=torch.float64), []
             for t in range(len(tokens)):
                 s = cfg["decay"] * s + u[t]
@@ -241,7 +340,21 @@ def toy_plain(cfg, w, tokens):
             x = x + P.plain_short_conv(u, f(pre + "conv.in_proj.weight"), f(pre + "conv.conv.weight"),
                                        f(pre + "conv.out_proj.weight"))
         g = P.plain_rms_norm(x, f(pre + "n2.weight"), 1e-5)
-        x = x + P.plain_swiglu(g, f(pre + "ff.w1.weight"), f(pre + "ff.w3.weight"), f(pre + "ff.w2.weight"))
+        if routed:
+            logits = g @ f(pre + "moe.router.weight").T
+            prob, top = torch.softmax(logits, -1), logits.argmax(-1)
+            two = logits.topk(2, dim=-1).values
+            gap = torch.minimum(gap, two[:, 0] - two[:, 1])
+            y = torch.zeros_like(x)
+            for t in range(len(tokens)):
+                e = int(top[t])
+                hid = torch.relu(g[t] @ f(pre + f"moe.experts.{e}.up.weight").T)
+                y[t] = hid @ f(pre + f"moe.experts.{e}.down.weight").T * prob[t, e]
+            x = x + y
+        else:
+            x = x + P.plain_swiglu(g, f(pre + "ff.w1.weight"), f(pre + "ff.w3.weight"), f(pre + "ff.w2.weight"))
+    if margins is not None:
+        margins.append(gap)
     return P.plain_rms_norm(x, f("toy.norm.weight"), 1e-5) @ f("toy.embed.weight").T
 
 
@@ -254,6 +367,12 @@ TOYS = {
     "shared": dict(layer_types=["attn", "conv", "attn_shared"], schedule=[[0, None], [1, None], [2, 0]]),
     # a window: its keys form a cache group of their own and its pages are given back on the way
     "window": dict(layer_types=["attn", "sum"], schedule=[[0, None], [1, None]], window=24),
+    # a feed-forward with routing (the last layer's, so that a token routed otherwise by a rounding
+    # error spoils its own logits only; such tokens, with a gap under 0.05 between the two best
+    # router logits, are left out of the comparison)
+    "routed": dict(layer_types=["conv", "attn+routed"], schedule=[[0, None], [1, None]]),
+    # another position encoding inside the attention the package ships
+    "position": dict(layer_types=["attn_stretched", "conv"], schedule=[[0, None], [1, None]]),
 }
 
 
@@ -269,29 +388,36 @@ def test_toy_architecture_registered_from_the_test(toy, dtype, tmp_path):
     w = load_file(str(tmp_path / toy / "model.safetensors"))
     g = torch.Generator().manual_seed(1)
     seqs = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (70, 9, 33)]
-    want = [toy_plain(cfg, w, s) for s in seqs]
+    margins = []
+    want = [toy_plain(cfg, w, s, margins) for s in seqs]
+    sure = [m > 0.05 for m in margins]                 # tokens whose expert does not hang on rounding
+    assert all(x.float().mean() > 0.8 for x in sure)
     eng = Engine(load_model(folder, dtype, DEV), max_tokens=1024, page_size=16)
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     tol = 3e-5 if dtype == "float32" else 4e-2
 
-    def close(a, b, what):
+    def close(a, b, what, keep=None):
         a, b = a.double().cpu(), b.double()
+        if keep is not None:
+            a, b = a[keep], b[keep]
         assert (a - b).abs().max() <= tol * max(1.0, b.abs().max().item()), (toy, what, (a - b).abs().max())
 
     # whole, then the same sequences in one unequal batch with the tail token by token
-    for s, wv in zip(seqs, want):
+    for s, wv, ok in zip(seqs, want, sure):
         slot = eng.open()
-        close(eng.step([(slot, s)], "all"), wv, "whole")
+        close(eng.step([(slot, s)], "all"), wv, "whole", ok)
         eng.close(slot)
     slots = [eng.open() for _ in seqs]
     cut = [len(s) - 5 for s in seqs]
     lg = eng.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], "last")
     for i in range(len(seqs)):
-        close(lg[i], want[i][cut[i] - 1], "batch prompt")
+        if sure[i][cut[i] - 1]:
+            close(lg[i], want[i][cut[i] - 1], "batch prompt")
     for j in range(5):
         lg = eng.step([(sl, [s[c + j]]) for sl, s, c in zip(slots, seqs, cut)], "last")
         for i in range(len(seqs)):
-            close(lg[i], want[i][cut[i] + j], f"decode {j}")
+            if sure[i][cut[i] + j]:
+                close(lg[i], want[i][cut[i] + j], f"decode {j}")
     if toy == "window":
         kvg = eng.cache.kv_groups[0]
         assert eng.cache._get(slots[0]).pages[kvg][0] is None     # pages before the window went back
