@@ -24,6 +24,12 @@
 // (programmatic dependent launch): weights do not depend on it, and the stream
 // of weights from HBM then does not pause at the kernel boundary.
 //
+// A norm between two products can ride on them (steps of few tokens pay more for a launch than for
+// the norm's arithmetic).  The product that completes the residual stream (mode 2) may also write
+// bf16(x_new * g), g the next norm's weight, and per row-tile sums of x_new^2 ("emit").  The product
+// that consumes those rows then multiplies each token's results by rsqrt(sum / dim + eps), summing
+// the tile sums in a fixed order ("scale"): W (x g s) = s W (x g), and the statistics stay float32.
+//
 // What it replaces in the reference: quantized_matvec, one output row per
 // dot product over the input (crates/mivi-quant/src/lib.rs:75-135).
 #include <cooperative_groups.h>
@@ -33,6 +39,18 @@
 namespace cg = cooperative_groups;
 
 namespace {
+
+constexpr int PART_STRIDE = 64;        // tile sums are laid out [tile][64 tokens]
+
+// The two optional ends of a norm carried by products (all null / 0 when unused).
+struct NormLink {
+    const float* scale_part;           // consumer: [n_scale_part][64] sums of squares of the rows it reads
+    int n_scale_part;
+    float inv_dim, eps;
+    const float* emit_g;               // producer (mode 2): the next norm's weight [N]
+    __nv_bfloat16* emit_x;             // bf16(x_new * g) [M, N]
+    float* emit_part;                  // [tiles][64] sums of x_new^2 over each tile's rows
+};
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
@@ -55,7 +73,7 @@ template <int NT, int RT, int UNROLL, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K,
-                    int ldo) {
+                    int ldo, const NormLink link) {
     constexpr int ROWS = RT * 16, COLS = NT * 8, LDR = COLS + 1;
     extern __shared__ float sm[];
     float* red = sm;                                   // [WARPS][ROWS][LDR] partial sums of the warps
@@ -178,6 +196,12 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         float v = 0.f;
 #pragma unroll
         for (int s = 0; s < 8; ++s) v += part[s];
+        if (link.scale_part) {
+            float ss = 0.f;
+            for (int p = lane; p < link.n_scale_part; p += 32) ss += link.scale_part[p * PART_STRIDE + m];
+            ss = mv_warp_sum(ss);
+            v *= 1.0f / sqrtf(ss * link.inv_dim + link.eps);
+        }
         if (bias && r < ROWS && n < N) v += bias[n];
         if (mode == 3) {
             // ROWS == 32: lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same features
@@ -185,11 +209,25 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
             if (lane < 16 && n + 16 < N)
                 ((__nv_bfloat16*)out)[(size_t)m * ldo + (n >> 5) * 16 + lane] =
                     __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
-        } else if (r < ROWS && n < N) {
-            const size_t o = (size_t)m * ldo + n;
-            if (mode == 0) ((float*)out)[o] = v;
-            else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-            else ((float*)out)[o] += v;
+        } else {
+            float sq = 0.f;
+            if (r < ROWS && n < N) {
+                const size_t o = (size_t)m * ldo + n;
+                if (mode == 0) ((float*)out)[o] = v;
+                else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+                else {
+                    const float x_new = ((float*)out)[o] + v;
+                    ((float*)out)[o] = x_new;
+                    if (link.emit_x) {
+                        link.emit_x[(size_t)m * N + n] = __float2bfloat16_rn(x_new * link.emit_g[n]);
+                        sq = x_new * x_new;
+                    }
+                }
+            }
+            if (mode == 2 && link.emit_x) {
+                sq = mv_warp_sum(sq);
+                if (lane == 0) link.emit_part[(size_t)blockIdx.y * PART_STRIDE + m] = sq;
+            }
         }
     }
     // nobody leaves while another block may still read its shared memory
@@ -198,7 +236,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
 
 template <int NT, int RT, int UNROLL, int WARPS>
 int launch(const void* W, const void* X, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-           cudaStream_t stream) {
+           const NormLink& link, cudaStream_t stream) {
     constexpr int ROWS = RT * 16, LDR = NT * 8 + 1;
     const int ksteps = (K + 31) / 32;
     const int tiles = (N + ROWS - 1) / ROWS;
@@ -236,25 +274,46 @@ int launch(const void* W, const void* X, const float* bias, void* out, int mode,
     cfg.attrs = attr;
     cfg.numAttrs = na;
     cudaLaunchKernelEx(&cfg, gemm_small_m_kernel<NT, RT, UNROLL, WARPS>, (const __nv_bfloat16*)W, (const __nv_bfloat16*)X, bias,
-                       out, mode, M, N, K, ldo);
+                       out, mode, M, N, K, ldo, link);
     return mv_launch_status();
 }
 
 }  // namespace
 
+// Rows of W per block for this shape: 32 halve the re-reads of X and are what the SwiGLU
+// epilogue needs; 16 keep more blocks for a narrow matrix.  (Also the rows behind one tile sum.)
+MV_API int mv_gemm_small_m_tile_rows(int N, int mode) { return (N >= 32 * 2 * 148 || mode == 3) ? 32 : 16; }
+
 // mode: 0 store float32, 1 store bfloat16, 2 add into float32, 3 SwiGLU (W rows in
 // groups of 16 gate + 16 up; out is bfloat16 [M, N/2] with row stride ldo).  Needs
 // 1 <= M <= 64, K a multiple of 8, and 16-byte aligned operands.
+// scale_part (or null): [n_scale_part][64] sums of squares; every token's results are multiplied
+// by rsqrt(sum / dim + eps) before bias and activation.  emit_x (or null, mode 2 only, ldo == N):
+// receives bf16(out_new * emit_g), and emit_part [tiles][64] the sums of out_new^2 per tile of
+// mv_gemm_small_m_tile_rows(N, 2) rows.
 MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void* out, int mode, int M,
-                           int N, int K, int ldo, cudaStream_t stream) {
+                           int N, int K, int ldo, const float* scale_part, int n_scale_part, int dim, float eps,
+                           const float* emit_g, void* emit_x, float* emit_part, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
+    if (emit_x && (mode != 2 || ldo != N || !emit_g || !emit_part)) return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || dim <= 0)) return (int)cudaErrorInvalidValue;
+    NormLink link = {};
+    if (scale_part) {
+        link.scale_part = scale_part;
+        link.n_scale_part = n_scale_part;
+        link.inv_dim = 1.0f / (float)dim;
+        link.eps = eps;
+    }
+    if (emit_x) {
+        link.emit_g = emit_g;
+        link.emit_x = (__nv_bfloat16*)emit_x;
+        link.emit_part = emit_part;
+    }
     const int nt = (M + 7) / 8;
-    // 32 rows per warp halve the re-reads of X and are what the SwiGLU epilogue needs;
-    // 16 rows keep more blocks for a narrow matrix
-    const bool wide = N >= 32 * 2 * 148 || mode == 3;
-#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, stream)
+    const bool wide = mv_gemm_small_m_tile_rows(N, mode) == 32;
+#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, link, stream)
     // few tokens: small blocks, many per SM; many tokens: large blocks, so that X is re-read less
     switch (nt) {
         case 1: if (wide) MV_GO(1, 2, 2, 4); else MV_GO(1, 1, 4, 4);

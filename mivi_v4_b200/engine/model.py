@@ -83,7 +83,14 @@ class Model:
         logits are wanted."""
         x = self.embedding.forward(step)
         for pos, entry in enumerate(self.schedule):
-            self.blocks[entry.block].forward(x, step, cache.view(pos, step.page_tables))
+            block = self.blocks[entry.block]
+            view = cache.view(pos, step.page_tables)
+            if hasattr(block, "entry_link"):
+                # a block that can hand its last norm on to the next one is told which block that is
+                nxt = self.blocks[self.schedule[pos + 1].block] if pos + 1 < len(self.schedule) else None
+                block.forward(x, step, view, after=nxt)
+            else:
+                block.forward(x, step, view)
         if step.n_out == 0:
             return None
         f = step.ws.get("final", (step.n_out, self.hidden_size), step.dtype)

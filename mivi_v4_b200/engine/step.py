@@ -9,6 +9,7 @@ enters a kernel, so it cannot change a result.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -79,6 +80,9 @@ class Workspace:
         return dst
 
 
+CARRY_NORMS_MAX_TOKENS = 64
+
+
 class StepContext:
     """Host and device view of one step.
 
@@ -102,6 +106,10 @@ class StepContext:
         self.is_decode = all(n == 1 for n in self.host_lens)
         self.max_len = max(self.host_lens, default=0)
         self.max_context = max((s + n for s, n in zip(starts, self.host_lens)), default=0)
+        # steps of few tokens in bfloat16 let the products around a norm carry it (MIVI_CARRY_NORMS=0: never)
+        self.carry_norms = (dtype == torch.bfloat16 and 1 <= self.n_tokens <= CARRY_NORMS_MAX_TOKENS
+                            and os.environ.get("MIVI_CARRY_NORMS", "1") != "0")
+        self._link = None
 
         parts: List[np.ndarray] = []
         spans: Dict[str, Tuple[int, int]] = {}
@@ -158,6 +166,15 @@ class StepContext:
         self.page_tables: Dict[int, torch.Tensor] = {
             g: view(f"pages{g}").view(max(self.n_seqs, 1) if rows else 1, widths[g]) if rows else view(f"pages{g}")
             for g, rows in page_rows.items()}
+
+    def leave_link(self, link) -> None:
+        """A block's last product has written the rows of the next block's first norm (or None)."""
+        self._link = link
+
+    def take_link(self, norm):
+        """The link left for this norm part, if the block before left one."""
+        link, self._link = self._link, None
+        return link if link is not None and link.norm is norm else None
 
     def upload(self, tokens: Optional[List[int]] = None) -> None:
         """One host-to-device copy of the step's arrays; ``tokens`` replaces the token ids first."""

@@ -9,6 +9,7 @@ is an error, and so is a library that cannot be built.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -41,7 +42,8 @@ _SIGNATURES = {
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P],
     },
     "bf16": {
-        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _P],
+        "mv_gemm_small_m_tile_rows": [_I, _I],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -182,10 +184,35 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Opti
 SMALL_M_MAX = 64
 
 
+NORM_PART_STRIDE = 64              # tile sums of a carried norm are laid out [tile][64 tokens]
+
+
+@dataclass
+class NormLink:
+    """A norm carried by the two products around it, in a step of few tokens.  The product
+    that completes the residual stream (``emit``) also writes ``xg`` = bf16(x_new * weight)
+    and, per tile of its rows, the sum of x_new^2 into ``partials``; the product that reads
+    the normed rows (``scale``) takes ``xg`` as its input and multiplies every token's
+    results by rsqrt(sum(partials) / dim + eps).  Statistics and scale are float32."""
+    norm: object                   # the norm part this stands for (identity only)
+    weight: torch.Tensor           # float32 [dim]
+    eps: float
+    dim: int
+    xg: torch.Tensor               # bfloat16 [tokens, dim]
+    partials: torch.Tensor         # float32 [>= ceil(dim / 16), 64]
+    n_partials: int = 0            # set by the emitting product
+
+
+def gemm_small_m_tile_rows(N: int, mode: int) -> int:
+    return int(_fn("bf16", "mv_gemm_small_m_tile_rows")(int(N), int(mode)))
+
+
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-                 accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+                 accumulate: bool = False, swiglu: bool = False, scale: Optional[NormLink] = None,
+                 emit: Optional[NormLink] = None) -> torch.Tensor:
     """out = x @ w.T for at most 64 rows of x, bfloat16 operands: the
-    weight-streaming tensor-core kernel of the decode step."""
+    weight-streaming tensor-core kernel of the decode step.  ``scale`` / ``emit``: the
+    two ends of a :class:`NormLink`."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
@@ -207,9 +234,27 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
         mode = 0 if out.dtype == torch.float32 else 1
         _need(out, "gemm out", None, (M, N))
         _dt(out)
+    sp, n_sp, dim, eps, eg, ex, ep = None, 0, 0, 0.0, None, None, None
+    if scale is not None:
+        if scale.n_partials <= 0 or scale.dim != K or x.data_ptr() != scale.xg.data_ptr():
+            raise KernelError("gemm_small_m: the scaled input must be the rows that the norm link's producer wrote")
+        _need(scale.partials, "norm partials", torch.float32)
+        sp, n_sp, dim, eps = scale.partials.data_ptr(), scale.n_partials, scale.dim, float(scale.eps)
+    if emit is not None:
+        tiles = -(-N // gemm_small_m_tile_rows(N, 2))
+        if mode != 2 or emit.dim != N:
+            raise KernelError("gemm_small_m: only a product that adds into the residual stream can emit a norm")
+        _need(emit.weight, "norm weight", torch.float32, (N,))
+        _need(emit.xg, "normed rows", torch.bfloat16, (M, N))
+        _need(emit.partials, "norm partials", torch.float32)
+        if emit.partials.numel() < tiles * NORM_PART_STRIDE:
+            raise KernelError(f"gemm_small_m: norm partials hold {emit.partials.numel()} values, {tiles} tiles need "
+                              f"{tiles * NORM_PART_STRIDE}")
+        eg, ex, ep = emit.weight.data_ptr(), emit.xg.data_ptr(), emit.partials.data_ptr()
+        emit.n_partials = tiles
     _check(_fn("bf16", "mv_gemm_small_m")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, _stream()), "mv_gemm_small_m")
+        out.data_ptr(), mode, M, N, K, ldo, sp, n_sp, dim, eps, eg, ex, ep, _stream()), "mv_gemm_small_m")
     return out
 
 

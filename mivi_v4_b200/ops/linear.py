@@ -35,21 +35,37 @@ def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16) -> bool:
+    """Whether a product of ``n_rows`` rows with ``w`` takes the kernel that can carry a
+    norm (``scale`` / ``emit`` of :func:`linear`)."""
+    return (_DECODE_GEMM != "tc" and 1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, *,
+                  scale: Optional[K.NormLink] = None) -> torch.Tensor:
     """out = silu(gate) * up where [gate | up] = x @ w_grouped.T and the rows of
     ``w_grouped`` alternate in groups of 16 (gate rows, then the up rows of the
     same features): the activation runs in the product's epilogue, so gate and
     up never go to memory.  Needs ``tensor_core_ok``."""
+    if scale is not None:
+        return K.gemm_small_m(x, w_grouped, out, swiglu=True, scale=scale)
     if x.shape[0] <= K.SMALL_M_MAX:
         return _small_m(x.shape[0])(x, w_grouped, out, swiglu=True)
     return K.gemm_tc(x, w_grouped, out, swiglu=True)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-           accumulate: bool = False) -> torch.Tensor:
+           accumulate: bool = False, scale: Optional[K.NormLink] = None,
+           emit: Optional[K.NormLink] = None) -> torch.Tensor:
     """out = x @ w.T (+ bias); with ``accumulate`` the product is added to
     ``out`` (float32), which is how a layer's result joins the residual
-    stream without a separate pass."""
+    stream without a separate pass.  ``scale`` / ``emit`` (see ``NormLink``) need
+    ``norm_link_ok`` for these operands."""
+    if scale is not None or emit is not None:
+        if not norm_link_ok(x.shape[0], w, x.dtype) or x.data_ptr() % 16:
+            raise K.KernelError("linear: these operands cannot carry a norm; ask norm_link_ok first")
+        return K.gemm_small_m(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit)
     if w.dtype == torch.float32 and x.dtype != torch.float32:
         x = x.float()
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0

@@ -29,6 +29,13 @@ class Part:
     # instead of replaying a recorded CUDA graph.
     graph_safe = True
 
+    def carries_norm(self, step):
+        """(accepts, emits): whether, in this step, the part's first product can take rows that still
+        lack their norm's scale (``forward(..., scale=link)``) and whether its last product, the one
+        that adds into the residual stream, can write the next norm's rows (``forward(..., emit=link)``).
+        A mixer or feed-forward that answers (False, False), the default, is never passed either."""
+        return False, False
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         """Local tensor name (appended to ``prefix``) -> how the checkpoint stores it."""
         return {}

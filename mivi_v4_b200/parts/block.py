@@ -23,11 +23,39 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, resid, step, view) -> None:
+    def entry_link(self, step):
+        """The first norm of this block as a link that the block before may fill, or None."""
+        if step.carry_norms and hasattr(self.mixer_norm, "link") and self.mixer.carries_norm(step)[0]:
+            return self.mixer_norm.link(step, "entry")
+        return None
+
+    def forward(self, resid, step, view, after=None) -> None:
+        """``after``: the block that runs next in this step, if any.  In a step of few tokens the two
+        norms are not kernels of their own where the parts allow it: the product that completes the
+        residual stream writes the next norm's rows, the product that reads them applies its scale."""
         N, H = resid.shape
-        u = step.ws.get("normed", (N, H), step.dtype)
-        self.mixer_norm.forward(resid, u)
-        self.mixer.forward(u, resid, step, view)
-        g = step.ws.get("normed", (N, H), step.dtype)
-        self.ffn_norm.forward(resid, g)
-        self.ffn.forward(g, resid, step)
+        carry = step.carry_norms
+        _, mixer_emits = self.mixer.carries_norm(step) if carry else (False, False)
+        ffn_accepts, ffn_emits = self.ffn.carries_norm(step) if carry else (False, False)
+        entry = step.take_link(self.mixer_norm)
+        mid = self.ffn_norm.link(step, "mid") if mixer_emits and ffn_accepts and hasattr(self.ffn_norm, "link") else None
+        leave = after.entry_link(step) if ffn_emits and after is not None and hasattr(after, "entry_link") else None
+        kw = {}
+        if entry is not None:
+            u, kw["scale"] = entry.xg, entry
+        else:
+            u = step.ws.get("normed", (N, H), step.dtype)
+            self.mixer_norm.forward(resid, u)
+        if mid is not None:
+            kw["emit"] = mid
+        self.mixer.forward(u, resid, step, view, **kw)
+        kw = {}
+        if mid is not None:
+            g, kw["scale"] = mid.xg, mid
+        else:
+            g = step.ws.get("normed", (N, H), step.dtype)
+            self.ffn_norm.forward(resid, g)
+        if leave is not None:
+            kw["emit"] = leave
+        self.ffn.forward(g, resid, step, **kw)
+        step.leave_link(leave)

@@ -6,7 +6,7 @@ from typing import Dict
 import torch
 
 from ..ops import kernels as K
-from ..ops.linear import linear, linear_swiglu, tensor_core_ok
+from ..ops.linear import linear, linear_swiglu, norm_link_ok, tensor_core_ok
 from .base import Part
 from .registry import register
 from .spec import ParamSpec
@@ -41,13 +41,17 @@ class SwiGLU(Part):
             self.w13 = torch.cat([w1, w3], dim=0).contiguous()
         self.w2 = t["w2.weight"]
 
-    def forward(self, g, resid, step) -> None:
+    def carries_norm(self, step):
+        n = step.n_tokens
+        return (bool(self.group) and norm_link_ok(n, self.w13, step.dtype)), norm_link_ok(n, self.w2, step.dtype)
+
+    def forward(self, g, resid, step, scale=None, emit=None) -> None:
         N = g.shape[0]
         h = step.ws.get("ffh", (N, self.ff), step.dtype)
         if self.group and tensor_core_ok(g, self.w13):
-            linear_swiglu(g, self.w13, h)
+            linear_swiglu(g, self.w13, h, scale=scale)
         else:
             gu = step.ws.get("proj", (N, 2 * self.ff), torch.float32)
-            linear(g, self.w13, gu)
+            linear(g, self.w13, gu, scale=scale)
             K.swiglu(gu, h, self.group)
-        linear(h, self.w2, resid, accumulate=True)
+        linear(h, self.w2, resid, accumulate=True, emit=emit)

@@ -8,7 +8,7 @@ import torch
 
 from ..cache.needs import KVNeed, StateNeed
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import linear, norm_link_ok
 from .base import Part
 from .registry import register
 from .spec import ParamSpec
@@ -46,14 +46,18 @@ class ShortConv(Part):
     def cache_need(self):
         return StateNeed((self.kernel - 1, self.hidden))
 
-    def forward(self, u, resid, step, view) -> None:
+    def carries_norm(self, step):
+        n = step.n_tokens
+        return norm_link_ok(n, self.w_in, step.dtype), norm_link_ok(n, self.w_out, step.dtype)
+
+    def forward(self, u, resid, step, view, scale=None, emit=None) -> None:
         N, H = u.shape
         p = step.ws.get("proj", (N, 3 * H), torch.float32)
-        linear(u, self.w_in, p, bias=self.b_in)
+        linear(u, self.w_in, p, bias=self.b_in, scale=scale)
         z = step.ws.get("mix", (N, H), step.dtype)
         K.shortconv(p, self.taps, self.b_conv, view.state, step.positions, step.seq_of, step.cu,
                     step.slots, step.starts, step.lens, z, step.n_seqs, decode=step.is_decode)
-        linear(z, self.w_out, resid, bias=self.b_out, accumulate=True)
+        linear(z, self.w_out, resid, bias=self.b_out, accumulate=True, emit=emit)
 
 
 @register("mixer", "gqa")
@@ -111,14 +115,18 @@ class GroupedQueryAttention(Part):
     def cache_need(self):
         return KVNeed(self.nkv, self.hd, self.window)
 
-    def forward(self, u, resid, step, view) -> None:
+    def carries_norm(self, step):
+        n = step.n_tokens
+        return norm_link_ok(n, self.w_qkv, step.dtype), norm_link_ok(n, self.w_o, step.dtype)
+
+    def forward(self, u, resid, step, view, scale=None, emit=None) -> None:
         N = u.shape[0]
         nh, nkv, hd = self.nh, self.nkv, self.hd
         if view.writable == self.shared_kv:
             raise RuntimeError("a shared_kv attention layer must read another layer's cache, and only it may")
         width = (nh + (0 if self.shared_kv else 2 * nkv)) * hd
         qkv = step.ws.get("proj", (N, width), torch.float32)
-        linear(u, self.w_qkv, qkv)
+        linear(u, self.w_qkv, qkv, scale=scale)
         q = step.ws.get("q", (N, nh * hd), step.dtype)
         rot = self.position.rotary(u.device)
         inv_freq, half_split = rot if rot is not None else (None, False)
@@ -142,4 +150,4 @@ class GroupedQueryAttention(Part):
         else:
             K.attention_generic(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                 self.scale, self.window)
-        linear(o, self.w_o, resid, accumulate=True)
+        linear(o, self.w_o, resid, accumulate=True, emit=emit)

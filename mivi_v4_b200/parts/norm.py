@@ -25,3 +25,11 @@ class RMSNorm(Part):
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return K.rmsnorm(x, self.weight, self.eps, out, rows)
+
+    def link(self, step, name: str) -> K.NormLink:
+        """This norm as something the products around it carry (steps of few tokens): buffers for
+        the rows bf16(x * weight) and the tile sums of squares, from the step's workspace."""
+        n = step.n_tokens
+        return K.NormLink(self, self.weight, self.eps, self.dim,
+                          step.ws.get("link_rows_" + name, (n, self.dim), torch.bfloat16),
+                          step.ws.get("link_sums_" + name, (-(-self.dim // 16), K.NORM_PART_STRIDE), torch.float32))

@@ -107,6 +107,53 @@ def test_gemm_small_m(kernel, M, N, Kd):
     K().check_device_errors()
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 17, 64])
+@pytest.mark.parametrize("H,F,swiglu", [(64, 48, False), (200, 96, True), (2048, 160, False), (9600, 64, True)])
+def test_gemm_small_m_carries_a_norm(M, H, F, swiglu):
+    """x_new = x + z Wo^T; y = rmsnorm(x_new) * g, then y W1^T (or its SwiGLU): the first product
+    writes the rows bf16(x_new * g) and the tile sums, the second applies the scale."""
+    from mivi_v4_b200.ops.linear import linear, linear_swiglu
+    eps = 1e-5
+    z, wo = rnd(M, 72, dtype=torch.bfloat16), rnd(H, 72, dtype=torch.bfloat16, seed=1)
+    x = rnd(M, H, scale=2.0, seed=2)
+    g = rnd(H, seed=3) + 1.0
+    w1 = rnd(2 * F if swiglu else F, H, dtype=torch.bfloat16, seed=4)
+    bias = None if swiglu else rnd(F, seed=5)
+    link = K().NormLink(None, g, eps, H, torch.empty(M, H, dtype=torch.bfloat16, device=DEV),
+                        torch.full((-(-H // 16), 64), float("nan"), device=DEV))
+    resid = x.clone()
+    linear(z, wo, resid, accumulate=True, emit=link)
+    x_new = x.double() + z.double() @ wo.double().T
+    assert torch.allclose(resid.double(), x_new, rtol=1e-5, atol=1e-4)
+    assert link.n_partials == -(-H // (32 if H >= 9472 else 16))
+    ss = link.partials[:link.n_partials, :M].double().sum(0)
+    assert torch.allclose(ss, (x_new ** 2).sum(1), rtol=1e-5)
+    y = P.plain_rms_norm(x_new, g.double(), eps)
+    if swiglu:
+        out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+        linear_swiglu(link.xg, w1, out, scale=link)
+        gu = (y @ w1.double().T).view(M, F // 16, 2, 16)
+        a, b = gu[:, :, 0].reshape(M, F), gu[:, :, 1].reshape(M, F)
+        want = a / (1 + torch.exp(-a)) * b
+    else:
+        out = torch.empty(M, F, device=DEV)
+        linear(link.xg, w1, out, bias=bias, scale=link)
+        want = y @ w1.double().T + bias.double()
+    # rounding x_new * g to bfloat16 moves a dot product of H terms by about 2^-9 sqrt(H) (3 sigma: delta);
+    # silu(a) b moves by about (|a| + |b|) delta
+    delta = 1e-2 * math.sqrt(H)
+    bound = delta * (a.abs() + b.abs() + 1) + 1e-2 * want.abs() if swiglu else delta + 1e-2 * want.abs()
+    err = (out.double().cpu() - want.cpu()).abs()
+    assert (err <= bound.cpu()).all(), (err - bound.cpu()).max()
+    # the same through the norm kernel and a plain product, for the size of the difference
+    u = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+    K().rmsnorm(resid, g, eps, u)
+    if not swiglu:
+        ref = torch.empty(M, F, device=DEV)
+        linear(u, w1, ref, bias=bias)
+        assert (out - ref).abs().max() <= 2 * (ref.double() - want).abs().max() + 1e-3
+
+
 def test_gemm_small_m_refuses_what_it_cannot_do():
     x, w = rnd(65, 64, dtype=torch.bfloat16), rnd(8, 64, dtype=torch.bfloat16)
     with pytest.raises(K().KernelError):
