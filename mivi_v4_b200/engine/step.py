@@ -80,7 +80,9 @@ class Workspace:
         return dst
 
 
-CARRY_NORMS_MAX_TOKENS = 64
+# measured on the 1.2B-parameter shape: 2 % faster at 8 tokens, slower from 16 on (the scale costs the
+# consuming product's epilogue one more round trip to L2 per token it owns)
+CARRY_NORMS_MAX_TOKENS = 8
 
 
 class StepContext:
