@@ -77,7 +77,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     constexpr int ROWS = RT * 16, COLS = NT * 8, LDR = COLS + 1;
     extern __shared__ float sm[];
     float* red = sm;                                   // [WARPS][ROWS][LDR] partial sums of the warps
-    float* csum = sm + WARPS * ROWS * LDR;             // [ROWS][LDR] their sum: this block's share
+    float* csum = sm + WARPS * ROWS * LDR;             // [COLS][ROWS] their sum: this block's share
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.y * ROWS;
@@ -167,12 +167,14 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
             mine[(row + 8) * LDR + col + 1] = acc[r][j][3];
         }
     __syncthreads();
+    // csum is laid out [token][row]: the lanes of a warp, one row each, then read consecutive words,
+    // which is what a read through distributed shared memory wants (scattered words crawl there)
     for (int idx = threadIdx.x; idx < ROWS * COLS; idx += WARPS * 32) {
-        const int r = idx / COLS, c = idx - r * COLS;
+        const int c = idx / ROWS, r = idx - c * ROWS;
         float v = 0.f;
 #pragma unroll
         for (int wp = 0; wp < WARPS; ++wp) v += red[(size_t)wp * ROWS * LDR + r * LDR + c];
-        csum[r * LDR + c] = v;
+        csum[c * ROWS + r] = v;
     }
 
     // The slices of this tile are added in rank order.  The work of adding is dealt out to all blocks
@@ -192,7 +194,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         const int n = n0 + r;
         float part[8];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) part[s] = (s < slices && r < ROWS) ? share[s][r * LDR + m] : 0.f;
+        for (int s = 0; s < 8; ++s) part[s] = (s < slices && r < ROWS) ? share[s][m * ROWS + r] : 0.f;
         float v = 0.f;
 #pragma unroll
         for (int s = 0; s < 8; ++s) v += part[s];

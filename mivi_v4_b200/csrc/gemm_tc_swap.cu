@@ -30,8 +30,7 @@ struct SwapLayout {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int LD = BN + 1;
-    static constexpr int CSUM_BYTES = BM * LD * 4;
+    static constexpr int CSUM_BYTES = BM * BN * 4;   // [token][row]: a warp reads consecutive words
     static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 8;
     static constexpr int TOTAL = (TILE_BYTES > CSUM_BYTES ? TILE_BYTES : CSUM_BYTES) + BAR_BYTES + 1024;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -127,7 +126,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (c0 + j < BN) csum[r * L::LD + c0 + j] = __uint_as_float(v[j]);
+                if (c0 + j < BN) csum[(c0 + j) * BM + r] = __uint_as_float(v[j]);      // [token][row]
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -145,28 +144,44 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         share[0] = csum;
     }
     {
+        // An item is 32 consecutive rows of the tile for one token.  A warp takes its items four at a
+        // time: first every load of the four (the slices' sums, and the old values where the product is
+        // added to memory), then the arithmetic and the stores - so four round trips overlap.
+        constexpr int CH = 4, WARPS_ALL = THREADS / 32;
         const int items = (BM / 32) * M;
-        for (int it = slice + slices * warp; it < items; it += slices * (THREADS / 32)) {
-            const int u = it % (BM / 32), m = it / (BM / 32);
-            const int r = u * 32 + lane, n = n0 + r;
-            float part[8];
+        for (int it0 = slice + slices * warp; it0 < items; it0 += CH * slices * WARPS_ALL) {
+            float part[CH][8], old[CH];
 #pragma unroll
-            for (int s = 0; s < 8; ++s) part[s] = s < slices ? share[s][r * L::LD + m] : 0.f;
-            float v = 0.f;
+            for (int c = 0; c < CH; ++c) {
+                const int it = it0 + c * slices * WARPS_ALL;
+                const int u = it % (BM / 32), m = it / (BM / 32);
+                const int r = u * 32 + lane, n = n0 + r;
 #pragma unroll
-            for (int s = 0; s < 8; ++s) v += part[s];
-            if (bias && n < N) v += bias[n];
-            if (mode == 3) {
-                // lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same features
-                const float up = __shfl_down_sync(0xffffffffu, v, 16);
-                if (lane < 16 && n + 16 < N)
-                    ((__nv_bfloat16*)out)[(size_t)m * ldo + (n >> 5) * 16 + lane] =
-                        __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
-            } else if (n < N) {
-                const size_t o = (size_t)m * ldo + n;
-                if (mode == 0) ((float*)out)[o] = v;
-                else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-                else ((float*)out)[o] += v;
+                for (int s = 0; s < 8; ++s) part[c][s] = (it < items && s < slices) ? share[s][m * BM + r] : 0.f;
+                old[c] = (mode == 2 && it < items && n < N) ? ((const float*)out)[(size_t)m * ldo + n] : 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const int it = it0 + c * slices * WARPS_ALL;
+                if (it >= items) break;
+                const int u = it % (BM / 32), m = it / (BM / 32);
+                const int r = u * 32 + lane, n = n0 + r;
+                float v = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) v += part[c][s];
+                if (bias && n < N) v += bias[n];
+                if (mode == 3) {
+                    // lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same features
+                    const float up = __shfl_down_sync(0xffffffffu, v, 16);
+                    if (lane < 16 && n + 16 < N)
+                        ((__nv_bfloat16*)out)[(size_t)m * ldo + (n >> 5) * 16 + lane] =
+                            __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+                } else if (n < N) {
+                    const size_t o = (size_t)m * ldo + n;
+                    if (mode == 0) ((float*)out)[o] = v;
+                    else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+                    else ((float*)out)[o] = old[c] + v;
+                }
             }
         }
     }
@@ -192,9 +207,12 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
     }
     const int tiles = (N + BM - 1) / BM;
     const int kblocks = (K + BK - 1) / BK;
-    // slices of K: enough blocks to fill the GPU about twice over, each with at least four K blocks
-    int slices = 1;
-    while (slices < 8 && tiles * slices < 2 * 148 && kblocks / (slices * 2) >= 4) slices *= 2;
+    // slices of K (at most 8, the portable cluster size): as many blocks as fit the GPU at one a
+    // multiprocessor, each with at least two K blocks
+    int slices = 148 / tiles;
+    slices = slices > 8 ? 8 : slices;
+    while (slices > 1 && kblocks / slices < 2) --slices;
+    if (slices < 1) slices = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(slices, tiles);
     cfg.blockDim = dim3(THREADS);
@@ -220,7 +238,7 @@ MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
-    if (M <= 16) return launch<16, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
-    if (M <= 32) return launch<32, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
-    return launch<64, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    if (M <= 16) return launch<16, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    if (M <= 32) return launch<32, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    return launch<64, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
 }

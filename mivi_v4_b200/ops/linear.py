@@ -18,15 +18,21 @@ from . import kernels as K
 
 import os
 
-_DECODE_GEMM = os.environ.get("MIVI_DECODE_GEMM", "mma")
+_DECODE_GEMM = os.environ.get("MIVI_DECODE_GEMM", "auto")
+MMA_MAX_ROWS = 8
 
 
 def _small_m(m: int):
-    """The kernel for at most 64 rows.  Two exist: the mma.sync kernel that streams
-    W through registers (``mma``, the default: faster at every batch size measured,
-    1 to 64, because a decode product is too short to repay a TMA pipeline's set-up)
-    and the tcgen05 kernel with swapped operands (``tc``, MIVI_DECODE_GEMM=tc)."""
-    return K.gemm_tc_swap if _DECODE_GEMM == "tc" else K.gemm_small_m
+    """The kernel for at most 64 rows.  Two exist: the mma.sync kernel that streams W
+    through registers, and the tcgen05 kernel with swapped operands (TMA ring,
+    accumulator in tensor memory).  Measured on whole decode steps of the
+    1.2B-parameter shape, the first wins up to 8 rows (a short product does not repay
+    the pipeline's set-up), the second from 16 rows on (1.3 ms against 1.4 at 16 rows,
+    1.7 ms against 2.7 at 64), where the first is bound by re-reading X.
+    MIVI_DECODE_GEMM=mma|tc forces one."""
+    if _DECODE_GEMM == "tc" or (_DECODE_GEMM != "mma" and m > MMA_MAX_ROWS):
+        return K.gemm_tc_swap
+    return K.gemm_small_m
 
 
 def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -38,7 +44,7 @@ def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16) -> bool:
     """Whether a product of ``n_rows`` rows with ``w`` takes the kernel that can carry a
     norm (``scale`` / ``emit`` of :func:`linear`)."""
-    return (_DECODE_GEMM != "tc" and 1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
+    return (_small_m(n_rows) is K.gemm_small_m and 1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
             and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
 
 

@@ -112,7 +112,7 @@ def test_gemm_small_m(kernel, M, N, Kd):
 def test_gemm_small_m_carries_a_norm(M, H, F, swiglu):
     """x_new = x + z Wo^T; y = rmsnorm(x_new) * g, then y W1^T (or its SwiGLU): the first product
     writes the rows bf16(x_new * g) and the tile sums, the second applies the scale."""
-    from mivi_v4_b200.ops.linear import linear, linear_swiglu
+    from mivi_v4_b200.ops.linear import linear
     eps = 1e-5
     z, wo = rnd(M, 72, dtype=torch.bfloat16), rnd(H, 72, dtype=torch.bfloat16, seed=1)
     x = rnd(M, H, scale=2.0, seed=2)
@@ -122,7 +122,7 @@ def test_gemm_small_m_carries_a_norm(M, H, F, swiglu):
     link = K().NormLink(None, g, eps, H, torch.empty(M, H, dtype=torch.bfloat16, device=DEV),
                         torch.full((-(-H // 16), 64), float("nan"), device=DEV))
     resid = x.clone()
-    linear(z, wo, resid, accumulate=True, emit=link)
+    K().gemm_small_m(z, wo, resid, accumulate=True, emit=link)
     x_new = x.double() + z.double() @ wo.double().T
     assert torch.allclose(resid.double(), x_new, rtol=1e-5, atol=1e-4)
     assert link.n_partials == -(-H // (32 if H >= 9472 else 16))
@@ -131,13 +131,13 @@ def test_gemm_small_m_carries_a_norm(M, H, F, swiglu):
     y = P.plain_rms_norm(x_new, g.double(), eps)
     if swiglu:
         out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
-        linear_swiglu(link.xg, w1, out, scale=link)
+        K().gemm_small_m(link.xg, w1, out, swiglu=True, scale=link)
         gu = (y @ w1.double().T).view(M, F // 16, 2, 16)
         a, b = gu[:, :, 0].reshape(M, F), gu[:, :, 1].reshape(M, F)
         want = a / (1 + torch.exp(-a)) * b
     else:
         out = torch.empty(M, F, device=DEV)
-        linear(link.xg, w1, out, bias=bias, scale=link)
+        K().gemm_small_m(link.xg, w1, out, bias=bias, scale=link)
         want = y @ w1.double().T + bias.double()
     # rounding x_new * g to bfloat16 moves a dot product of H terms by about 2^-9 sqrt(H) (3 sigma: delta);
     # silu(a) b moves by about (|a| + |b|) delta
