@@ -80,19 +80,23 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32
         : "memory");
 }
 
-// One row of S (128 values in registers): maximum over the keys the row may see.
+// One row of S (128 values in registers): maximum over the keys the row may see; sixteen chains, so
+// that no instruction waits for the one before it.
+template <bool MASK>
+__device__ __forceinline__ float chunk_max(const unsigned (&s)[32], int c, int visible) {
+    float a[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 32; i += 4)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (!MASK || c + i + e < visible) a[e] = fmaxf(a[e], __uint_as_float(s[i + e]));
+    return fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
+}
 template <bool MASK>
 __device__ __forceinline__ float row_max(const unsigned (&s0)[32], const unsigned (&s1)[32], const unsigned (&s2)[32],
                                          const unsigned (&s3)[32], int visible) {
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        if (!MASK || i < visible) mx = fmaxf(mx, __uint_as_float(s0[i]));
-        if (!MASK || 32 + i < visible) mx = fmaxf(mx, __uint_as_float(s1[i]));
-        if (!MASK || 64 + i < visible) mx = fmaxf(mx, __uint_as_float(s2[i]));
-        if (!MASK || 96 + i < visible) mx = fmaxf(mx, __uint_as_float(s3[i]));
-    }
-    return mx;
+    return fmaxf(fmaxf(chunk_max<MASK>(s0, 0, visible), chunk_max<MASK>(s1, 32, visible)),
+                 fmaxf(chunk_max<MASK>(s2, 64, visible), chunk_max<MASK>(s3, 96, visible)));
 }
 
 // 32 keys of one row: P = exp2(s * scale - ref) as bfloat16 into the row's four 16-byte chunks; returns their sum.
@@ -305,15 +309,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float ref = m == -INFINITY ? 0.f : m * scale_log2;
             float sum;
             if (mask) {
-                sum = row_exp<true>(s0, 0, visible, scale_log2, ref, p_tile, r);
-                sum += row_exp<true>(s1, 32, visible, scale_log2, ref, p_tile, r);
-                sum += row_exp<true>(s2, 64, visible, scale_log2, ref, p_tile, r);
-                sum += row_exp<true>(s3, 96, visible, scale_log2, ref, p_tile, r);
+                sum = (row_exp<true>(s0, 0, visible, scale_log2, ref, p_tile, r) +
+                       row_exp<true>(s1, 32, visible, scale_log2, ref, p_tile, r)) +
+                      (row_exp<true>(s2, 64, visible, scale_log2, ref, p_tile, r) +
+                       row_exp<true>(s3, 96, visible, scale_log2, ref, p_tile, r));
             } else {
-                sum = row_exp<false>(s0, 0, visible, scale_log2, ref, p_tile, r);
-                sum += row_exp<false>(s1, 32, visible, scale_log2, ref, p_tile, r);
-                sum += row_exp<false>(s2, 64, visible, scale_log2, ref, p_tile, r);
-                sum += row_exp<false>(s3, 96, visible, scale_log2, ref, p_tile, r);
+                sum = (row_exp<false>(s0, 0, visible, scale_log2, ref, p_tile, r) +
+                       row_exp<false>(s1, 32, visible, scale_log2, ref, p_tile, r)) +
+                      (row_exp<false>(s2, 64, visible, scale_log2, ref, p_tile, r) +
+                       row_exp<false>(s3, 96, visible, scale_log2, ref, p_tile, r));
             }
             l = l * corr + sum;
             // P written (and O rescaled): tell the MMA warp

@@ -144,43 +144,73 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         share[0] = csum;
     }
     {
-        // An item is 32 consecutive rows of the tile for one token.  A warp takes its items four at a
-        // time: first every load of the four (the slices' sums, and the old values where the product is
-        // added to memory), then the arithmetic and the stores - so four round trips overlap.
-        constexpr int CH = 4, WARPS_ALL = THREADS / 32;
-        const int items = (BM / 32) * M;
-        for (int it0 = slice + slices * warp; it0 < items; it0 += CH * slices * WARPS_ALL) {
-            float part[CH][8], old[CH];
+        // An item is the tile's 128 rows for one token, four consecutive rows per lane (16-byte reads
+        // through distributed shared memory, 16-byte stores).  A warp takes its items two at a time:
+        // first every load of both (the slices' sums, and the old values where the product is added
+        // to memory), then the arithmetic and the stores - so the round trips overlap.
+        constexpr int CH = 2, WARPS_ALL = THREADS / 32;
+        const int r = 4 * lane, n = n0 + r;
+        const bool vec_ok = n + 3 < N && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0;   // else one by one
+        for (int m0 = slice + slices * warp; m0 < M; m0 += CH * slices * WARPS_ALL) {
+            float4 part[CH][8], old[CH];
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
-                const int it = it0 + c * slices * WARPS_ALL;
-                const int u = it % (BM / 32), m = it / (BM / 32);
-                const int r = u * 32 + lane, n = n0 + r;
+                const int m = m0 + c * slices * WARPS_ALL;
 #pragma unroll
-                for (int s = 0; s < 8; ++s) part[c][s] = (it < items && s < slices) ? share[s][m * BM + r] : 0.f;
-                old[c] = (mode == 2 && it < items && n < N) ? ((const float*)out)[(size_t)m * ldo + n] : 0.f;
+                for (int s = 0; s < 8; ++s)
+                    part[c][s] = (m < M && s < slices) ? *reinterpret_cast<const float4*>(share[s] + m * BM + r)
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                old[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (mode == 2 && m < M) {
+                    const float* o = (const float*)out + (size_t)m * ldo + n;
+                    if (vec_ok) old[c] = *reinterpret_cast<const float4*>(o);
+                    else {
+                        if (n < N) old[c].x = o[0];
+                        if (n + 1 < N) old[c].y = o[1];
+                        if (n + 2 < N) old[c].z = o[2];
+                        if (n + 3 < N) old[c].w = o[3];
+                    }
+                }
             }
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
-                const int it = it0 + c * slices * WARPS_ALL;
-                if (it >= items) break;
-                const int u = it % (BM / 32), m = it / (BM / 32);
-                const int r = u * 32 + lane, n = n0 + r;
-                float v = 0.f;
+                const int m = m0 + c * slices * WARPS_ALL;
+                if (m >= M) break;
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int s = 0; s < 8; ++s) v += part[c][s];
-                if (bias && n < N) v += bias[n];
+                for (int s = 0; s < 8; ++s) {
+                    v[0] += part[c][s].x; v[1] += part[c][s].y; v[2] += part[c][s].z; v[3] += part[c][s].w;
+                }
+                if (bias) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (n + e < N) v[e] += bias[n + e];
+                }
                 if (mode == 3) {
-                    // lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same features
-                    const float up = __shfl_down_sync(0xffffffffu, v, 16);
-                    if (lane < 16 && n + 16 < N)
-                        ((__nv_bfloat16*)out)[(size_t)m * ldo + (n >> 5) * 16 + lane] =
-                            __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
-                } else if (n < N) {
+                    // rows in groups of 16 gate + 16 up: of every 8 lanes the first 4 hold gate rows,
+                    // the next 4 the up rows of the same features
+                    float up[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) up[e] = __shfl_down_sync(0xffffffffu, v[e], 4);
+                    if ((lane & 4) == 0 && n + 16 < N) {
+                        __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)m * ldo + (n >> 5) * 16 + (r & 15);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) o[e] = __float2bfloat16_rn(v[e] / (1.0f + expf(-v[e])) * up[e]);
+                    }
+                } else {
                     const size_t o = (size_t)m * ldo + n;
-                    if (mode == 0) ((float*)out)[o] = v;
-                    else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-                    else ((float*)out)[o] = old[c] + v;
+                    if (mode == 2) { v[0] += old[c].x; v[1] += old[c].y; v[2] += old[c].z; v[3] += old[c].w; }
+                    if (mode == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (n + e < N) ((__nv_bfloat16*)out)[o + e] = __float2bfloat16_rn(v[e]);
+                    } else if (vec_ok) {
+                        *reinterpret_cast<float4*>((float*)out + o) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (n + e < N) ((float*)out)[o + e] = v[e];
+                    }
                 }
             }
         }

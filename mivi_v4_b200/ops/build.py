@@ -29,7 +29,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "gemm_simt.cu", "shortconv.cu", "attention.cu", "attention_decode.cu",
              "sampling.cu"],
     "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_swap.cu", "attention_prefill.cu",
-             "attention_prefill_tc.cu"],
+             "attention_prefill_tc.cu", "attention_decode_tc.cu"],
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

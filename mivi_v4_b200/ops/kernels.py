@@ -47,6 +47,7 @@ _SIGNATURES = {
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
     },
 }
@@ -491,6 +492,41 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, page_table, positions,
         _need(out, "attention out", None, (N, nh * hd)), _dt(q), part_o.data_ptr(), part_ml.data_ptr(),
         tickets.data_ptr(), N, nh, nkv, hd, float(scale), int(window), splits, gt, head_tiles, _stream()),
         "mv_attention_decode")
+    return out
+
+
+def attention_decode_tc_plan(N: int, nkv: int, context_cap: int) -> int:
+    """Key splits for the tcgen05 decode attention: about two blocks for each of the GPU's
+    multiprocessors twice over, at least two key blocks of 128 a split.  Like
+    ``attention_decode_plan`` it depends on the page table's reach, not on the lengths."""
+    blocks = max(1, -(-context_cap // 128))
+    want = -(-4 * N_SMS // max(1, N * nkv))
+    return max(1, min(64, want, blocks // 2))
+
+
+def attention_decode_tc(q: torch.Tensor, pool: torch.Tensor, page_table, positions, seq_of, out: torch.Tensor,
+                        nh: int, nkv: int, hd: int, scale: float, ws, splits: Optional[int] = None):
+    """Attention of single query tokens over long caches, both products on tcgen05 (bfloat16,
+    head size 64, pages of 64 tokens, no window).  Same arguments and result as
+    :func:`attention_decode`."""
+    N = q.shape[0]
+    if not attention_prefill_tc_supported(q.dtype, hd, pool, 0) or nh % nkv or nh // nkv > 128:
+        raise KernelError(f"attention_decode_tc: needs bfloat16, head size 64, a dense pool of 64-token pages and "
+                          f"at most 128 heads a kv head, got {q.dtype}, {hd}, pool {tuple(pool.shape)}, {nh}/{nkv}")
+    _check_kv(pool, nkv, hd, 64, "attention")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    splits = attention_decode_tc_plan(N, nkv, page_table.shape[1] * 64) if splits is None else int(splits)
+    part_o = ws.get("attn_part_o", (N * nh * splits * hd,), torch.float32)
+    part_ml = ws.get("attn_part_ml", (N * nh * splits * 2,), torch.float32)
+    _check(_fn("bf16", "mv_attention_decode_tc")(
+        _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.shape[0] * 2 * nkv * 64,
+        _need(page_table, "page table", torch.int32), page_table.shape[1],
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(out, "attention out", None, (N, nh * hd)), part_o.data_ptr(), part_ml.data_ptr(), N, nh, nkv,
+        float(scale), splits, _error_flag(q.device).data_ptr(), _stream()), "mv_attention_decode_tc")
+    if splits > 1:
+        add_launches(1)                    # the kernel that merges the splits
     return out
 
 

@@ -144,7 +144,7 @@ def prefill_step(a) -> int:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mivi_v4_b200.ops.probe")
     ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc_swap", "gemm_tc", "attention_decode", "attention_prefill",
-                                      "attention_prefill_tc",
+                                      "attention_prefill_tc", "attention_decode_tc",
                                        "decode_step", "prefill_step"])
     ap.add_argument("--config", default=None, help="config.json for decode_step (default: bench.py's)")
     ap.add_argument("--prompt", type=int, default=512)
@@ -213,7 +213,7 @@ def main(argv=None) -> int:
     def ints(v):
         return torch.tensor(v, dtype=torch.int32, device=dev)
 
-    if a.kernel == "attention_decode":
+    if a.kernel in ("attention_decode", "attention_decode_tc"):
         B = a.batch
         lengths = [a.context + i for i in range(B)]
         pool, table = cache(lengths)
@@ -221,11 +221,15 @@ def main(argv=None) -> int:
         out = torch.empty_like(q)
         ws = Workspace(dev)
         seq_of, positions = ints(list(range(B))), ints([n - 1 for n in lengths])
-        run = lambda: K.attention_decode(q, pool, table, positions, seq_of, out, nh, nkv, hd, scale, 0, ws)
+        if a.kernel == "attention_decode_tc":
+            run = lambda: K.attention_decode_tc(q, pool, table, positions, seq_of, out, nh, nkv, hd, scale, ws)
+        else:
+            run = lambda: K.attention_decode(q, pool, table, positions, seq_of, out, nh, nkv, hd, scale, 0, ws)
         run()
         us = _timed([run], a.reps)
         kv_bytes = sum(lengths) * nkv * hd * 2 * 2
-        print(f"attention_decode batch={B} context={a.context}: {us:.2f} us, cache at {kv_bytes / us / 1e3:.0f} GB/s")
+        K.check_device_errors()
+        print(f"{a.kernel} batch={B} context={a.context}: {us:.2f} us, cache at {kv_bytes / us / 1e3:.0f} GB/s")
     else:
         T = a.tokens
         pool, table = cache([T])

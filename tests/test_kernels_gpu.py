@@ -429,6 +429,35 @@ def test_attention_prefill_tc(nh, nkv):
     assert not torch.isnan(out.float()).any()
 
 
+@pytest.mark.parametrize("splits", [None, 1, 3, 7])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (3, 1), (5, 5), (12, 2)])
+def test_attention_decode_tc(nh, nkv, splits):
+    """The tcgen05 decode kernel (head size 64, pages of 64): single tokens at the end and in the
+    middle of caches of many lengths, any number of key splits, with one far key that stands out."""
+    from mivi_v4_b200.engine.step import Workspace
+    dtype, hd, page = torch.bfloat16, 64, 64
+    lengths = [1, 33, 300, 64, 129, 1000, 128, 2500]
+    pool, table, dense = build_cache(lengths, nkv, hd, page, dtype, seed=nh + 1)
+    queries = [(b, n - 1) for b, n in enumerate(lengths)] + [(2, 0), (2, 127), (2, 128), (5, 511), (7, 1300)]
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(len(queries), nh, hd, generator=g)
+    for row, far in ((5, 7), (7, 1900)):                     # sequences 5 and 7, last position
+        kf = dense[queries[row][0]][0][far, 0].float()
+        q[row, 0] = kf / kf.norm() * 6.0 * (hd ** 0.25)
+    q = q.to(dtype)
+    N = len(queries)
+    out = torch.full((N, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    K().attention_decode_tc(q.reshape(N, nh * hd).contiguous().to(DEV), pool, table, ints([p for _, p in queries]),
+                            ints([b for b, _ in queries]), out, nh, nkv, hd, scale, Workspace(DEV), splits=splits)
+    K().check_device_errors()
+    assert not torch.isnan(out.float()).any()
+    for i, (b, pos) in enumerate(queries):
+        want = plain_attend(q[i], dense[b][0], dense[b][1], pos, nh, nkv, scale, 0)
+        got = out[i].reshape(nh, hd).double().cpu()
+        assert torch.allclose(got, want, rtol=1.5e-2, atol=1.5e-2), (i, b, pos, (got - want).abs().max())
+
+
 def grouped(w1, w3, G=16):
     F, H = w1.shape
     return torch.stack([w1.view(F // G, G, H), w3.view(F // G, G, H)], dim=1).reshape(2 * F, H).contiguous()
