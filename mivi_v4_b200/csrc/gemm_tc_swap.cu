@@ -224,6 +224,16 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
+// Slices of K (at most 8, the portable cluster size): as many blocks as fit the GPU at two a
+// multiprocessor, each with at least two K blocks.
+int k_slices(int N, int K) {
+    const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
+    int slices = 2 * 148 / tiles;
+    slices = slices >= 8 ? 8 : (slices >= 4 ? 4 : (slices >= 2 ? 2 : 1));   // clusters of other sizes schedule worse
+    while (slices > 1 && kblocks / slices < 2) slices >>= 1;
+    return slices < 1 ? 1 : slices;
+}
+
 template <int BN, int STAGES>
 int launch(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
            int* err, cudaStream_t stream) {
@@ -236,13 +246,7 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
         attr_set = true;
     }
     const int tiles = (N + BM - 1) / BM;
-    const int kblocks = (K + BK - 1) / BK;
-    // slices of K (at most 8, the portable cluster size): as many blocks as fit the GPU at one a
-    // multiprocessor, each with at least two K blocks
-    int slices = 148 / tiles;
-    slices = slices > 8 ? 8 : slices;
-    while (slices > 1 && kblocks / slices < 2) --slices;
-    if (slices < 1) slices = 1;
+    const int slices = k_slices(N, K);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(slices, tiles);
     cfg.blockDim = dim3(THREADS);
@@ -268,7 +272,14 @@ MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
-    if (M <= 16) return launch<16, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
-    if (M <= 32) return launch<32, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
-    return launch<64, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    // A ring of 8 stages fills a multiprocessor's shared memory with one block.  Clusters of such
+    // blocks need 8 free multiprocessors in one GPC each, and only 15 fit the GPU at a time: a
+    // product that is cut along K takes 4 stages, so that two blocks share a multiprocessor.
+    const bool deep = k_slices(N, K) == 1;
+#define MV_GO(BN) return deep ? launch<BN, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream) \
+                              : launch<BN, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream)
+    if (M <= 16) MV_GO(16);
+    if (M <= 32) MV_GO(32);
+    MV_GO(64);
+#undef MV_GO
 }
