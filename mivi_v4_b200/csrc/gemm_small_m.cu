@@ -40,16 +40,16 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int PART_STRIDE = 64;        // tile sums are laid out [tile][64 tokens]
 
 // The two optional ends of a norm carried by products (all null / 0 when unused).
 struct NormLink {
-    const float* scale_part;           // consumer: [n_scale_part][64] sums of squares of the rows it reads
-    int n_scale_part;
+    const float* scale_part;           // consumer: [tokens][scale_stride], n_scale_part sums of squares per row it reads
+    int n_scale_part, scale_stride;
     float inv_dim, eps;
     const float* emit_g;               // producer (mode 2): the next norm's weight [N]
     __nv_bfloat16* emit_x;             // bf16(x_new * g) [M, N]
-    float* emit_part;                  // [tiles][64] sums of x_new^2 over each tile's rows
+    float* emit_part;                  // [tokens][emit_stride] sums of x_new^2 over each tile's rows
+    int emit_stride;
 };
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
@@ -200,7 +200,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         for (int s = 0; s < 8; ++s) v += part[s];
         if (link.scale_part) {
             float ss = 0.f;
-            for (int p = lane; p < link.n_scale_part; p += 32) ss += link.scale_part[p * PART_STRIDE + m];
+            for (int p = lane; p < link.n_scale_part; p += 32) ss += link.scale_part[(size_t)m * link.scale_stride + p];
             ss = mv_warp_sum(ss);
             v *= 1.0f / sqrtf(ss * link.inv_dim + link.eps);
         }
@@ -228,7 +228,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
             }
             if (mode == 2 && link.emit_x) {
                 sq = mv_warp_sum(sq);
-                if (lane == 0) link.emit_part[(size_t)blockIdx.y * PART_STRIDE + m] = sq;
+                if (lane == 0) link.emit_part[(size_t)m * link.emit_stride + blockIdx.y] = sq;
             }
         }
     }
@@ -289,22 +289,26 @@ MV_API int mv_gemm_small_m_tile_rows(int N, int mode) { return (N >= 32 * 2 * 14
 // mode: 0 store float32, 1 store bfloat16, 2 add into float32, 3 SwiGLU (W rows in
 // groups of 16 gate + 16 up; out is bfloat16 [M, N/2] with row stride ldo).  Needs
 // 1 <= M <= 64, K a multiple of 8, and 16-byte aligned operands.
-// scale_part (or null): [n_scale_part][64] sums of squares; every token's results are multiplied
-// by rsqrt(sum / dim + eps) before bias and activation.  emit_x (or null, mode 2 only, ldo == N):
-// receives bf16(out_new * emit_g), and emit_part [tiles][64] the sums of out_new^2 per tile of
-// mv_gemm_small_m_tile_rows(N, 2) rows.
+// scale_part (or null): [M][scale_stride] of which n_scale_part sums of squares per token; every token's
+// results are multiplied by rsqrt(sum / dim + eps) before bias and activation.  emit_x (or null, mode 2
+// only, ldo == N): receives bf16(out_new * emit_g), and emit_part [M][emit_stride] the sums of out_new^2
+// per tile of mv_gemm_small_m_tile_rows(N, 2) rows.
 MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void* out, int mode, int M,
-                           int N, int K, int ldo, const float* scale_part, int n_scale_part, int dim, float eps,
-                           const float* emit_g, void* emit_x, float* emit_part, cudaStream_t stream) {
+                           int N, int K, int ldo, const float* scale_part, int n_scale_part, int scale_stride,
+                           int dim, float eps, const float* emit_g, void* emit_x, float* emit_part,
+                           int emit_stride, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
-    if (emit_x && (mode != 2 || ldo != N || !emit_g || !emit_part)) return (int)cudaErrorInvalidValue;
-    if (scale_part && (n_scale_part <= 0 || dim <= 0)) return (int)cudaErrorInvalidValue;
+    if (emit_x && (mode != 2 || ldo != N || !emit_g || !emit_part ||
+                   emit_stride < (N + mv_gemm_small_m_tile_rows(N, 2) - 1) / mv_gemm_small_m_tile_rows(N, 2)))
+        return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
     NormLink link = {};
     if (scale_part) {
         link.scale_part = scale_part;
         link.n_scale_part = n_scale_part;
+        link.scale_stride = scale_stride;
         link.inv_dim = 1.0f / (float)dim;
         link.eps = eps;
     }
@@ -312,6 +316,7 @@ MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void
         link.emit_g = emit_g;
         link.emit_x = (__nv_bfloat16*)emit_x;
         link.emit_part = emit_part;
+        link.emit_stride = emit_stride;
     }
     const int nt = (M + 7) / 8;
     const bool wide = mv_gemm_small_m_tile_rows(N, mode) == 32;

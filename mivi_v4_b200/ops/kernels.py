@@ -42,7 +42,7 @@ _SIGNATURES = {
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P],
     },
     "bf16": {
-        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _P],
+        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P],
         "mv_gemm_small_m_tile_rows": [_I, _I],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -185,7 +185,6 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Opti
 SMALL_M_MAX = 64
 
 
-NORM_PART_STRIDE = 64              # tile sums of a carried norm are laid out [tile][64 tokens]
 
 
 @dataclass
@@ -200,7 +199,7 @@ class NormLink:
     eps: float
     dim: int
     xg: torch.Tensor               # bfloat16 [tokens, dim]
-    partials: torch.Tensor         # float32 [>= ceil(dim / 16), 64]
+    partials: torch.Tensor         # float32 [tokens, >= ceil(dim / 16)]: the tile sums of one token lie together
     n_partials: int = 0            # set by the emitting product
 
 
@@ -235,28 +234,37 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
         mode = 0 if out.dtype == torch.float32 else 1
         _need(out, "gemm out", None, (M, N))
         _dt(out)
-    sp, n_sp, dim, eps, eg, ex, ep = None, 0, 0, 0.0, None, None, None
+    link = _link_args(x, M, N, K, mode, scale, emit, -(-N // gemm_small_m_tile_rows(N, 2)))
+    _check(_fn("bf16", "mv_gemm_small_m")(
+        _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
+        out.data_ptr(), mode, M, N, K, ldo, *link, _stream()), "mv_gemm_small_m")
+    return out
+
+
+def _link_args(x, M: int, N: int, K: int, mode: int, scale: Optional[NormLink], emit: Optional[NormLink],
+               tiles: int):
+    """The nine arguments that carry a norm through a product: (partials, count, stride, dim, eps)
+    of the link it consumes and (weight, rows, partials, stride) of the link it emits, which
+    writes ``tiles`` sums a row."""
+    sp, n_sp, s_stride, dim, eps, eg, ex, ep, e_stride = None, 0, 0, 0, 0.0, None, None, None, 0
     if scale is not None:
         if scale.n_partials <= 0 or scale.dim != K or x.data_ptr() != scale.xg.data_ptr():
-            raise KernelError("gemm_small_m: the scaled input must be the rows that the norm link's producer wrote")
+            raise KernelError("gemm: the scaled input must be the rows that the norm link's producer wrote")
         _need(scale.partials, "norm partials", torch.float32)
-        sp, n_sp, dim, eps = scale.partials.data_ptr(), scale.n_partials, scale.dim, float(scale.eps)
+        sp, n_sp, s_stride = scale.partials.data_ptr(), scale.n_partials, scale.partials.shape[1]
+        dim, eps = scale.dim, float(scale.eps)
     if emit is not None:
-        tiles = -(-N // gemm_small_m_tile_rows(N, 2))
         if mode != 2 or emit.dim != N:
-            raise KernelError("gemm_small_m: only a product that adds into the residual stream can emit a norm")
+            raise KernelError("gemm: only a product that adds into the residual stream can emit a norm")
         _need(emit.weight, "norm weight", torch.float32, (N,))
         _need(emit.xg, "normed rows", torch.bfloat16, (M, N))
         _need(emit.partials, "norm partials", torch.float32)
-        if emit.partials.numel() < tiles * NORM_PART_STRIDE:
-            raise KernelError(f"gemm_small_m: norm partials hold {emit.partials.numel()} values, {tiles} tiles need "
-                              f"{tiles * NORM_PART_STRIDE}")
-        eg, ex, ep = emit.weight.data_ptr(), emit.xg.data_ptr(), emit.partials.data_ptr()
+        if emit.partials.dim() != 2 or emit.partials.shape[0] < M or emit.partials.shape[1] < tiles:
+            raise KernelError(f"gemm: norm partials [{tuple(emit.partials.shape)}] cannot hold {tiles} tile "
+                              f"sums for each of {M} rows")
+        eg, ex, ep, e_stride = emit.weight.data_ptr(), emit.xg.data_ptr(), emit.partials.data_ptr(), emit.partials.shape[1]
         emit.n_partials = tiles
-    _check(_fn("bf16", "mv_gemm_small_m")(
-        _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, sp, n_sp, dim, eps, eg, ex, ep, _stream()), "mv_gemm_small_m")
-    return out
+    return sp, n_sp, s_stride, dim, eps, eg, ex, ep, e_stride
 
 
 _error_flags = {}

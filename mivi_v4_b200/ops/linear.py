@@ -43,7 +43,9 @@ def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16) -> bool:
     """Whether a product of ``n_rows`` rows with ``w`` takes the kernel that can carry a
-    norm (``scale`` / ``emit`` of :func:`linear`)."""
+    norm (``scale`` / ``emit`` of :func:`linear`): the mma.sync kernel of few rows.  (In the
+    tcgen05 kernel of many rows the epilogue is on the critical path: carrying the norm there
+    measured 8 % slower than the norm kernels it saved.)"""
     return (_small_m(n_rows) is K.gemm_small_m and 1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
             and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
 

@@ -32,4 +32,4 @@ class RMSNorm(Part):
         n = step.n_tokens
         return K.NormLink(self, self.weight, self.eps, self.dim,
                           step.ws.get("link_rows_" + name, (n, self.dim), torch.bfloat16),
-                          step.ws.get("link_sums_" + name, (-(-self.dim // 16), K.NORM_PART_STRIDE), torch.float32))
+                          step.ws.get("link_sums_" + name, (n, -(-self.dim // 64) * 4), torch.float32))

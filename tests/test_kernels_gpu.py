@@ -109,9 +109,10 @@ def test_gemm_small_m(kernel, M, N, Kd):
 
 @pytest.mark.parametrize("M", [1, 5, 8, 17, 64])
 @pytest.mark.parametrize("H,F,swiglu", [(64, 48, False), (200, 96, True), (2048, 160, False), (9600, 64, True)])
-def test_gemm_small_m_carries_a_norm(M, H, F, swiglu):
+def test_gemm_carries_a_norm(M, H, F, swiglu):
     """x_new = x + z Wo^T; y = rmsnorm(x_new) * g, then y W1^T (or its SwiGLU): the first product
     writes the rows bf16(x_new * g) and the tile sums, the second applies the scale."""
+    gemm = K().gemm_small_m
     from mivi_v4_b200.ops.linear import linear
     eps = 1e-5
     z, wo = rnd(M, 72, dtype=torch.bfloat16), rnd(H, 72, dtype=torch.bfloat16, seed=1)
@@ -120,24 +121,25 @@ def test_gemm_small_m_carries_a_norm(M, H, F, swiglu):
     w1 = rnd(2 * F if swiglu else F, H, dtype=torch.bfloat16, seed=4)
     bias = None if swiglu else rnd(F, seed=5)
     link = K().NormLink(None, g, eps, H, torch.empty(M, H, dtype=torch.bfloat16, device=DEV),
-                        torch.full((-(-H // 16), 64), float("nan"), device=DEV))
+                        torch.full((M, -(-H // 64) * 4), float("nan"), device=DEV))
     resid = x.clone()
-    K().gemm_small_m(z, wo, resid, accumulate=True, emit=link)
+    gemm(z, wo, resid, accumulate=True, emit=link)
+    K().check_device_errors()
     x_new = x.double() + z.double() @ wo.double().T
     assert torch.allclose(resid.double(), x_new, rtol=1e-5, atol=1e-4)
     assert link.n_partials == -(-H // (32 if H >= 9472 else 16))
-    ss = link.partials[:link.n_partials, :M].double().sum(0)
+    ss = link.partials[:, :link.n_partials].double().sum(1)
     assert torch.allclose(ss, (x_new ** 2).sum(1), rtol=1e-5)
     y = P.plain_rms_norm(x_new, g.double(), eps)
     if swiglu:
         out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
-        K().gemm_small_m(link.xg, w1, out, swiglu=True, scale=link)
+        gemm(link.xg, w1, out, swiglu=True, scale=link)
         gu = (y @ w1.double().T).view(M, F // 16, 2, 16)
         a, b = gu[:, :, 0].reshape(M, F), gu[:, :, 1].reshape(M, F)
         want = a / (1 + torch.exp(-a)) * b
     else:
         out = torch.empty(M, F, device=DEV)
-        K().gemm_small_m(link.xg, w1, out, bias=bias, scale=link)
+        gemm(link.xg, w1, out, bias=bias, scale=link)
         want = y @ w1.double().T + bias.double()
     # rounding x_new * g to bfloat16 moves a dot product of H terms by about 2^-9 sqrt(H) (3 sigma: delta);
     # silu(a) b moves by about (|a| + |b|) delta
