@@ -154,6 +154,24 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     // this kernel that have not started yet.)
     mv_pdl_launch_dependents();
 
+    // What the epilogue's first item (most warps have at most one) will want from global memory is asked
+    // for now and not touched until then: the answers arrive while the sums go through shared memory
+    // and the cluster barrier.
+    const int m_first = slice + slices * warp;
+    const int n_lane = n0 + lane;
+    const bool lane_ok = lane < ROWS && n_lane < N;
+    float early_old = 0.f, early_g = 0.f, early_part[4] = {0.f, 0.f, 0.f, 0.f};
+    if (m_first < M) {
+        if (mode == 2 && lane_ok) early_old = ((const float*)out)[(size_t)m_first * ldo + n_lane];
+        if (link.scale_part) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (lane + 32 * e < link.n_scale_part)
+                    early_part[e] = link.scale_part[(size_t)m_first * link.scale_stride + lane + 32 * e];
+        }
+    }
+    if (link.emit_x && lane_ok) early_g = link.emit_g[n_lane];
+
     // the warps' partial sums -> shared memory -> their sum in warp order
     float* mine = red + (size_t)warp * ROWS * LDR;
 #pragma unroll
@@ -200,7 +218,19 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         for (int s = 0; s < 8; ++s) v += part[s];
         if (link.scale_part) {
             float ss = 0.f;
-            for (int p = lane; p < link.n_scale_part; p += 32) ss += link.scale_part[(size_t)m * link.scale_stride + p];
+            if (m == m_first) {
+                ss = (early_part[0] + early_part[1]) + (early_part[2] + early_part[3]);
+                for (int p = lane + 128; p < link.n_scale_part; p += 32)
+                    ss += link.scale_part[(size_t)m * link.scale_stride + p];
+            } else {
+                float e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (lane + 32 * k < link.n_scale_part) e[k] = link.scale_part[(size_t)m * link.scale_stride + lane + 32 * k];
+                ss = (e[0] + e[1]) + (e[2] + e[3]);
+                for (int p = lane + 128; p < link.n_scale_part; p += 32)
+                    ss += link.scale_part[(size_t)m * link.scale_stride + p];
+            }
             ss = mv_warp_sum(ss);
             v *= 1.0f / sqrtf(ss * link.inv_dim + link.eps);
         }
@@ -218,10 +248,10 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
                 if (mode == 0) ((float*)out)[o] = v;
                 else if (mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
                 else {
-                    const float x_new = ((float*)out)[o] + v;
+                    const float x_new = (m == m_first ? early_old : ((float*)out)[o]) + v;
                     ((float*)out)[o] = x_new;
                     if (link.emit_x) {
-                        link.emit_x[(size_t)m * N + n] = __float2bfloat16_rn(x_new * link.emit_g[n]);
+                        link.emit_x[(size_t)m * N + n] = __float2bfloat16_rn(x_new * early_g);
                         sq = x_new * x_new;
                     }
                 }
