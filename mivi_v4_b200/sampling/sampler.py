@@ -26,6 +26,10 @@ class Sampler:
         self._bufs = {}
         self._pinned = {}
         self._events = {}
+        self._done = {}
+        # the sampled tokens go to the host on a stream of their own: the step after this one does not
+        # wait behind the copy
+        self._copy_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         from ..engine.step import Workspace
         self._ws = Workspace(self.device)
 
@@ -42,18 +46,22 @@ class Sampler:
                     torch.empty((max(B, 1),), dtype=torch.int32, device=self.device))
             self._bufs[slot] = bufs
         work, out_all = bufs
-        meta: List[int] = [int(s) & 0x7fffffff for s in streams] + [int(s) for s in steps]
         use_pen = p.uses_penalties and any(len(r) for r in recent)
-        if use_pen:
-            meta += [min(len(r), RECENT_TOKENS_WINDOW) for r in recent]
-            for r in recent:
-                r = list(r)[-RECENT_TOKENS_WINDOW:]
-                meta += r + [0] * (RECENT_TOKENS_WINDOW - len(r))
-        m = self._ws.stage(f"sample_meta{slot}", meta)
-        streams_d, steps_d = m[:B], m[B:2 * B]
-        n_recent_d = m[2 * B:3 * B] if use_pen else None
-        recent_d = m[3 * B:].view(B, RECENT_TOKENS_WINDOW) if use_pen else None
         out = out_all[:B]
+        if p.temperature <= 0.0 and not use_pen:
+            # the largest logit: no draw, so no stream and step numbers to send up
+            streams_d = steps_d = n_recent_d = recent_d = None
+        else:
+            meta: List[int] = [int(s) & 0x7fffffff for s in streams] + [int(s) for s in steps]
+            if use_pen:
+                meta += [min(len(r), RECENT_TOKENS_WINDOW) for r in recent]
+                for r in recent:
+                    r = list(r)[-RECENT_TOKENS_WINDOW:]
+                    meta += r + [0] * (RECENT_TOKENS_WINDOW - len(r))
+            m = self._ws.stage(f"sample_meta{slot}", meta)
+            streams_d, steps_d = m[:B], m[B:2 * B]
+            n_recent_d = m[2 * B:3 * B] if use_pen else None
+            recent_d = m[3 * B:].view(B, RECENT_TOKENS_WINDOW) if use_pen else None
         K.sample(logits, work, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                  min_p=p.min_p, repetition_penalty=p.repetition_penalty, presence_penalty=p.presence_penalty,
                  frequency_penalty=p.frequency_penalty, recent=recent_d, n_recent=n_recent_d, seed=self.seed,
@@ -69,9 +77,17 @@ class Sampler:
             pinned = torch.empty(max(B, 64), dtype=torch.int32).pin_memory()
             self._pinned[slot] = pinned
         host = pinned[:B]
-        host.copy_(out, non_blocking=True)
         event = self._events.setdefault(slot, torch.cuda.Event())
-        event.record()
+        if self._copy_stream is None:
+            host.copy_(out, non_blocking=True)
+            event.record()
+            return host, event
+        done = self._done.setdefault(slot, torch.cuda.Event())
+        done.record()                                   # the sampling kernel, on the launching stream
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(done)
+            host.copy_(out, non_blocking=True)
+            event.record()
         return host, event
 
     def sample(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
