@@ -25,6 +25,17 @@ namespace {
 
 constexpr int THREADS = 192;
 
+// The two optional ends of a norm carried by products (see gemm_small_m.cu; all null / 0 when unused).
+struct NormLink {
+    const float* scale_part;           // consumer: [tokens][scale_stride], n_scale_part sums of squares per row it reads
+    int n_scale_part, scale_stride;
+    float inv_dim, eps;
+    const float* emit_g;               // producer (mode 2): the next norm's weight [N]
+    __nv_bfloat16* emit_x;             // bf16(x_new * g) [M, N]
+    float* emit_part;                  // [tokens][emit_stride] sums of x_new^2 over each tile's 128 rows
+    int emit_stride;
+};
+
 template <int BN, int STAGES>
 struct SwapLayout {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -40,7 +51,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
-                    int* __restrict__ err) {
+                    const NormLink link, int* __restrict__ err) {
     using L = SwapLayout<BN, STAGES>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -153,9 +164,15 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const bool vec_ok = n + 3 < N && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0;   // else one by one
         for (int m0 = slice + slices * warp; m0 < M; m0 += CH * slices * WARPS_ALL) {
             float4 part[CH][8], old[CH];
+            float ss[CH];
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
                 const int m = m0 + c * slices * WARPS_ALL;
+                // a carried norm's sums of this token: lane p holds sums p, p + 32, ...
+                ss[c] = 0.f;
+                if (link.scale_part && m < M)
+                    for (int p = lane; p < link.n_scale_part; p += 32)
+                        ss[c] += link.scale_part[(size_t)m * link.scale_stride + p];
 #pragma unroll
                 for (int s = 0; s < 8; ++s)
                     part[c][s] = (m < M && s < slices) ? *reinterpret_cast<const float4*>(share[s] + m * BM + r)
@@ -180,6 +197,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                 for (int s = 0; s < 8; ++s) {
                     v[0] += part[c][s].x; v[1] += part[c][s].y; v[2] += part[c][s].z; v[3] += part[c][s].w;
+                }
+                if (link.scale_part) {
+                    const float sc = 1.0f / sqrtf(mv_warp_sum(ss[c]) * link.inv_dim + link.eps);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] *= sc;
                 }
                 if (bias) {
 #pragma unroll
@@ -211,6 +233,18 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         for (int e = 0; e < 4; ++e)
                             if (n + e < N) ((float*)out)[o + e] = v[e];
                     }
+                    if (mode == 2 && link.emit_x) {
+                        // the next norm's rows and this tile's share of the token's sum of squares
+                        float sq = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (n + e < N) {
+                                link.emit_x[(size_t)m * N + n + e] = __float2bfloat16_rn(v[e] * link.emit_g[n + e]);
+                                sq = fmaf(v[e], v[e], sq);
+                            }
+                        sq = mv_warp_sum(sq);
+                        if (lane == 0) link.emit_part[(size_t)m * link.emit_stride + blockIdx.y] = sq;
+                    }
                 }
             }
         }
@@ -236,7 +270,7 @@ int k_slices(int N, int K) {
 
 template <int BN, int STAGES>
 int launch(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-           int* err, cudaStream_t stream) {
+           const NormLink& link, int* err, cudaStream_t stream) {
     using L = SwapLayout<BN, STAGES>;
     CUtensorMap mw, mx;
     if (!tensor_map(W, N, K, BM, &mw) || !tensor_map(X, M, K, BN, &mx)) return (int)cudaErrorInvalidValue;
@@ -259,25 +293,45 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = slices > 1 ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, gemm_tc_swap_kernel<BN, STAGES>, mw, mx, bias, out, mode, M, N, K, ldo, err);
+    cudaLaunchKernelEx(&cfg, gemm_tc_swap_kernel<BN, STAGES>, mw, mx, bias, out, mode, M, N, K, ldo, link, err);
     return mv_launch_status();
 }
 
 }  // namespace
 
 // Same contract as mv_gemm_small_m (modes 0-3, 1 <= M <= 64, K a multiple of 8,
-// 16-byte aligned operands), plus the error flag of the bounded waits.
+// 16-byte aligned operands; scale_part / emit_x as there, with one sum per tile of 128 rows), plus
+// the error flag of the bounded waits.
 MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
-                           int K, int ldo, int* err, cudaStream_t stream) {
+                           int K, int ldo, const float* scale_part, int n_scale_part, int scale_stride, int dim,
+                           float eps, const float* emit_g, void* emit_x, float* emit_part, int emit_stride,
+                           int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
+    if (emit_x && (mode != 2 || ldo != N || !emit_g || !emit_part || emit_stride < (N + BM - 1) / BM))
+        return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
+    NormLink link = {};
+    if (scale_part) {
+        link.scale_part = scale_part;
+        link.n_scale_part = n_scale_part;
+        link.scale_stride = scale_stride;
+        link.inv_dim = 1.0f / (float)dim;
+        link.eps = eps;
+    }
+    if (emit_x) {
+        link.emit_g = emit_g;
+        link.emit_x = (__nv_bfloat16*)emit_x;
+        link.emit_part = emit_part;
+        link.emit_stride = emit_stride;
+    }
     // A ring of 8 stages fills a multiprocessor's shared memory with one block.  Clusters of such
     // blocks need 8 free multiprocessors in one GPC each, and only 15 fit the GPU at a time: a
     // product that is cut along K takes 4 stages, so that two blocks share a multiprocessor.
     const bool deep = k_slices(N, K) == 1;
-#define MV_GO(BN) return deep ? launch<BN, 8>(X, W, bias, out, mode, M, N, K, ldo, err, stream) \
-                              : launch<BN, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream)
+#define MV_GO(BN) return deep ? launch<BN, 8>(X, W, bias, out, mode, M, N, K, ldo, link, err, stream) \
+                              : launch<BN, 4>(X, W, bias, out, mode, M, N, K, ldo, link, err, stream)
     if (M <= 16) MV_GO(16);
     if (M <= 32) MV_GO(32);
     MV_GO(64);

@@ -80,9 +80,10 @@ class Workspace:
         return dst
 
 
-# Steps in which the products around a norm carry it: those of the mma.sync kernel of few rows.  Measured
-# on the 1.2B-parameter shape: 8 % faster at 8 tokens (0.85 -> 0.79 ms a step).
-CARRY_NORMS_MAX_TOKENS = 8
+# Steps in which the products around a norm carry it: those of at most 64 tokens, whose products run on
+# the two weight-streaming kernels.  Measured on the 1.2B-parameter shape: 0.85 -> 0.79 ms a step at 8
+# tokens.
+CARRY_NORMS_MAX_TOKENS = 64
 
 
 class StepContext:

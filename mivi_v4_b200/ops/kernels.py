@@ -45,7 +45,7 @@ _SIGNATURES = {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P],
         "mv_gemm_small_m_tile_rows": [_I, _I],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-        "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
@@ -321,7 +321,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
 
 
 def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-                 accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+                 accumulate: bool = False, swiglu: bool = False, scale: Optional[NormLink] = None,
+                 emit: Optional[NormLink] = None) -> torch.Tensor:
     """out = x @ w.T for at most 64 rows of x on the tcgen05 tensor cores with the
     operands' roles swapped (rows of w on the MMA's M side): a TMA pipeline that
     streams w once.  Same contract as ``gemm_small_m``."""
@@ -346,9 +347,10 @@ def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
         mode = 0 if out.dtype == torch.float32 else 1
         _need(out, "gemm out", None, (M, N))
         _dt(out)
+    link = _link_args(x, M, N, K, mode, scale, emit, -(-N // 128))
     _check(_fn("bf16", "mv_gemm_tc_swap")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_swap")
+        out.data_ptr(), mode, M, N, K, ldo, *link, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_swap")
     return out
 
 

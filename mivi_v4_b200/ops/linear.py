@@ -42,11 +42,11 @@ def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16) -> bool:
-    """Whether a product of ``n_rows`` rows with ``w`` takes the kernel that can carry a
-    norm (``scale`` / ``emit`` of :func:`linear`): the mma.sync kernel of few rows.  (In the
-    tcgen05 kernel of many rows the epilogue is on the critical path: carrying the norm there
+    """Whether a product of ``n_rows`` rows with ``w`` takes a kernel that can carry a
+    norm (``scale`` / ``emit`` of :func:`linear`): one of the two of at most 64 rows.  (In the
+    tcgen05 kernel of more rows the epilogue is on the critical path: carrying the norm there
     measured 8 % slower than the norm kernels it saved.)"""
-    return (_small_m(n_rows) is K.gemm_small_m and 1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
+    return (1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
             and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
 
 
@@ -57,7 +57,7 @@ def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, *
     same features): the activation runs in the product's epilogue, so gate and
     up never go to memory.  Needs ``tensor_core_ok``."""
     if scale is not None:
-        return K.gemm_small_m(x, w_grouped, out, swiglu=True, scale=scale)
+        return _small_m(x.shape[0])(x, w_grouped, out, swiglu=True, scale=scale)
     if x.shape[0] <= K.SMALL_M_MAX:
         return _small_m(x.shape[0])(x, w_grouped, out, swiglu=True)
     return K.gemm_tc(x, w_grouped, out, swiglu=True)
@@ -73,7 +73,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
     if scale is not None or emit is not None:
         if not norm_link_ok(x.shape[0], w, x.dtype) or x.data_ptr() % 16:
             raise K.KernelError("linear: these operands cannot carry a norm; ask norm_link_ok first")
-        return K.gemm_small_m(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit)
+        return _small_m(x.shape[0])(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit)
     if w.dtype == torch.float32 and x.dtype != torch.float32:
         x = x.float()
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0

@@ -107,12 +107,13 @@ def test_gemm_small_m(kernel, M, N, Kd):
     K().check_device_errors()
 
 
+@pytest.mark.parametrize("kernel", ["gemm_small_m", "gemm_tc_swap"])
 @pytest.mark.parametrize("M", [1, 5, 8, 17, 64])
 @pytest.mark.parametrize("H,F,swiglu", [(64, 48, False), (200, 96, True), (2048, 160, False), (9600, 64, True)])
-def test_gemm_carries_a_norm(M, H, F, swiglu):
+def test_gemm_carries_a_norm(kernel, M, H, F, swiglu):
     """x_new = x + z Wo^T; y = rmsnorm(x_new) * g, then y W1^T (or its SwiGLU): the first product
     writes the rows bf16(x_new * g) and the tile sums, the second applies the scale."""
-    gemm = K().gemm_small_m
+    gemm = getattr(K(), kernel)
     from mivi_v4_b200.ops.linear import linear
     eps = 1e-5
     z, wo = rnd(M, 72, dtype=torch.bfloat16), rnd(H, 72, dtype=torch.bfloat16, seed=1)
@@ -127,7 +128,7 @@ def test_gemm_carries_a_norm(M, H, F, swiglu):
     K().check_device_errors()
     x_new = x.double() + z.double() @ wo.double().T
     assert torch.allclose(resid.double(), x_new, rtol=1e-5, atol=1e-4)
-    assert link.n_partials == -(-H // (32 if H >= 9472 else 16))
+    assert link.n_partials == (-(-H // (32 if H >= 9472 else 16)) if kernel == "gemm_small_m" else -(-H // 128))
     ss = link.partials[:, :link.n_partials].double().sum(1)
     assert torch.allclose(ss, (x_new ** 2).sum(1), rtol=1e-5)
     y = P.plain_rms_norm(x_new, g.double(), eps)
