@@ -19,9 +19,11 @@
 #define MV_MAX_HEAD_DIM 256
 
 // ----------------------------------------------------- q/k norm, rope, append
-// One warp per (token, head slot); head slots are nh query heads, then nkv key
-// heads, then nkv value heads, as they lie in a row of the fused projection.
-template <typename T>
+// One warp per token and group of SLOTS head slots; head slots are nh query heads, then nkv key
+// heads, then nkv value heads, as they lie in a row of the fused projection.  A head's row is read
+// once, two neighbouring elements a lane (8 bytes), and stays in registers; the rows of all of a
+// warp's slots are requested before any is used, so their round trips to memory overlap.
+template <typename T, int SLOTS>
 __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __restrict__ wq,
                                   const float* __restrict__ wk, float eps,
                                   const float* __restrict__ inv_freq, int half_split,
@@ -33,49 +35,103 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int slots_per_tok = nh + 2 * nkv;
-    if (warp >= N * slots_per_tok) return;
-    const int n = warp / slots_per_tok, hs = warp - n * slots_per_tok;
-    const float* row = qkv + (size_t)n * slots_per_tok * hd + (size_t)hs * hd;
-    const int pos = positions[n];
+    const int groups = (slots_per_tok + SLOTS - 1) / SLOTS;
+    if (warp >= N * groups) return;
+    const int n = warp / groups, hs0 = (warp - n * groups) * SLOTS;
     const int half = hd >> 1;
-    const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
-
-    T* dst;
-    if (is_q) {
-        dst = q_out + (size_t)n * nh * hd + (size_t)hs * hd;
-    } else {
-        if (!append) return;
-        const int g = is_k ? hs - nh : hs - nh - nkv;
-        const int page_size = 1 << page_shift;
-        const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
-        dst = pool + (size_t)page * page_stride + (size_t)(is_k ? 0 : 1) * nkv * page_size * hd +
-              ((size_t)g * page_size + (pos & (page_size - 1))) * hd;
-    }
-    if (!is_q && !is_k) {                       // value head: copy
-        for (int d = lane; d < hd; d += 32) dst[d] = mv_from_f32<T>(row[d]);
-        return;
-    }
-    const float* w = is_q ? wq : wk;
-    float scale = 1.f;
-    if (w) {
-        float ss = 0.f;
-        for (int d = lane; d < hd; d += 32) ss = fmaf(row[d], row[d], ss);
-        ss = mv_warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)hd + eps);
-    }
-    for (int i = lane; i < half; i += 32) {
-        const int ia = half_split ? i : 2 * i;
-        const int ib = half_split ? i + half : 2 * i + 1;
-        float a = row[ia], b = row[ib];
-        if (w) { a = a * scale * w[ia]; b = b * scale * w[ib]; }
-        if (inv_freq) {
-            float s, c;
-            sincosf((float)pos * inv_freq[i], &s, &c);
-            const float ra = a * c - b * s, rb = a * s + b * c;
-            a = ra; b = rb;
+    constexpr int MAXJ = MV_MAX_HEAD_DIM / 64;
+    float2 x[SLOTS][MAXJ];
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const float* row = qkv + ((size_t)n * slots_per_tok + hs0 + s) * hd;
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            const int i = lane + 32 * j;
+            x[s][j] = (hs0 + s < slots_per_tok && i < half) ? *reinterpret_cast<const float2*>(row + 2 * i)
+                                                            : make_float2(0.f, 0.f);
         }
-        dst[ia] = mv_from_f32<T>(a);
-        dst[ib] = mv_from_f32<T>(b);
+    }
+    const int pos = positions[n];
+    const int page_size = 1 << page_shift;
+    // the rotation of pair i at this position is the same for every head: worked out once a warp
+    float sn[MAXJ], cs[MAXJ];
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+        const int i = lane + 32 * j;
+        sn[j] = 0.f;
+        cs[j] = 1.f;
+        if (inv_freq && !half_split && i < half && hs0 < nh + nkv) sincosf((float)pos * inv_freq[i], &sn[j], &cs[j]);
+    }
+    // where this token's keys and values go (only asked for if one of the slots is a key or value head)
+    T* kv_row = nullptr;
+    if (append && hs0 + SLOTS > nh) {
+        const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
+        kv_row = pool + (size_t)page * page_stride + (size_t)(pos & (page_size - 1)) * hd;
+    }
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const int hs = hs0 + s;
+        if (hs >= slots_per_tok) break;
+        const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)n * nh + hs) * hd;
+        } else {
+            if (!append) continue;
+            const int g = is_k ? hs - nh : hs - nh - nkv;
+            dst = kv_row + ((size_t)(is_k ? 0 : 1) * nkv + g) * page_size * hd;
+        }
+        if (!is_q && !is_k) {                       // value head: copy
+#pragma unroll
+            for (int j = 0; j < MAXJ; ++j) {
+                const int i = lane + 32 * j;
+                if (i < half) mv_store2(dst + 2 * i, x[s][j].x, x[s][j].y);
+            }
+            continue;
+        }
+        const float* w = is_q ? wq : wk;
+        float scale = 1.f;
+        if (w) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < MAXJ; ++j) ss = fmaf(x[s][j].x, x[s][j].x, fmaf(x[s][j].y, x[s][j].y, ss));
+            ss = mv_warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+        if (!half_split) {
+            // pairs (2i, 2i+1): the two elements a lane holds
+#pragma unroll
+            for (int j = 0; j < MAXJ; ++j) {
+                const int i = lane + 32 * j;
+                if (i >= half) break;
+                float a = x[s][j].x, b = x[s][j].y;
+                if (w) {
+                    const float2 ww = *reinterpret_cast<const float2*>(w + 2 * i);
+                    a = a * scale * ww.x;
+                    b = b * scale * ww.y;
+                }
+                if (inv_freq) {
+                    const float ra = a * cs[j] - b * sn[j], rb = a * sn[j] + b * cs[j];
+                    a = ra; b = rb;
+                }
+                mv_store2(dst + 2 * i, a, b);
+            }
+        } else {
+            // pairs (i, i + half): the partner of an element lies half a row away; read by element
+            const float* row = qkv + ((size_t)n * slots_per_tok + hs) * hd;
+            for (int i = lane; i < half; i += 32) {
+                float a = row[i], b = row[i + half];
+                if (w) { a = a * scale * w[i]; b = b * scale * w[i + half]; }
+                if (inv_freq) {
+                    float sn1, cs1;
+                    sincosf((float)pos * inv_freq[i], &sn1, &cs1);
+                    const float ra = a * cs1 - b * sn1, rb = a * sn1 + b * cs1;
+                    a = ra; b = rb;
+                }
+                dst[i] = mv_from_f32<T>(a);
+                dst[i + half] = mv_from_f32<T>(b);
+            }
+        }
     }
 }
 
@@ -88,15 +144,25 @@ MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, flo
     if (hd % 2 || hd > MV_MAX_HEAD_DIM || (page_size & (page_size - 1))) return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    const long long warps = (long long)N * (nh + 2 * nkv);
+    // many tokens: four head slots a warp, whose loads overlap; few: one, for more warps
+    const int slots = N >= 64 ? 4 : 1;
+    const long long warps = (long long)N * ((nh + 2 * nkv + slots - 1) / slots);
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
-    if (dtype == MV_DT_BF16)
-        mv_launch(qk_prepare_kernel<__nv_bfloat16>, blocks, threads, 0, stream, 
+    if (slots == 4 && dtype == MV_DT_BF16)
+        mv_launch(qk_prepare_kernel<__nv_bfloat16, 4>, blocks, threads, 0, stream,
+            qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
+            page_shift, (__nv_bfloat16*)pool, page_stride, append, (__nv_bfloat16*)q_out, N, nh, nkv, hd);
+    else if (slots == 4)
+        mv_launch(qk_prepare_kernel<float, 4>, blocks, threads, 0, stream,
+            qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
+            page_shift, (float*)pool, page_stride, append, (float*)q_out, N, nh, nkv, hd);
+    else if (dtype == MV_DT_BF16)
+        mv_launch(qk_prepare_kernel<__nv_bfloat16, 1>, blocks, threads, 0, stream, 
             qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
             page_shift, (__nv_bfloat16*)pool, page_stride, append, (__nv_bfloat16*)q_out, N, nh, nkv, hd);
     else
-        mv_launch(qk_prepare_kernel<float>, blocks, threads, 0, stream, 
+        mv_launch(qk_prepare_kernel<float, 1>, blocks, threads, 0, stream, 
             qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, table_stride,
             page_shift, (float*)pool, page_stride, append, (float*)q_out, N, nh, nkv, hd);
     return mv_launch_status();

@@ -82,10 +82,8 @@ rmsnorm_regs_kernel(const float* __restrict__ x, const float* __restrict__ w, TO
         const int c = threadIdx.x + j * THREADS;
         if (c < nv) {
             const float4 ww = reinterpret_cast<const float4*>(w)[c];
-            yr[4 * c + 0] = mv_from_f32<TO>(v[j].x * scale * ww.x);
-            yr[4 * c + 1] = mv_from_f32<TO>(v[j].y * scale * ww.y);
-            yr[4 * c + 2] = mv_from_f32<TO>(v[j].z * scale * ww.z);
-            yr[4 * c + 3] = mv_from_f32<TO>(v[j].w * scale * ww.w);
+            mv_store4(yr + 4 * c, v[j].x * scale * ww.x, v[j].y * scale * ww.y, v[j].z * scale * ww.z,
+                      v[j].w * scale * ww.w);
         }
     }
 }
@@ -93,7 +91,7 @@ rmsnorm_regs_kernel(const float* __restrict__ x, const float* __restrict__ w, TO
 MV_API int mv_rmsnorm(const float* x, const float* w, void* y, int y_dtype, const int* rows,
                       int n_rows, int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (H % 4 == 0 && H <= 8192 && H >= 256 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+    if (H % 4 == 0 && H <= 8192 && H >= 256 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
         if (y_dtype == MV_DT_BF16)
             mv_launch(rmsnorm_regs_kernel<__nv_bfloat16, 256>, n_rows, 256, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
         else

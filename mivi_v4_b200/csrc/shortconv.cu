@@ -75,11 +75,78 @@ __global__ void shortconv_fwd_vec4_kernel(const float* __restrict__ p, const flo
         y.w = fmaf(w[(d + 3) * k + j], bx.w, y.w);
     }
     const float4 c = *reinterpret_cast<const float4*>(p + (size_t)n * 3 * H + H + d);
-    TO* dst = z + (size_t)n * H + d;
-    dst[0] = mv_from_f32<TO>(c.x * y.x);
-    dst[1] = mv_from_f32<TO>(c.y * y.y);
-    dst[2] = mv_from_f32<TO>(c.z * y.z);
-    dst[3] = mv_from_f32<TO>(c.w * y.w);
+    mv_store4(z + (size_t)n * H + d, c.x * y.x, c.y * y.y, c.z * y.z, c.w * y.w);
+}
+
+// The same for a convolution of width KW (2 to 4) and steps of many tokens: a thread takes four
+// channels of TOK consecutive tokens and carries the last KW-1 values of B*x in registers, so a
+// token's B, C and x are read once (the kernel above reads B and x of the KW-1 tokens before it
+// again for every token).  Where the tile crosses into another sequence the history is fetched anew.
+template <typename TO, int KW, int TOK>
+__global__ void shortconv_fwd_tile_kernel(const float* __restrict__ p, const float* __restrict__ w,
+                                          const float* __restrict__ bias, const float* __restrict__ state,
+                                          const int* __restrict__ positions, const int* __restrict__ seq_of,
+                                          const int* __restrict__ slots, const int* __restrict__ starts,
+                                          TO* __restrict__ z, int N, int H) {
+    mv_pdl_begin();
+    const int H4 = H >> 2;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int tiles = (N + TOK - 1) / TOK;
+    if (i >= (long long)tiles * H4) return;
+    const int tile = (int)(i / H4), d = (int)(i - (long long)tile * H4) * 4;
+    float taps[4][KW];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int j = 0; j < KW; ++j) taps[e][j] = w[(d + e) * KW + j];
+    const float4 bs = bias ? *reinterpret_cast<const float4*>(bias + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 hist[KW - 1];
+    int prev_b = -1;
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+        const int n = tile * TOK + t;
+        if (n >= N) break;
+        const int b = seq_of[n];
+        const float* row = p + (size_t)n * 3 * H;
+        if (b != prev_b) {
+            // the KW-1 values before this token: from this step's rows or from the carried state
+            const int pos = positions[n], start = starts[b];
+            const float* st = state + (size_t)slots[b] * (KW - 1) * H;
+#pragma unroll
+            for (int j = 0; j < KW - 1; ++j) {
+                const int src = pos - (KW - 1) + j;
+                if (src >= start) {
+                    const float* r2 = p + (size_t)(n - (pos - src)) * 3 * H;
+                    const float4 bb = *reinterpret_cast<const float4*>(r2 + d);
+                    const float4 xx = *reinterpret_cast<const float4*>(r2 + 2 * H + d);
+                    hist[j] = make_float4(bb.x * xx.x, bb.y * xx.y, bb.z * xx.z, bb.w * xx.w);
+                } else {
+                    hist[j] = *reinterpret_cast<const float4*>(st + (size_t)(src - start + (KW - 1)) * H + d);
+                }
+            }
+            prev_b = b;
+        }
+        const float4 bb = *reinterpret_cast<const float4*>(row + d);
+        const float4 c = *reinterpret_cast<const float4*>(row + H + d);
+        const float4 xx = *reinterpret_cast<const float4*>(row + 2 * H + d);
+        const float4 cur = make_float4(bb.x * xx.x, bb.y * xx.y, bb.z * xx.z, bb.w * xx.w);
+        float4 y = bs;
+#pragma unroll
+        for (int j = 0; j < KW - 1; ++j) {
+            y.x = fmaf(taps[0][j], hist[j].x, y.x);
+            y.y = fmaf(taps[1][j], hist[j].y, y.y);
+            y.z = fmaf(taps[2][j], hist[j].z, y.z);
+            y.w = fmaf(taps[3][j], hist[j].w, y.w);
+        }
+        y.x = fmaf(taps[0][KW - 1], cur.x, y.x);
+        y.y = fmaf(taps[1][KW - 1], cur.y, y.y);
+        y.z = fmaf(taps[2][KW - 1], cur.z, y.z);
+        y.w = fmaf(taps[3][KW - 1], cur.w, y.w);
+        mv_store4(z + (size_t)n * H + d, c.x * y.x, c.y * y.y, c.z * y.z, c.w * y.w);
+#pragma unroll
+        for (int j = 0; j + 1 < KW - 1; ++j) hist[j] = hist[j + 1];
+        hist[KW - 2] = cur;
+    }
 }
 
 // One thread per (sequence, channel): the state after this step's tokens.
@@ -162,7 +229,19 @@ MV_API int mv_shortconv(const float* p, const float* w, const float* bias, float
     if (k < 1 || k > MV_MAX_CONV_K) return (int)cudaErrorInvalidValue;
     const int threads = 256;
     const unsigned blocks = (unsigned)(((long long)N * H + threads - 1) / threads);
-    if (H % 4 == 0 && (((uintptr_t)p | (uintptr_t)state | (uintptr_t)bias) & 15) == 0) {
+    constexpr int TOK = 4;
+    const bool aligned = H % 4 == 0 && (((uintptr_t)p | (uintptr_t)state | (uintptr_t)bias | (uintptr_t)z) & 15) == 0;
+    if (aligned && N >= 64 && k >= 2 && k <= 4) {
+        const unsigned tblocks = (unsigned)(((long long)((N + TOK - 1) / TOK) * (H / 4) + threads - 1) / threads);
+#define MV_TILE(TO_, KW_) mv_launch(shortconv_fwd_tile_kernel<TO_, KW_, TOK>, tblocks, threads, 0, stream, p, w, bias, \
+                                    state, positions, seq_of, slots, starts, (TO_*)z, N, H)
+        if (z_dtype == MV_DT_BF16) {
+            if (k == 2) MV_TILE(__nv_bfloat16, 2); else if (k == 3) MV_TILE(__nv_bfloat16, 3); else MV_TILE(__nv_bfloat16, 4);
+        } else {
+            if (k == 2) MV_TILE(float, 2); else if (k == 3) MV_TILE(float, 3); else MV_TILE(float, 4);
+        }
+#undef MV_TILE
+    } else if (aligned) {
         const unsigned vblocks = (unsigned)(((long long)N * (H / 4) + threads - 1) / threads);
         if (z_dtype == MV_DT_BF16)
             mv_launch(shortconv_fwd_vec4_kernel<__nv_bfloat16>, vblocks, threads, 0, stream, p, w, bias, state, positions,
