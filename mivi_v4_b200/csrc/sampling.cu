@@ -102,6 +102,29 @@ __device__ unsigned long long block_excl_scan(unsigned long long v, Shared& sh, 
     return sh.wsum[warp] + inc - v;
 }
 
+// The largest value of the block and, among equal ones, its smallest index, to *dst.
+__device__ __forceinline__ void block_argmax_first(float best, int besti, Shared& sh, int* dst) {
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    if ((tid & 31) == 0) { sh.fred[tid >> 5] = best; sh.ired[tid >> 5] = besti; }
+    __syncthreads();
+    if (tid < 32) {
+        best = sh.fred[tid]; besti = sh.ired[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+        }
+        if (tid == 0) *dst = besti == 0x7fffffff ? 0 : besti;
+    }
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
               float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
@@ -114,12 +137,35 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     const float* src = logits + (size_t)b * ld;
     float* x = work + (size_t)b * V;
 
+    const int nr = n_recent ? min(n_recent[b], RECENT_MAX) : 0;
+    const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
+
+    // 0. greedy without penalties: the first maximum of the logits as they are, read once, four at a time
+    if (temperature <= 0.f && !pen) {
+        float best = -INFINITY;
+        int besti = 0x7fffffff;
+        const bool vec = (((uintptr_t)src) & 15) == 0;
+        const int V4 = vec ? V >> 2 : 0;
+        for (int i = tid; i < V4; i += THREADS) {
+            const float4 v = reinterpret_cast<const float4*>(src)[i];
+            // within a thread the indices go up, so ">" keeps the first of equal values
+            if (v.x > best) { best = v.x; besti = 4 * i; }
+            if (v.y > best) { best = v.y; besti = 4 * i + 1; }
+            if (v.z > best) { best = v.z; besti = 4 * i + 2; }
+            if (v.w > best) { best = v.w; besti = 4 * i + 3; }
+        }
+        for (int i = 4 * V4 + tid; i < V; i += THREADS) {
+            const float v = src[i];
+            if (v > best) { best = v; besti = i; }
+        }
+        block_argmax_first(best, besti, sh, out + b);
+        return;
+    }
+
     for (int i = tid; i < V; i += THREADS) x[i] = src[i];
     __syncthreads();
 
     // 1. penalties, once per distinct recent token
-    const int nr = n_recent ? min(n_recent[b], RECENT_MAX) : 0;
-    const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
     if (pen && tid < nr) {
         const int* rc = recent + (size_t)b * RECENT_MAX;
         const int tok = rc[tid];
@@ -149,24 +195,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             const float v = x[i];
             if (v > best) { best = v; besti = i; }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
-        }
-        if ((tid & 31) == 0) { sh.fred[tid >> 5] = best; sh.ired[tid >> 5] = besti; }
-        __syncthreads();
-        if (tid < 32) {
-            best = sh.fred[tid]; besti = sh.ired[tid];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-                if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
-            }
-            if (tid == 0) out[b] = besti == 0x7fffffff ? 0 : besti;
-        }
+        block_argmax_first(best, besti, sh, out + b);
         return;
     }
 
