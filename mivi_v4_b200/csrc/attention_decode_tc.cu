@@ -130,6 +130,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // No slack for aligning: with it two blocks would not fit a multiprocessor.  The kernel has no
     // static shared memory, so the dynamic part starts on a 1024-byte boundary; if it ever does not,
     // the block reports it and leaves.
+    mv_pdl_launch_dependents();
     extern __shared__ __align__(1024) unsigned char smem[];
     const unsigned q_s = smem_u32(smem);
     if (q_s & 1023u) {
@@ -176,6 +177,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_holder;
+    // set-up done (it may have run under the tail of the kernel before): from here on the step's data
+    mv_pdl_wait();
 
     if (warp < 4) {
         // registers move from this warpgroup to the softmax warps (128 each at launch)
@@ -413,7 +416,7 @@ MV_API int mv_attention_decode_tc(const void* q, const void* pool, long long poo
         cudaFuncSetAttribute(attention_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
         attr_set = true;
     }
-    attention_decode_tc_kernel<<<dim3(splits, nkv, N), DT_THREADS, DT_SMEM, stream>>>(
+    mv_launch(attention_decode_tc_kernel, dim3(splits, nkv, N), DT_THREADS, DT_SMEM, stream,
         mq, mkv, page_table, table_stride, positions, seq_of, (__nv_bfloat16*)o, part_o, part_ml, nh, nkv,
         scale * 1.4426950408889634f, err);
     int rc = mv_launch_status();

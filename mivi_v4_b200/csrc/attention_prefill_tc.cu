@@ -134,6 +134,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ page_table, int table_stride, const int* __restrict__ cu,
                             const int* __restrict__ starts, __nv_bfloat16* __restrict__ o, int B, int nh, int nkv,
                             float scale_log2, int* __restrict__ err) {
+    mv_pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const unsigned q_s = smem_u32(smem);
@@ -188,6 +189,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_holder;
+    // set-up done (it may have run under the tail of the kernel before): from here on the step's data
+    mv_pdl_wait();
 
     if (warp < 4) {
         // registers move from this warpgroup to the softmax warps (168 each at launch)
@@ -377,7 +380,7 @@ MV_API int mv_attention_prefill_tc(const void* q, const void* pool, long long po
         attr_set = true;
     }
     dim3 grid((N + TILES * BQ - 1) / (TILES * BQ) + B, nh);
-    attention_prefill_tc_kernel<<<grid, AT_THREADS, AT_SMEM, stream>>>(
+    mv_launch(attention_prefill_tc_kernel, grid, AT_THREADS, AT_SMEM, stream,
         mq, mkv, page_table, table_stride, cu, starts, (__nv_bfloat16*)o, B, nh, nkv,
         scale * 1.4426950408889634f, err);
     return mv_launch_status();

@@ -102,13 +102,22 @@ __device__ __forceinline__ void mv_pdl_begin() {
 #ifndef __CUDACC_RTC__
 #include <stdlib.h>
 #include <utility>
-// The attribute is off unless MIVI_PDL=1 is set in the environment: on the decode
-// step of the 1.2B-parameter model it measured a few percent slower than plain
-// stream order inside a CUDA graph, so plain order is the default.
+// The attribute is on unless MIVI_PDL=0 is set in the environment.  Measured on decode steps of the
+// 1.2B-parameter model it is worth 8 to 11 % from 16 tokens on, where the products run on the TMA
+// pipeline of gemm_tc_swap.cu and request their first weight tiles before the wait, and 3 % on a
+// prefill; the register-streaming gemm_small_m.cu gains nothing from it and has a switch of its own
+// (MIVI_PDL_SMALL_M=1), off by default.
 static inline bool mv_pdl_enabled() {
     static const bool on = [] {
         const char* e = getenv("MIVI_PDL");
-        return e && e[0] == '1';
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+static inline bool mv_pdl_small_m_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("MIVI_PDL_SMALL_M");
+        return mv_pdl_enabled() && e && e[0] == '1';
     }();
     return on;
 }

@@ -291,7 +291,7 @@ int launch(const void* W, const void* X, const float* bias, void* out, int mode,
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
-    if (mv_pdl_enabled()) {
+    if (mv_pdl_small_m_enabled()) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;

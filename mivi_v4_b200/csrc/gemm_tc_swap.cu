@@ -89,9 +89,21 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const unsigned tmem_base = *tmem_holder;
 
     bool acc_ok = nkb > 0;
+    // Under programmatic dependent launch this block may have started while the kernel before it is
+    // still running.  The weights do not depend on that kernel: the ring's first round of W tiles is
+    // requested at once; X, and everything the epilogue reads, only after the wait.
+    mv_pdl_launch_dependents();
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            const int first = nkb < STAGES ? nkb : STAGES;
+            for (int i = 0; i < first; ++i) {
+                mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
+                tma_load_2d(tiles0 + i * L::STAGE_BYTES, &map_w, (kb0 + i) * BK, n0, full0 + 8 * i);
+            }
+            mv_pdl_wait();
+            for (int i = 0; i < first; ++i)
+                tma_load_2d(tiles0 + i * L::STAGE_BYTES + L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * i);
+            for (int i = first; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const unsigned phase = (unsigned)(i / STAGES) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, err, 1)) break;
@@ -145,6 +157,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // The slices of this tile are added in rank order.  The work of adding is dealt out to all blocks
     // of the cluster: an item is 32 consecutive rows for one token (a warp, one row per lane), item i
     // belongs to block i mod slices.  A lane first requests its value from every slice, then adds.
+    mv_pdl_wait();                 // the epilogue reads (and overwrites) what the kernel before may still use
     const float* share[8];
     if (slices > 1) {
         cg::cluster_group cluster = cg::this_cluster();
@@ -286,13 +299,22 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = L::TOTAL;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = slices;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (mv_pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (slices > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = slices;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = slices > 1 ? 1 : 0;
+    cfg.numAttrs = na;
     cudaLaunchKernelEx(&cfg, gemm_tc_swap_kernel<BN, STAGES>, mw, mx, bias, out, mode, M, N, K, ldo, link, err);
     return mv_launch_status();
 }
