@@ -134,7 +134,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ page_table, int table_stride, const int* __restrict__ cu,
                             const int* __restrict__ starts, __nv_bfloat16* __restrict__ o, int B, int nh, int nkv,
                             float scale_log2, int* __restrict__ err) {
-    mv_pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const unsigned q_s = smem_u32(smem);
@@ -356,6 +355,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     }
+    // Only now may the next kernel's blocks be given multiprocessors: signalled earlier, they would take
+    // the places of this grid's own later blocks and sit there waiting.
+    mv_pdl_launch_dependents();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -380,7 +382,9 @@ MV_API int mv_attention_prefill_tc(const void* q, const void* pool, long long po
         attr_set = true;
     }
     dim3 grid((N + TILES * BQ - 1) / (TILES * BQ) + B, nh);
-    mv_launch(attention_prefill_tc_kernel, grid, AT_THREADS, AT_SMEM, stream,
+    // a plain launch, not a programmatic one (see attention_decode_tc.cu); the kernel after it still
+    // starts under this one's tail
+    attention_prefill_tc_kernel<<<grid, AT_THREADS, AT_SMEM, stream>>>(
         mq, mkv, page_table, table_stride, cu, starts, (__nv_bfloat16*)o, B, nh, nkv,
         scale * 1.4426950408889634f, err);
     return mv_launch_status();
