@@ -1,32 +1,36 @@
 // Attention of a step's single tokens over long caches on the fifth-generation
-// tensor cores (head size 64, pages of 64 tokens, bfloat16, no window): flash
-// decoding whose two products are tcgen05.mma.
+// tensor cores (head size 64, pages of 64 tokens, bfloat16, no window, at most
+// 16 query heads a kv head): flash decoding whose two products are tcgen05.mma.
 //
-// Block = one query token, one kv head, one split of that token's keys.  The
-// query heads that share the kv head are the rows of the MMA's M side: head i of
-// the group sits at row (i mod 4) * 32 + i / 4 of a 128-row tile, so that the
-// four softmax warps (tensor memory lets a warp read only its own quarter of the
-// lanes) each own a quarter of the heads.  The other rows hold whatever the
-// shared memory held; rows never mix in either product, and they are not written
-// out.  Keys and values come in blocks of 128 (two pages) by TMA straight out of
-// the paged pool, as in attention_prefill_tc.cu.
+// Block = one query token, one kv head, one split of that token's keys.  Keys
+// and values come in blocks of 128 (two pages) by TMA straight out of the paged
+// pool, as in attention_prefill_tc.cu.
+//
+// The scores are computed TRANSPOSED, S^T = K Q^T: the 128 keys of a block are
+// the MMA's M side (one lane of tensor memory each), the query heads that share
+// the kv head its N side (16 columns).  Each of the 128 softmax threads then owns
+// one key and all heads, so the exponentials of a block are a handful of
+// instructions a warp (a thread per query row, the other way round, would issue
+// 128 of them with one lane at work).  The maximum over the keys is taken by
+// shuffles and one exchange through shared memory a block.  P goes to shared
+// memory as [head row][key], the swizzled K-major A operand of O += P V with
+// head i at row (i mod 4) * 32 + i / 4 of a 128-row tile; V is taken MN-major as
+// it lies in the cache.  The rows of no head hold whatever the shared memory
+// held; rows never mix in the product, and they are not written out.
 //
 //   warp 0      TMA: the query rows once, then K and V of every key block of the
 //               split into rings of two stages each;
-//   warp 1      MMA: S = Q K^T (128 x 128 x 64), issued for block j + 1 as soon as
-//               the softmax warps have taken S of block j into registers; then
-//               O += P V (128 x 64 x 128), V taken MN-major as it lies in the cache;
-//   warps 4-7   softmax, one row per lane: mask past the token's position, maximum,
-//               P = exp2(...) as bfloat16 into shared memory in the swizzled K-major
-//               layout, row sum in float32; O stays in tensor memory and is rescaled
-//               only when a row's maximum outgrows its reference by more than 2^8.
+//   warp 1      MMA: S^T (128 x 16 x 64), issued for block j + 1 as soon as the
+//               softmax warps have taken S^T of block j into registers; then
+//               O += P V (128 x 64 x 128);
+//   warps 4-7   softmax as above; O stays in tensor memory and is rescaled only
+//               when a head's maximum outgrows its reference by more than 2^8.
 //
 // A split writes its unnormalised O rows with their reference maximum and sum; a
 // second kernel (one warp per token and head) merges the splits in a fixed order.
 // With one split the rows are written out directly.  Every mbarrier wait is
-// bounded (tc_common.cuh).  Two blocks fit a multiprocessor (112 KB of shared
-// memory, 256 columns of tensor memory each), so one block's set-up hides behind
-// the other's stream.
+// bounded (tc_common.cuh).  Two blocks fit a multiprocessor, so one block's
+// set-up hides behind the other's stream.
 //
 // Same mathematics as attention_decode.cu (reference: crates/mivi-model/src/
 // transformer.rs:114-167, 293-298).
@@ -35,13 +39,14 @@
 namespace {
 
 constexpr int DT_THREADS = 256;
-constexpr int BQ = 128, BKV = 128, HD = 64, PAGE = 64;
-constexpr int Q_BYTES = BQ * HD * 2;               // 16 KB
+constexpr int BQ = 128, BKV = 128, HD = 64, PAGE = 64, NQ = 16;
+constexpr int Q_BYTES = NQ * HD * 2;               // 2 KB: 16 head rows
 constexpr int KV_BYTES = BKV * HD * 2;             // 16 KB per stage (two pages)
 constexpr int P_BYTES = BQ * BKV * 2;              // 32 KB: two K-major sub-tiles of [128 x 64]
 constexpr int STAGES_KV = 2;
-constexpr int DT_SMEM = Q_BYTES + 2 * STAGES_KV * KV_BYTES + P_BYTES + 256;
-constexpr unsigned S_COL0 = 0, O_COL0 = 128, TMEM_COLS = 256;
+constexpr int X_BYTES = 3 * 4 * NQ * 4;            // maxima (two buffers) and sums exchanged between the warps
+constexpr int DT_SMEM = Q_BYTES + 2 * STAGES_KV * KV_BYTES + P_BYTES + X_BYTES + 256;
+constexpr unsigned S_COL0 = 0, O_COL0 = 64, TMEM_COLS = 128;
 constexpr float RESCALE_ABOVE = 8.0f;
 
 enum { B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + STAGES_KV, B_VFULL = B_KEMPTY + STAGES_KV,
@@ -65,6 +70,14 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -76,69 +89,31 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-
-// Maximum of 32 values of a row, of those among them that exist; four chains, so that no instruction waits
-// for the one before it.
-template <bool MASK>
-__device__ __forceinline__ float chunk_max(const unsigned (&s)[32], int c, int visible) {
-    float a[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 32; i += 4)
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            if (!MASK || c + i + e < visible) a[e] = fmaxf(a[e], __uint_as_float(s[i + e]));
-    return fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
-}
-
-// 32 keys of one row: P = exp2(s * scale - ref) as bfloat16 into the row's four 16-byte chunks; returns their sum.
-template <bool MASK>
-__device__ __forceinline__ float row_exp(const unsigned (&s)[32], int c, int visible, float scale_log2, float ref,
-                                         unsigned char* p_tile, int r) {
-    float sum0 = 0.f, sum1 = 0.f;
-    unsigned packed[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-        float p0 = ex2(fmaf(__uint_as_float(s[i]), scale_log2, -ref));
-        float p1 = ex2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -ref));
-        if (MASK) {
-            if (c + i >= visible) p0 = 0.f;
-            if (c + i + 1 >= visible) p1 = 0.f;
-        }
-        sum0 += p0;
-        sum1 += p1;
-        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-        packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
-    }
-    unsigned char* sub = p_tile + (c >> 6) * (BQ * 128) + r * 128;
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-        const int chunk = ((c & 63) >> 3) + q4;
-        *reinterpret_cast<uint4*>(sub + ((chunk ^ (r & 7)) << 4)) =
-            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-    }
-    return sum0 + sum1;
-}
+// the 128 softmax threads meet (the other warps do not take part)
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // grid (splits, nkv, N).  part_o [N, nh, splits, 64], part_ml [N, nh, splits, 2] (reference maximum times
-// scale_log2, sum); with one split the rows go to o [N, nh * 64] directly.
+// scale_log2, sum); with one split the rows go to o [N, nh * 64] directly.  GP: heads a kv head, rounded up
+// to 4, 8 or 16.
+template <int GP>
 __global__ void __launch_bounds__(DT_THREADS, 2)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                            const int* __restrict__ page_table, int table_stride, const int* __restrict__ positions,
                            const int* __restrict__ seq_of, __nv_bfloat16* __restrict__ o,
                            float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
                            float scale_log2, int* __restrict__ err) {
-    // No slack for aligning: with it two blocks would not fit a multiprocessor.  The kernel has no
-    // static shared memory, so the dynamic part starts on a 1024-byte boundary; if it ever does not,
-    // the block reports it and leaves.
+    // No slack for aligning: the kernel has no static shared memory, so the dynamic part starts on a
+    // 1024-byte boundary; if it ever does not, the block reports it and leaves.
     extern __shared__ __align__(1024) unsigned char smem[];
-    const unsigned q_s = smem_u32(smem);
-    if (q_s & 1023u) {
+    const unsigned k_s = smem_u32(smem);
+    if (k_s & 1023u) {
         if (threadIdx.x == 0) atomicExch(err, 30);
         return;
     }
-    const unsigned k_s = q_s + Q_BYTES, v_s = k_s + STAGES_KV * KV_BYTES, p_s = v_s + STAGES_KV * KV_BYTES;
-    unsigned char* p_ptr = smem + Q_BYTES + 2 * STAGES_KV * KV_BYTES;
-    unsigned long long* bars = (unsigned long long*)(p_ptr + P_BYTES);
+    const unsigned v_s = k_s + STAGES_KV * KV_BYTES, p_s = v_s + STAGES_KV * KV_BYTES, q_s = p_s + P_BYTES;
+    unsigned char* p_ptr = smem + 2 * STAGES_KV * KV_BYTES;
+    float* xch = reinterpret_cast<float*>(p_ptr + P_BYTES + Q_BYTES);          // [3][4 warps][NQ]
+    unsigned long long* bars = (unsigned long long*)(p_ptr + P_BYTES + Q_BYTES + X_BYTES);
     unsigned* tmem_holder = (unsigned*)(bars + B_COUNT);
     const unsigned bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (unsigned)i; };
@@ -151,7 +126,6 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const int j0 = split * per, n_blocks = max(0, min(blocks_all, j0 + per) - j0);
     const int* table = page_table + (size_t)seq_of[n] * table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int active_warps = min(4, G);                 // head i sits in quarter i mod 4
 
     if (threadIdx.x == 0) {
         mbar_init(bar(B_Q), 1);
@@ -162,8 +136,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             mbar_init(bar(B_VEMPTY + s), 1);
         }
         mbar_init(bar(B_SFULL), 1);
-        mbar_init(bar(B_SEMPTY), active_warps);
-        mbar_init(bar(B_PFULL), active_warps);
+        mbar_init(bar(B_SEMPTY), 4);
+        mbar_init(bar(B_PFULL), 4);
         mbar_init(bar(B_PVDONE), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -176,155 +150,179 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_holder;
-    // set-up done (it may have run under the tail of the kernel before): from here on the step's data
     mv_pdl_wait();
 
     if (warp < 4) {
         // registers move from this warpgroup to the softmax warps (128 each at launch)
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0) {
-        if (lane == 0 && n_blocks > 0) {
-            // head i of the group: one row of 128 bytes to row (i mod 4) * 32 + i / 4 of the Q tile
-            mbar_expect_tx(bar(B_Q), (unsigned)G * HD * 2);
-            for (int i = 0; i < G; ++i)
-                tma_load_2d(q_s + (unsigned)(((i & 3) * 32 + (i >> 2)) * 128), &map_q, 0, n * nh + g * G + i, bar(B_Q));
-            for (int j = 0; j < n_blocks; ++j) {
-                const int s = j % STAGES_KV;
-                const unsigned ph = (unsigned)(j / STAGES_KV) & 1u;
-                const int jb = j0 + j;
-                const int pg0 = table[min(2 * jb, table_stride - 1)], pg1 = table[min(2 * jb + 1, table_stride - 1)];
-                if (!mbar_wait(bar(B_KEMPTY + s), ph ^ 1u, err, 31)) break;
-                mbar_expect_tx(bar(B_KFULL + s), KV_BYTES);
-                tma_load_2d(k_s + s * KV_BYTES, &map_kv, 0, ((pg0 * 2 + 0) * nkv + g) * PAGE, bar(B_KFULL + s));
-                tma_load_2d(k_s + s * KV_BYTES + KV_BYTES / 2, &map_kv, 0, ((pg1 * 2 + 0) * nkv + g) * PAGE,
-                            bar(B_KFULL + s));
-                if (!mbar_wait(bar(B_VEMPTY + s), ph ^ 1u, err, 32)) break;
-                mbar_expect_tx(bar(B_VFULL + s), KV_BYTES);
-                tma_load_2d(v_s + s * KV_BYTES, &map_kv, 0, ((pg0 * 2 + 1) * nkv + g) * PAGE, bar(B_VFULL + s));
-                tma_load_2d(v_s + s * KV_BYTES + KV_BYTES / 2, &map_kv, 0, ((pg1 * 2 + 1) * nkv + g) * PAGE,
-                            bar(B_VFULL + s));
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && n_blocks > 0) {
-            const unsigned idesc_qk = instr_desc(BQ, BKV);
-            const unsigned idesc_pv = instr_desc(BQ, HD) | (1u << 16);          // B operand MN-major
-            bool ok = mbar_wait(bar(B_Q), 0, err, 33);
-            auto issue_qk = [&](int j) {
-                const int s = j % STAGES_KV;
-                if (!mbar_wait(bar(B_KFULL + s), (unsigned)(j / STAGES_KV) & 1u, err, 34)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    mma_f16(tmem_base + S_COL0, smem_desc(q_s + k * 32), smem_desc(k_s + s * KV_BYTES + k * 32),
-                            idesc_qk, k > 0 ? 1u : 0u);
-                mma_commit(bar(B_SFULL));
-                mma_commit(bar(B_KEMPTY + s));
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j % STAGES_KV;
-                if (j + 1 < n_blocks) {
-                    // S of block j is in the softmax warps' registers: its columns are free for block j + 1
-                    if (!(ok = mbar_wait(bar(B_SEMPTY), (unsigned)j & 1u, err, 35))) break;
-                    if (!(ok = issue_qk(j + 1))) break;
+            if (lane == 0 && n_blocks > 0) {
+                // head i of the group: one row of 128 bytes, row i of the Q tile (the MMA's N side)
+                mbar_expect_tx(bar(B_Q), (unsigned)G * HD * 2);
+                for (int i = 0; i < G; ++i) tma_load_2d(q_s + (unsigned)(i * 128), &map_q, 0, n * nh + g * G + i, bar(B_Q));
+                for (int j = 0; j < n_blocks; ++j) {
+                    const int s = j % STAGES_KV;
+                    const unsigned ph = (unsigned)(j / STAGES_KV) & 1u;
+                    const int jb = j0 + j;
+                    const int pg0 = table[min(2 * jb, table_stride - 1)], pg1 = table[min(2 * jb + 1, table_stride - 1)];
+                    if (!mbar_wait(bar(B_KEMPTY + s), ph ^ 1u, err, 31)) break;
+                    mbar_expect_tx(bar(B_KFULL + s), KV_BYTES);
+                    tma_load_2d(k_s + s * KV_BYTES, &map_kv, 0, ((pg0 * 2 + 0) * nkv + g) * PAGE, bar(B_KFULL + s));
+                    tma_load_2d(k_s + s * KV_BYTES + KV_BYTES / 2, &map_kv, 0, ((pg1 * 2 + 0) * nkv + g) * PAGE,
+                                bar(B_KFULL + s));
+                    if (!mbar_wait(bar(B_VEMPTY + s), ph ^ 1u, err, 32)) break;
+                    mbar_expect_tx(bar(B_VFULL + s), KV_BYTES);
+                    tma_load_2d(v_s + s * KV_BYTES, &map_kv, 0, ((pg0 * 2 + 1) * nkv + g) * PAGE, bar(B_VFULL + s));
+                    tma_load_2d(v_s + s * KV_BYTES + KV_BYTES / 2, &map_kv, 0, ((pg1 * 2 + 1) * nkv + g) * PAGE,
+                                bar(B_VFULL + s));
                 }
-                if (!(ok = mbar_wait(bar(B_PFULL), (unsigned)j & 1u, err, 36))) break;
-                if (!(ok = mbar_wait(bar(B_VFULL + s), (unsigned)(j / STAGES_KV) & 1u, err, 37))) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int k = 0; k < BKV / 16; ++k) {
-                    const unsigned a_addr = p_s + (k >> 2) * (BQ * 128) + (k & 3) * 32;
-                    const unsigned b_addr = v_s + s * KV_BYTES + k * 16 * 128;
-                    mma_f16(tmem_base + O_COL0, smem_desc(a_addr), smem_desc_mn(b_addr), idesc_pv,
-                            (j > 0 || k > 0) ? 1u : 0u);
-                }
-                mma_commit(bar(B_PVDONE));
-                mma_commit(bar(B_VEMPTY + s));
             }
-        }
+        } else if (warp == 1) {
+            if (lane == 0 && n_blocks > 0) {
+                const unsigned idesc_qk = instr_desc(BKV, NQ);                      // keys x heads
+                const unsigned idesc_pv = instr_desc(BQ, HD) | (1u << 16);          // B operand MN-major
+                bool ok = mbar_wait(bar(B_Q), 0, err, 33);
+                auto issue_qk = [&](int j) {
+                    const int s = j % STAGES_KV;
+                    if (!mbar_wait(bar(B_KFULL + s), (unsigned)(j / STAGES_KV) & 1u, err, 34)) return false;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k)
+                        mma_f16(tmem_base + S_COL0, smem_desc(k_s + s * KV_BYTES + k * 32), smem_desc(q_s + k * 32),
+                                idesc_qk, k > 0 ? 1u : 0u);
+                    mma_commit(bar(B_SFULL));
+                    mma_commit(bar(B_KEMPTY + s));
+                    return true;
+                };
+                if (ok) ok = issue_qk(0);
+                for (int j = 0; j < n_blocks && ok; ++j) {
+                    const int s = j % STAGES_KV;
+                    if (j + 1 < n_blocks) {
+                        // S^T of block j is in the softmax warps' registers: its columns are free for block j + 1
+                        if (!(ok = mbar_wait(bar(B_SEMPTY), (unsigned)j & 1u, err, 35))) break;
+                        if (!(ok = issue_qk(j + 1))) break;
+                    }
+                    if (!(ok = mbar_wait(bar(B_PFULL), (unsigned)j & 1u, err, 36))) break;
+                    if (!(ok = mbar_wait(bar(B_VFULL + s), (unsigned)(j / STAGES_KV) & 1u, err, 37))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int k = 0; k < BKV / 16; ++k) {
+                        const unsigned a_addr = p_s + (k >> 2) * (BQ * 128) + (k & 3) * 32;
+                        const unsigned b_addr = v_s + s * KV_BYTES + k * 16 * 128;
+                        mma_f16(tmem_base + O_COL0, smem_desc(a_addr), smem_desc_mn(b_addr), idesc_pv,
+                                (j > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit(bar(B_PVDONE));
+                    mma_commit(bar(B_VEMPTY + s));
+                }
+            }
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-        if ((warp & 3) < active_warps) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;                   // row of the tile = lane of tensor memory
-        const int head_in_group = lane * 4 + quarter;
-        const bool live = head_in_group < G;
-        const int h = g * G + head_in_group;
+        const int t = quarter * 32 + lane;                   // this thread's key within a block = its lane of tensor memory
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         const unsigned s_addr = tmem_base + lane_addr + S_COL0, o_addr = tmem_base + lane_addr + O_COL0;
-        float m = -INFINITY, l = 0.f;
+        // the O row of lane t belongs to head own (if own < G): head i sits at row (i mod 4) * 32 + i / 4
+        const int own = lane * 4 + quarter;
+        float m[GP], l[GP];                                  // reference maxima (the same in every thread), this key's sums
+#pragma unroll
+        for (int h = 0; h < GP; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
         bool ok = true;
         for (int j = 0; j < n_blocks && ok; ++j) {
             ok = mbar_wait(bar(B_SFULL), (unsigned)j & 1u, err, 38);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned s0[32], s1[32], s2[32], s3[32];
-            tmem_ld32(s_addr, s0);
-            tmem_ld32(s_addr + 32, s1);
-            tmem_ld32(s_addr + 64, s2);
-            tmem_ld32(s_addr + 96, s3);
+            unsigned sr[16];
+            tmem_ld16(s_addr, sr);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_SEMPTY));
-            const int visible = kv_len - (j0 + j) * BKV;      // keys of this block that exist
-            const bool mask = visible < BKV;                  // only a token's last block is ragged
-            float mx = mask ? fmaxf(fmaxf(chunk_max<true>(s0, 0, visible), chunk_max<true>(s1, 32, visible)),
-                                    fmaxf(chunk_max<true>(s2, 64, visible), chunk_max<true>(s3, 96, visible)))
-                            : fmaxf(fmaxf(chunk_max<false>(s0, 0, visible), chunk_max<false>(s1, 32, visible)),
-                                    fmaxf(chunk_max<false>(s2, 64, visible), chunk_max<false>(s3, 96, visible)));
-            if (!live) mx = 0.f;                              // rows of no head: anything finite
-            float corr = 1.0f;
-            if (mx > m && (m == -INFINITY || (mx - m) * scale_log2 > RESCALE_ABOVE)) {
-                corr = m == -INFINITY ? 0.f : ex2((m - mx) * scale_log2);
-                m = mx;
+            const bool valid = t < kv_len - (j0 + j) * BKV;   // this key exists
+            float sv[GP];
+            float* wmax = xch + (j & 1) * 4 * NQ;             // two buffers: the next block writes the other one
+#pragma unroll
+            for (int h = 0; h < GP; ++h) {
+                sv[h] = valid ? __uint_as_float(sr[h]) : -INFINITY;
+                const float wm = mv_warp_max(sv[h]);
+                if (lane == 0) wmax[quarter * NQ + h] = wm;
+            }
+            softmax_sync();
+            float corr[GP];
+            bool any = false;
+#pragma unroll
+            for (int h = 0; h < GP; ++h) {
+                const float mx = fmaxf(fmaxf(wmax[h], wmax[NQ + h]), fmaxf(wmax[2 * NQ + h], wmax[3 * NQ + h]));
+                corr[h] = 1.0f;
+                if (h < G && mx > m[h] && (m[h] == -INFINITY || (mx - m[h]) * scale_log2 > RESCALE_ABOVE)) {
+                    corr[h] = m[h] == -INFINITY ? 0.f : ex2((m[h] - mx) * scale_log2);
+                    m[h] = mx;
+                    any = true;
+                }
             }
             // P of the block before and O are in use until its second product is done
             if (j > 0) {
                 ok = mbar_wait(bar(B_PVDONE), (unsigned)(j - 1) & 1u, err, 39);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+                if (any) {                                   // the same decision in every thread
+                    float mine = 1.0f;
+#pragma unroll
+                    for (int h = 0; h < GP; ++h)
+                        if (h == own) mine = corr[h];
 #pragma unroll
                     for (int c = 0; c < HD; c += 32) {
                         unsigned v[32];
                         tmem_ld32(o_addr + (unsigned)c, v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * mine);
                         tmem_st32(o_addr + (unsigned)c, v);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
-            const float ref = m == -INFINITY ? 0.f : m * scale_log2;
-            float sum;
-            if (mask) {
-                sum = (row_exp<true>(s0, 0, visible, scale_log2, ref, p_ptr, r) +
-                       row_exp<true>(s1, 32, visible, scale_log2, ref, p_ptr, r)) +
-                      (row_exp<true>(s2, 64, visible, scale_log2, ref, p_ptr, r) +
-                       row_exp<true>(s3, 96, visible, scale_log2, ref, p_ptr, r));
-            } else {
-                sum = (row_exp<false>(s0, 0, visible, scale_log2, ref, p_ptr, r) +
-                       row_exp<false>(s1, 32, visible, scale_log2, ref, p_ptr, r)) +
-                      (row_exp<false>(s2, 64, visible, scale_log2, ref, p_ptr, r) +
-                       row_exp<false>(s3, 96, visible, scale_log2, ref, p_ptr, r));
+            // this key's column of P, one bfloat16 a head, into the head's row of the swizzled K-major tile
+            unsigned char* pcol = p_ptr + (t >> 6) * (BQ * 128) + (t & 7) * 2;
+            const int chunk = (t & 63) >> 3;
+#pragma unroll
+            for (int h = 0; h < GP; ++h) {
+                if (h < G) {
+                    const float p = valid ? ex2(fmaf(sv[h], scale_log2, -m[h] * scale_log2)) : 0.f;
+                    l[h] = l[h] * corr[h] + p;
+                    const int row = (h & 3) * 32 + (h >> 2);
+                    *reinterpret_cast<__nv_bfloat16*>(pcol + row * 128 + ((chunk ^ (row & 7)) << 4)) = __float2bfloat16_rn(p);
+                }
             }
-            l = l * corr + sum;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PFULL));
         }
         if (ok && n_blocks > 0) ok = mbar_wait(bar(B_PVDONE), (unsigned)(n_blocks - 1) & 1u, err, 40);
+        // the heads' sums over all keys: by shuffles, then across the four warps
+        float* wsum = xch + 2 * 4 * NQ;
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+            const float ws = mv_warp_sum(l[h]);
+            if (lane == 0) wsum[quarter * NQ + h] = ws;
+        }
+        softmax_sync();
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool live = own < G;
+            float m_own = -INFINITY, l_own = 0.f;
+#pragma unroll
+            for (int h = 0; h < GP; ++h)
+                if (h == own) {
+                    m_own = m[h];
+                    l_own = (wsum[h] + wsum[NQ + h]) + (wsum[2 * NQ + h] + wsum[3 * NQ + h]);
+                }
+            const int hh = g * G + own;
             const bool direct = splits == 1;
-            const float inv = direct && l > 0.f ? 1.0f / l : 1.0f;
-            float* po = part_o + (((size_t)n * nh + h) * splits + split) * HD;
+            const float inv = direct && l_own > 0.f ? 1.0f / l_own : 1.0f;
+            float* po = part_o + (((size_t)n * nh + hh) * splits + split) * HD;
 #pragma unroll
             for (int c = 0; c < HD; c += 32) {
                 unsigned v[32];
@@ -337,7 +335,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 }
                 if (live) {
                     if (direct) {
-                        __nv_bfloat16* dst = o + ((size_t)n * nh + h) * HD + c;
+                        __nv_bfloat16* dst = o + ((size_t)n * nh + hh) * HD + c;
 #pragma unroll
                         for (int d = 0; d < 32; d += 8) {
                             unsigned w4[4];
@@ -359,11 +357,10 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 }
             }
             if (live && !direct) {
-                float* pm = part_ml + (((size_t)n * nh + h) * splits + split) * 2;
-                pm[0] = m == -INFINITY ? -INFINITY : m * scale_log2;
-                pm[1] = l;
+                float* pm = part_ml + (((size_t)n * nh + hh) * splits + split) * 2;
+                pm[0] = m_own == -INFINITY ? -INFINITY : m_own * scale_log2;
+                pm[1] = l_own;
             }
-        }
         }
     }
     // Only now may the next kernel's blocks be given multiprocessors: signalled earlier, they would take
@@ -401,28 +398,37 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 
 }  // namespace
 
-// bfloat16, head size 64, pages of 64 tokens, no window, at most 128 query heads per kv head.
+// bfloat16, head size 64, pages of 64 tokens, no window, at most 16 query heads per kv head.
 // pool_rows = pages * 2 * nkv * 64.  part_o [N, nh, splits, 64] and part_ml [N, nh, splits, 2] float32.
 MV_API int mv_attention_decode_tc(const void* q, const void* pool, long long pool_rows, const int* page_table,
                                   int table_stride, const int* positions, const int* seq_of, void* o, float* part_o,
                                   float* part_ml, int N, int nh, int nkv, float scale, int splits, int* err,
                                   cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (nh % nkv || nh / nkv > 128 || splits < 1 || ((uintptr_t)q & 15) || ((uintptr_t)pool & 15))
+    if (nh % nkv || nh / nkv > NQ || splits < 1 || ((uintptr_t)q & 15) || ((uintptr_t)pool & 15))
         return (int)cudaErrorInvalidValue;
     CUtensorMap mq, mkv;
     if (!tensor_map(q, N * nh, HD, 1, &mq) || !tensor_map(pool, (int)pool_rows, HD, PAGE, &mkv))
         return (int)cudaErrorInvalidValue;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(attention_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
-        attr_set = true;
-    }
     // A plain launch, not a programmatic one: started early, this grid's blocks (two fill a
     // multiprocessor) measured 12 us slower at 64 tokens; the kernel after it still starts under its tail.
-    attention_decode_tc_kernel<<<dim3(splits, nkv, N), DT_THREADS, DT_SMEM, stream>>>(
-        mq, mkv, page_table, table_stride, positions, seq_of, (__nv_bfloat16*)o, part_o, part_ml, nh, nkv,
-        scale * 1.4426950408889634f, err);
+    const int G = nh / nkv;
+#define MV_GO(GP)                                                                                              \
+    do {                                                                                                       \
+        static bool attr_set = false;                                                                          \
+        if (!attr_set) {                                                                                       \
+            cudaFuncSetAttribute(attention_decode_tc_kernel<GP>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                 DT_SMEM);                                                                     \
+            attr_set = true;                                                                                   \
+        }                                                                                                      \
+        attention_decode_tc_kernel<GP><<<dim3(splits, nkv, N), DT_THREADS, DT_SMEM, stream>>>(                 \
+            mq, mkv, page_table, table_stride, positions, seq_of, (__nv_bfloat16*)o, part_o, part_ml, nh, nkv, \
+            scale * 1.4426950408889634f, err);                                                                 \
+    } while (0)
+    if (G <= 4) MV_GO(4);
+    else if (G <= 8) MV_GO(8);
+    else MV_GO(16);
+#undef MV_GO
     int rc = mv_launch_status();
     if (rc || splits == 1) return rc;
     const int rows = N * nh;

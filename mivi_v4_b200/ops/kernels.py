@@ -516,15 +516,26 @@ def attention_decode_tc_plan(N: int, nkv: int, context_cap: int) -> int:
     return max(1, min(64, want, blocks // 2))
 
 
+DECODE_TC_MAX_GROUP = 16
+
+
+def attention_decode_tc_supported(dtype: torch.dtype, hd: int, pool: torch.Tensor, window: int, nh: int,
+                                  nkv: int) -> bool:
+    """What the tcgen05 decode attention takes: as the tcgen05 prefill attention, and at most 16
+    query heads a kv head (they are the 16 columns of its transposed scores)."""
+    return (attention_prefill_tc_supported(dtype, hd, pool, window) and nkv > 0 and nh % nkv == 0
+            and nh // nkv <= DECODE_TC_MAX_GROUP)
+
+
 def attention_decode_tc(q: torch.Tensor, pool: torch.Tensor, page_table, positions, seq_of, out: torch.Tensor,
                         nh: int, nkv: int, hd: int, scale: float, ws, splits: Optional[int] = None):
     """Attention of single query tokens over long caches, both products on tcgen05 (bfloat16,
     head size 64, pages of 64 tokens, no window).  Same arguments and result as
     :func:`attention_decode`."""
     N = q.shape[0]
-    if not attention_prefill_tc_supported(q.dtype, hd, pool, 0) or nh % nkv or nh // nkv > 128:
+    if not attention_decode_tc_supported(q.dtype, hd, pool, 0, nh, nkv):
         raise KernelError(f"attention_decode_tc: needs bfloat16, head size 64, a dense pool of 64-token pages and "
-                          f"at most 128 heads a kv head, got {q.dtype}, {hd}, pool {tuple(pool.shape)}, {nh}/{nkv}")
+                          f"at most 16 heads a kv head, got {q.dtype}, {hd}, pool {tuple(pool.shape)}, {nh}/{nkv}")
     _check_kv(pool, nkv, hd, 64, "attention")
     if q.dtype != pool.dtype or out.dtype != q.dtype:
         raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")

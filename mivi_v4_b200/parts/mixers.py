@@ -137,8 +137,8 @@ class GroupedQueryAttention(Part):
             K.qk_prepare(qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
                          step.seq_of, view.page_table, view.pool, q, nh, nkv, hd)
         o = step.ws.get("mix", (N, nh * hd), step.dtype)
-        if N <= K.DECODE_ATTENTION_MAX_TOKENS and K.attention_prefill_tc_supported(step.dtype, hd, view.pool,
-                                                                                  self.window):
+        if N <= K.DECODE_ATTENTION_MAX_TOKENS and K.attention_decode_tc_supported(step.dtype, hd, view.pool,
+                                                                                 self.window, nh, nkv):
             # few query tokens, head size 64: flash decoding with both products on tcgen05
             K.attention_decode_tc(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                   self.scale, step.ws)

@@ -433,7 +433,7 @@ def test_attention_prefill_tc(nh, nkv):
 
 
 @pytest.mark.parametrize("splits", [None, 1, 3, 7])
-@pytest.mark.parametrize("nh,nkv", [(8, 2), (3, 1), (5, 5), (12, 2)])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (3, 1), (5, 5), (12, 2), (16, 1)])
 def test_attention_decode_tc(nh, nkv, splits):
     """The tcgen05 decode kernel (head size 64, pages of 64): single tokens at the end and in the
     middle of caches of many lengths, any number of key splits, with one far key that stands out."""
