@@ -88,10 +88,59 @@ rmsnorm_regs_kernel(const float* __restrict__ x, const float* __restrict__ w, TO
     }
 }
 
+// Many rows (a prefill): one WARP per row, each lane keeping up to 16 float4 of it in registers.  All
+// of a row's loads are in flight at once and the sum needs shuffles only, no block barrier.  H a multiple
+// of 4, at most 2048 (16 float4 a lane).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
+                    const int* __restrict__ rows, int n_rows, int H, float eps) {
+    mv_pdl_begin();
+    constexpr int MAXV = 16;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (i >= n_rows) return;
+    const int r = rows ? rows[i] : i;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * H);
+    const int nv = H >> 2;
+    float4 v[MAXV];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        const int c = lane + 32 * j;
+        v[j] = c < nv ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = mv_warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* yr = y + (size_t)i * H;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        const int c = lane + 32 * j;
+        if (c < nv) {
+            const float4 ww = reinterpret_cast<const float4*>(w)[c];
+            mv_store4(yr + 4 * c, v[j].x * scale * ww.x, v[j].y * scale * ww.y, v[j].z * scale * ww.z,
+                      v[j].w * scale * ww.w);
+        }
+    }
+}
+
 MV_API int mv_rmsnorm(const float* x, const float* w, void* y, int y_dtype, const int* rows,
                       int n_rows, int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (H % 4 == 0 && H <= 8192 && H >= 256 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
+    const bool aligned = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0;
+    if (aligned && H <= 2048 && H >= 512 && n_rows >= 512) {
+        const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+        if (y_dtype == MV_DT_BF16)
+            mv_launch(rmsnorm_warp_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, w, (__nv_bfloat16*)y, rows, n_rows, H, eps);
+        else
+            mv_launch(rmsnorm_warp_kernel<float>, blocks, 256, 0, stream, x, w, (float*)y, rows, n_rows, H, eps);
+        return mv_launch_status();
+    }
+    if (aligned && H <= 8192 && H >= 256) {
         if (y_dtype == MV_DT_BF16)
             mv_launch(rmsnorm_regs_kernel<__nv_bfloat16, 256>, n_rows, 256, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
         else

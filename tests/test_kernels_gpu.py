@@ -36,7 +36,8 @@ def test_embed(dtype, V, H, N):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,H,eps", [(1, 16, 1e-5), (7, 200, 1e-6), (3, 2048, 1e-5), (2, 5000, 1e-3)])
+@pytest.mark.parametrize("n,H,eps", [(1, 16, 1e-5), (7, 200, 1e-6), (3, 2048, 1e-5), (2, 5000, 1e-3),
+                                     (600, 2048, 1e-5), (513, 516, 1e-6)])       # many rows: a warp a row
 def test_rmsnorm(out_dtype, n, H, eps):
     x, w = rnd(n, H, scale=3.0), rnd(H) + 1.0
     out = torch.empty(n, H, dtype=out_dtype, device=DEV)
