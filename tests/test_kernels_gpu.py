@@ -48,7 +48,10 @@ def test_rmsnorm(out_dtype, n, H, eps):
     rows = ints([n - 1, 0])
     out2 = torch.empty(2, H, dtype=out_dtype, device=DEV)
     K().rmsnorm(x, w, eps, out2, rows)
-    assert torch.equal(out2, out[rows.long()])
+    if n < 512:
+        assert torch.equal(out2, out[rows.long()])
+    else:       # many rows take another kernel, which adds the squares in another order
+        assert torch.allclose(out2.double(), out[rows.long()].double(), rtol=tol, atol=tol)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
