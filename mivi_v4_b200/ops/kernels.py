@@ -513,6 +513,8 @@ def attention_decode_tc_plan(N: int, nkv: int, context_cap: int) -> int:
     reach, not on the lengths."""
     blocks = max(1, -(-context_cap // 128))
     want = (2 * N_SMS) // max(1, N * nkv)
+    if blocks <= 8:
+        return 1          # up to 1,024 cached tokens a split saves less than its merge kernel costs
     return max(1, min(64, want, blocks // 2))
 
 
