@@ -87,10 +87,13 @@ __device__ __forceinline__ void store_chunk(const unsigned (&r)[32], int row, in
                     }
                     float4* p = reinterpret_cast<float4*>(dst + j);
                     if (mode == 2) {
-                        const float4 old = *p;
-                        v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                        // added in memory: nothing comes back, so the epilogue does not wait for a read
+                        // (one add an element a product: the same sum as load, add, store)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                    } else {
+                        *p = v;
                     }
-                    *p = v;
                 }
             } else {
 #pragma unroll
