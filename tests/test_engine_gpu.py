@@ -132,4 +132,17 @@ def test_long_prompts_in_chunks(folders, dtype):
     second = eng.step([(s, a[230:])], "all")
     eng.close(s)
     assert_close(torch.cat([first, second]), want_a, dtype, "one prompt in chunks of 230 and 470")
+    # chunks of 100 tokens: steps of few tokens with many tokens of one sequence each (in bfloat16 the
+    # tcgen05 decode attention, a block a token), two sequences side by side
+    sa, sb = eng.open(), eng.open()
+    rows_a, rows_b = [], []
+    for lo in range(0, 700, 50):
+        items = [(sa, a[lo:lo + 50])] + ([(sb, b[lo:lo + 50])] if lo < 300 else [])
+        got = eng.step(items, "all")
+        rows_a.append(got[:50])
+        if lo < 300:
+            rows_b.append(got[50:])
+    eng.close(sa), eng.close(sb)
+    assert_close(torch.cat(rows_a), want_a, dtype, "chunks of 50, the longer")
+    assert_close(torch.cat(rows_b), want_b, dtype, "chunks of 50, the shorter")
     eng.cache.check()
