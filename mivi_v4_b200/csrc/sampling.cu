@@ -6,7 +6,12 @@
 // (150-218) or the plain categorical draw (138-148).
 //
 // One block of 1024 threads per row; the row is copied to scratch first, so the
-// caller's logits stay as they are.
+// caller's logits stay as they are.  Thread t owns the run of indices
+// [t * seg, (t + 1) * seg), seg = ceil(V / 1024): running sums in index order are
+// then prefix sums in thread order.  In the scratch the k-th element of thread t
+// lies at k * 1024 + t, so that every pass reads it coalesced (laid out by index,
+// a thread's run would be 256 bytes away from its neighbour's).  The scratch of a
+// row holds seg * 1024 values; the places past V hold -infinity.
 //
 // Two things are this library's own.  (1) The uniform number: the reference
 // keeps one xorshift64* state for its single sequence (sampler.rs:70-76); a
@@ -135,7 +140,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     __shared__ Shared sh;
     const int b = blockIdx.x, tid = threadIdx.x;
     const float* src = logits + (size_t)b * ld;
-    float* x = work + (size_t)b * V;
+    const int seg = (V + THREADS - 1) / THREADS, VP = seg * THREADS;
+    float* x = work + (size_t)b * VP;                  // element i at x[(i % seg) * THREADS + i / seg]
 
     const int nr = n_recent ? min(n_recent[b], RECENT_MAX) : 0;
     const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
@@ -162,7 +168,28 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
         return;
     }
 
-    for (int i = tid; i < V; i += THREADS) x[i] = src[i];
+    // The copy, read by index and written to its place, both coalesced: a warp moves tiles of 32 threads'
+    // runs x 32 elements through a 32 x 33 tile of its own in shared memory.
+    {
+        extern __shared__ float tiles[];
+        const int warp = tid >> 5, lane = tid & 31;
+        float* tile = tiles + warp * (32 * 33);
+        const int t0 = warp * 32;                       // the warp's threads: t0 .. t0 + 31
+        for (int k0 = 0; k0 < seg; k0 += 32) {
+            // row a of the tile: the 32 elements k0 .. k0+31 of thread t0 + a's run, consecutive indices
+#pragma unroll 4
+            for (int a = 0; a < 32; ++a) {
+                const int k = k0 + lane, i = (t0 + a) * seg + k;
+                tile[a * 33 + lane] = (k < seg && i < V) ? src[i] : -INFINITY;
+            }
+            __syncwarp();
+            // column b of the tile goes to place (k0 + b) * THREADS + t0 .. t0+31: consecutive places
+#pragma unroll 4
+            for (int bcol = 0; bcol < 32; ++bcol)
+                if (k0 + bcol < seg) x[(size_t)(k0 + bcol) * THREADS + t0 + lane] = tile[lane * 33 + bcol];
+            __syncwarp();
+        }
+    }
     __syncthreads();
 
     // 1. penalties, once per distinct recent token
@@ -178,11 +205,12 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             }
         }
         if (first) {
-            float v = x[tok];
+            float& xt = x[(size_t)(tok % seg) * THREADS + tok / seg];
+            float v = xt;
             if (rep_pen > 0.f && rep_pen != 1.f) v = v > 0.f ? v / rep_pen : v * rep_pen;
             if (pres_pen != 0.f) v -= pres_pen;
             if (freq_pen != 0.f) v -= freq_pen * (float)count;
-            x[tok] = v;
+            xt = v;
         }
     }
     __syncthreads();
@@ -191,9 +219,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     if (temperature <= 0.f) {
         float best = -INFINITY;
         int besti = 0x7fffffff;
-        for (int i = tid; i < V; i += THREADS) {
-            const float v = x[i];
-            if (v > best) { best = v; besti = i; }
+        for (int k = 0; k < seg; ++k) {
+            const float v = x[(size_t)k * THREADS + tid];
+            if (v > best) { best = v; besti = tid * seg + k; }
         }
         block_argmax_first(best, besti, sh, out + b);
         return;
@@ -202,7 +230,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     // 3. temperature, maximum
     const float inv_t = 1.0f / temperature;
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += THREADS) {
+    for (int i = tid; i < VP; i += THREADS) {          // these passes do not care which index a place holds
         const float v = x[i] * inv_t;
         x[i] = v;
         mx = fmaxf(mx, v);
@@ -212,7 +240,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     // 4. min-p
     if (min_p > 0.f && min_p < 1.f) {
         const float thr = mx + logf(min_p);
-        for (int i = tid; i < V; i += THREADS)
+        for (int i = tid; i < VP; i += THREADS)
             if (x[i] < thr) x[i] = -INFINITY;
         __syncthreads();
     }
@@ -226,7 +254,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             __syncthreads();
             const unsigned prefix = sh.sel_prefix;
             const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = tid; i < V; i += THREADS) {
+            for (int i = tid; i < VP; i += THREADS) {
                 const unsigned key = order_key(x[i]);
                 if ((key & himask) == prefix) atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
             }
@@ -244,19 +272,18 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             __syncthreads();
         }
         const unsigned cut = sh.sel_prefix;
-        for (int i = tid; i < V; i += THREADS)
+        for (int i = tid; i < VP; i += THREADS)
             if (order_key(x[i]) < cut) x[i] = -INFINITY;
         __syncthreads();
     }
 
     // 6. softmax masses in fixed point; each thread owns a run of indices
-    const int seg = (V + THREADS - 1) / THREADS;
-    const int i0 = min(V, tid * seg), i1 = min(V, i0 + seg);
+    float* xr = x + tid;                               // this thread's run: xr[k * THREADS], index tid * seg + k
     unsigned long long mine = 0;
-    for (int i = i0; i < i1; ++i) {
-        const float v = x[i];
+    for (int k = 0; k < seg; ++k) {
+        const float v = xr[(size_t)k * THREADS];
         const float e = v == -INFINITY ? 0.f : expf(v - mx);
-        x[i] = e;
+        xr[(size_t)k * THREADS] = e;
         mine += fixed40(e);
     }
     unsigned long long total;
@@ -275,8 +302,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             __syncthreads();
             const unsigned prefix = sh.sel_prefix;
             const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = i0; i < i1; ++i) {
-                const float e = x[i];
+            for (int k = 0; k < seg; ++k) {
+                const float e = xr[(size_t)k * THREADS];
                 const unsigned key = __float_as_uint(e);          // e >= 0: bit order is value order
                 if (e > 0.f && (key & himask) == prefix) {
                     atomicAdd(&sh.mass[(key >> shift) & 255u], fixed40(e));
@@ -309,15 +336,15 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
         }
         // rank of this thread's first tie, in index order
         unsigned long long ties = 0;
-        for (int i = i0; i < i1; ++i) ties += (x[i] == cut_e && cut_e > 0.f) ? 1 : 0;
+        for (int k = 0; k < seg; ++k) ties += (xr[(size_t)k * THREADS] == cut_e && cut_e > 0.f) ? 1 : 0;
         unsigned long long tie_total;
         unsigned long long tie_rank = block_excl_scan(ties, sh, &tie_total);
         mine = 0;
-        for (int i = i0; i < i1; ++i) {
-            const float e = x[i];
+        for (int k = 0; k < seg; ++k) {
+            const float e = xr[(size_t)k * THREADS];
             bool keep = e > cut_e;
             if (e == cut_e && cut_e > 0.f) { keep = tie_rank < n_take; ++tie_rank; }
-            if (!keep) x[i] = 0.f;
+            if (!keep) xr[(size_t)k * THREADS] = 0.f;
             else mine += fixed40(e);
         }
         block_excl_scan(mine, sh, &kept);
@@ -335,11 +362,11 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     __syncthreads();
     if (mine > 0 && before <= r && r < before + mine) {
         unsigned long long c = before;
-        for (int i = i0; i < i1; ++i) {
-            const unsigned long long qv = fixed40(x[i]);
+        for (int k = 0; k < seg; ++k) {
+            const unsigned long long qv = fixed40(xr[(size_t)k * THREADS]);
             if (qv == 0) continue;
             c += qv;
-            if (r < c) { sh.result = i; break; }
+            if (r < c) { sh.result = tid * seg + k; break; }
         }
     }
     __syncthreads();
@@ -361,7 +388,13 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
                      const int* recent, const int* n_recent, unsigned long long seed, const int* streams,
                      const int* steps, int* out, cudaStream_t stream) {
     if (B <= 0) return 0;
-    mv_launch(sample_kernel, B, THREADS, 0, stream, logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
-                                             pres_pen, freq_pen, recent, n_recent, seed, streams, steps, out);
+    constexpr size_t TILES = (size_t)(THREADS / 32) * 32 * 33 * sizeof(float);   // a 32 x 33 tile a warp
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
+        attr_set = true;
+    }
+    mv_launch(sample_kernel, B, THREADS, TILES, stream, logits, ld, work, V, temperature, top_k, top_p, min_p,
+              rep_pen, pres_pen, freq_pen, recent, n_recent, seed, streams, steps, out);
     return mv_launch_status();
 }

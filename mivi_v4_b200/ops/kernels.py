@@ -618,19 +618,28 @@ def attention_prefill_tc(q: torch.Tensor, pool: torch.Tensor, page_table, cu, st
     return out
 
 
+def sample_scratch_width(V: int) -> int:
+    """Floats of scratch a row of V logits needs: V rounded up to the sampling block's 1,024 threads."""
+    return -(-int(V) // 1024) * 1024
+
+
 def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, temperature: float,
            top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
            presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
            recent: Optional[torch.Tensor] = None, n_recent: Optional[torch.Tensor] = None, seed: int = 0,
            streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One token per row of ``logits`` [B, V] (float32, rows may be strided)."""
+    """One token per row of ``logits`` [B, V] (float32, rows may be strided).  ``work``: scratch of
+    ``sample_scratch_width(V)`` floats a row."""
     B, V = logits.shape
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 on a CUDA device with unit column stride")
+    if work.dim() != 2 or work.shape[0] < B:
+        raise KernelError(f"sample: scratch {tuple(work.shape)} has fewer rows than the {B} rows of logits")
     if recent is not None and (recent.shape != (B, RECENT_MAX)):
         raise KernelError(f"sample: recent tokens shape {tuple(recent.shape)}, expected [{B}, {RECENT_MAX}]")
     _check(_fn("core", "mv_sample")(
-        logits.data_ptr(), logits.stride(0), _need(work, "sample scratch", torch.float32, (None, V)), B, V,
+        logits.data_ptr(), logits.stride(0),
+        _need(work, "sample scratch", torch.float32, (None, sample_scratch_width(V))), B, V,
         float(temperature), int(top_k), float(top_p), float(min_p), float(repetition_penalty),
         float(presence_penalty), float(frequency_penalty),
         _need(recent, "recent", torch.int32, optional=True),

@@ -42,7 +42,7 @@ class Sampler:
         p = self.params
         bufs = self._bufs.get(slot)
         if bufs is None or bufs[0].shape[0] < B:
-            bufs = (torch.empty((max(B, 1), V), dtype=torch.float32, device=self.device),
+            bufs = (torch.empty((max(B, 1), K.sample_scratch_width(V)), dtype=torch.float32, device=self.device),
                     torch.empty((max(B, 1),), dtype=torch.int32, device=self.device))
             self._bufs[slot] = bufs
         work, out_all = bufs

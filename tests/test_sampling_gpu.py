@@ -12,7 +12,7 @@ def run_kernel(logits, seed, streams, steps, recent, **kw):
     from mivi_v4_b200.ops import kernels as K
     B, V = logits.shape
     lg = logits.to(DEV)
-    work = torch.empty(B, V, device=DEV)
+    work = torch.empty(B, K.sample_scratch_width(V), device=DEV)
     out = torch.empty(B, dtype=torch.int32, device=DEV)
     rec = torch.zeros(B, 64, dtype=torch.int32)
     nrec = torch.zeros(B, dtype=torch.int32)
