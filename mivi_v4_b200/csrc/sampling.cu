@@ -29,6 +29,7 @@ namespace {
 
 constexpr int THREADS = 1024;
 constexpr int RECENT_MAX = 64;
+constexpr int RING = 128;              // places of a device-side ring of recent tokens: twice the window
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -135,7 +136,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
               float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
               float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
               unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
-              int* __restrict__ out) {
+              int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out) {
     mv_pdl_begin();
     __shared__ Shared sh;
     const int b = blockIdx.x, tid = threadIdx.x;
@@ -143,7 +144,13 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     const int seg = (V + THREADS - 1) / THREADS, VP = seg * THREADS;
     float* x = work + (size_t)b * VP;                  // element i at x[(i % seg) * THREADS + i / seg]
 
-    const int nr = n_recent ? min(n_recent[b], RECENT_MAX) : 0;
+    // The recent tokens of a row come from the caller (recent, n_recent) or from a ring that this kernel
+    // keeps itself on the device: ring [states, 128], state ring_row[b], the token sampled at step s at place
+    // s mod 128.  Step s looks at the places of steps s-1 ... s-64; its own place lies outside them, so a
+    // step that runs twice sees the same tokens and writes the same place both times.
+    int* my_ring = ring ? ring + (size_t)ring_row[b] * RING : nullptr;
+    const int my_step = steps ? steps[b] : 0;
+    const int nr = my_ring ? min(my_step, RECENT_MAX) : (n_recent ? min(n_recent[b], RECENT_MAX) : 0);
     const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
 
     // 0. greedy without penalties: the first maximum of the logits as they are, read once, four at a time
@@ -165,6 +172,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             if (v > best) { best = v; besti = i; }
         }
         block_argmax_first(best, besti, sh, out + b);
+        if (my_ring && tid == 0) my_ring[my_step & (RING - 1)] = out[b];
         return;
     }
 
@@ -194,12 +202,15 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
 
     // 1. penalties, once per distinct recent token
     if (pen && tid < nr) {
-        const int* rc = recent + (size_t)b * RECENT_MAX;
-        const int tok = rc[tid];
+        // recent token j (0 <= j < nr)
+        auto rc_at = [&](int j) {
+            return my_ring ? my_ring[(my_step - 1 - j) & (RING - 1)] : recent[(size_t)b * RECENT_MAX + j];
+        };
+        const int tok = rc_at(tid);
         bool first = tok >= 0 && tok < V;
         int count = 0;
         for (int j = 0; j < nr; ++j) {
-            if (rc[j] == tok) {
+            if (rc_at(j) == tok) {
                 if (j < tid) first = false;
                 ++count;
             }
@@ -224,6 +235,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             if (v > best) { best = v; besti = tid * seg + k; }
         }
         block_argmax_first(best, besti, sh, out + b);
+        if (my_ring && tid == 0) my_ring[my_step & (RING - 1)] = out[b];      // thread 0 wrote out[b] itself
         return;
     }
 
@@ -378,6 +390,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
                 if (src[i] * inv_t == mx) { res = i; break; }
         }
         out[b] = res;
+        if (my_ring) my_ring[my_step & (RING - 1)] = res;
     }
 }
 
@@ -386,7 +399,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
 MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int V, float temperature,
                      int top_k, float top_p, float min_p, float rep_pen, float pres_pen, float freq_pen,
                      const int* recent, const int* n_recent, unsigned long long seed, const int* streams,
-                     const int* steps, int* out, cudaStream_t stream) {
+                     const int* steps, int* ring, const int* ring_row, int* out, cudaStream_t stream) {
     if (B <= 0) return 0;
     constexpr size_t TILES = (size_t)(THREADS / 32) * 32 * 33 * sizeof(float);   // a 32 x 33 tile a warp
     static bool attr_set = false;
@@ -395,6 +408,6 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
         attr_set = true;
     }
     mv_launch(sample_kernel, B, THREADS, TILES, stream, logits, ld, work, V, temperature, top_k, top_p, min_p,
-              rep_pen, pres_pen, freq_pen, recent, n_recent, seed, streams, steps, out);
+              rep_pen, pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out);
     return mv_launch_status();
 }

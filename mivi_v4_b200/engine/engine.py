@@ -339,10 +339,10 @@ class _EngineBackend:
     def forward_and_sample(self, requests: Sequence[Request], token_lists) -> List[int]:
         """Forward the given tokens and sample the next one for every request.
 
-        Without penalties (which need the newest token on the host), the step AFTER this one is
-        enqueued before the host waits for this one's tokens: the sampling kernel's output is fed to
-        the next step on the device, for every request that can go on (it has tokens left to
-        generate).  If a request then turns out to have stopped, its row of the early step is simply
+        The step AFTER this one is enqueued before the host waits for this one's tokens (the recent
+        tokens that penalties look at are kept on the device by the sampling kernel itself): the
+        sampling kernel's output is fed to the next step on the device, for every request that can
+        go on (it has tokens left to generate).  If a request then turns out to have stopped, its row of the early step is simply
         not used; the other rows do not depend on it.  The next call finds its work already running."""
         sampler, eng = self.sampler, self.engine
         handles = [r.handle for r in requests]
@@ -355,11 +355,11 @@ class _EngineBackend:
         else:
             logits = eng.step([(r.handle, t) for r, t in zip(requests, token_lists)], "last", copy=False)
             out_dev = sampler.launch(logits, [r.index for r in requests], [len(r.output) for r in requests],
-                                     [r.output for r in requests])
+                                     [r.output for r in requests], states=handles)
             host, event = sampler.read_async(out_dev)
             rows = list(range(len(requests)))
         # the step after this one, for the requests that will still have tokens to generate
-        if not sampler.params.uses_penalties and eng.cuda_graphs:
+        if eng.cuda_graphs:
             goers = [(i, r) for i, r in zip(rows, requests) if len(r.output) + 2 <= r.max_new_tokens]
             if goers and len(goers) == len([r for r in requests if len(r.output) + 1 < r.max_new_tokens]):
                 src = out_dev if [i for i, _ in goers] == list(range(out_dev.numel())) else \
@@ -367,7 +367,8 @@ class _EngineBackend:
                 nxt = eng.decode_from_device([r.handle for _, r in goers], src)
                 if nxt is not None:
                     out2 = sampler.launch(nxt, [r.index for _, r in goers], [len(r.output) + 1 for _, r in goers],
-                                          [[] for _ in goers], slot=1 - early["slot"] if early else 1)
+                                          [[] for _ in goers], slot=1 - early["slot"] if early else 1,
+                                          states=[r.handle for _, r in goers])
                     host2, event2 = sampler.read_async(out2, slot=1 - early["slot"] if early else 1)
                     self._early = dict(handles=[r.handle for _, r in goers], out=out2, host=host2, event=event2,
                                        slot=1 - early["slot"] if early else 1)

@@ -20,6 +20,7 @@ F32, BF16 = 0, 1
 MAX_HEAD_DIM = 256
 MAX_CONV_K = 16
 RECENT_MAX = 64
+RECENT_RING = 128
 
 
 class KernelError(RuntimeError):
@@ -39,7 +40,7 @@ _SIGNATURES = {
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
                                 _I, _I, _P],
-        "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P],
+        "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P],
@@ -627,14 +628,20 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
            top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
            presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
            recent: Optional[torch.Tensor] = None, n_recent: Optional[torch.Tensor] = None, seed: int = 0,
-           streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> torch.Tensor:
+           streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None,
+           ring: Optional[torch.Tensor] = None, ring_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of ``logits`` [B, V] (float32, rows may be strided).  ``work``: scratch of
-    ``sample_scratch_width(V)`` floats a row."""
+    ``sample_scratch_width(V)`` floats a row.  The recent tokens that the penalties look at come
+    either from the caller (``recent`` [B, 64], ``n_recent``) or from ``ring`` [states, 128], which the
+    kernel keeps itself: row b uses state ``ring_rows[b]``, looks at the places of its last
+    min(steps[b], 64) steps and writes the token it samples to place steps[b] mod 128."""
     B, V = logits.shape
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 on a CUDA device with unit column stride")
     if work.dim() != 2 or work.shape[0] < B:
         raise KernelError(f"sample: scratch {tuple(work.shape)} has fewer rows than the {B} rows of logits")
+    if ring is not None and (steps is None or recent is not None):
+        raise KernelError("sample: a ring of recent tokens needs the rows' steps, and excludes a caller's recent tokens")
     if recent is not None and (recent.shape != (B, RECENT_MAX)):
         raise KernelError(f"sample: recent tokens shape {tuple(recent.shape)}, expected [{B}, {RECENT_MAX}]")
     _check(_fn("core", "mv_sample")(
@@ -645,5 +652,7 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
         _need(recent, "recent", torch.int32, optional=True),
         _need(n_recent, "n_recent", torch.int32, (B,), True), int(seed) & ((1 << 64) - 1),
         _need(streams, "streams", torch.int32, (B,), True), _need(steps, "steps", torch.int32, (B,), True),
+        _need(ring, "recent ring", torch.int32, (None, RECENT_RING), True),
+        _need(ring_rows, "ring rows", torch.int32, (B,), ring is None),
         _need(out, "sample out", torch.int32, (B,)), _stream()), "mv_sample")
     return out

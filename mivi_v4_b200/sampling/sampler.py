@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import time
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -27,6 +27,7 @@ class Sampler:
         self._pinned = {}
         self._events = {}
         self._done = {}
+        self._ring = None             # recent tokens kept on the device: int32 [states, 128]
         # the sampled tokens go to the host on a stream of their own: the step after this one does not
         # wait behind the copy
         self._copy_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
@@ -34,10 +35,14 @@ class Sampler:
         self._ws = Workspace(self.device)
 
     def launch(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
-               recent: Sequence[Sequence[int]], slot: int = 0) -> torch.Tensor:
+               recent: Sequence[Sequence[int]], slot: int = 0,
+               states: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Enqueue the sampling kernel; returns the device tensor (int32 [B]) that will hold the
         tokens.  ``slot`` (0 or 1) picks one of two sets of buffers, so that two launches can be in
-        flight."""
+        flight.  ``states``: a small integer per row that stays with its sequence (the engine's slot);
+        with it the recent tokens that the penalties look at are kept on the device, in a ring per
+        state that the kernel itself appends to, and ``recent`` is not used: a step can then be
+        enqueued before the host knows the token of the step before it."""
         B, V = logits.shape
         p = self.params
         bufs = self._bufs.get(slot)
@@ -46,13 +51,26 @@ class Sampler:
                     torch.empty((max(B, 1),), dtype=torch.int32, device=self.device))
             self._bufs[slot] = bufs
         work, out_all = bufs
-        use_pen = p.uses_penalties and any(len(r) for r in recent)
+        on_device = states is not None and p.uses_penalties
+        use_pen = p.uses_penalties and not on_device and any(len(r) for r in recent)
         out = out_all[:B]
-        if p.temperature <= 0.0 and not use_pen:
+        ring = rows_d = None
+        if on_device:
+            need = max(int(x) for x in states) + 1
+            if self._ring is None or self._ring.shape[0] < need:
+                grown = torch.zeros((max(need, 2 * (0 if self._ring is None else self._ring.shape[0]), 8),
+                                     K.RECENT_RING), dtype=torch.int32, device=self.device)
+                if self._ring is not None:
+                    grown[:self._ring.shape[0]] = self._ring
+                self._ring = grown
+            ring = self._ring
+        if p.temperature <= 0.0 and not use_pen and not on_device:
             # the largest logit: no draw, so no stream and step numbers to send up
             streams_d = steps_d = n_recent_d = recent_d = None
         else:
             meta: List[int] = [int(s) & 0x7fffffff for s in streams] + [int(s) for s in steps]
+            if on_device:
+                meta += [int(x) for x in states]
             if use_pen:
                 meta += [min(len(r), RECENT_TOKENS_WINDOW) for r in recent]
                 for r in recent:
@@ -60,12 +78,13 @@ class Sampler:
                     meta += r + [0] * (RECENT_TOKENS_WINDOW - len(r))
             m = self._ws.stage(f"sample_meta{slot}", meta)
             streams_d, steps_d = m[:B], m[B:2 * B]
+            rows_d = m[2 * B:3 * B] if on_device else None
             n_recent_d = m[2 * B:3 * B] if use_pen else None
             recent_d = m[3 * B:].view(B, RECENT_TOKENS_WINDOW) if use_pen else None
         K.sample(logits, work, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                  min_p=p.min_p, repetition_penalty=p.repetition_penalty, presence_penalty=p.presence_penalty,
                  frequency_penalty=p.frequency_penalty, recent=recent_d, n_recent=n_recent_d, seed=self.seed,
-                 streams=streams_d, steps=steps_d)
+                 streams=streams_d, steps=steps_d, ring=ring, ring_rows=rows_d)
         return out
 
     def read_async(self, out: torch.Tensor, slot: int = 0):

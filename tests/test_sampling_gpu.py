@@ -88,3 +88,34 @@ def test_large_vocabulary():
     assert got[0] in top3[0] and got[1] in top3[1]
     want = [P.plain_sample(logits[b], temperature=1.0, top_k=3, u=P.plain_uniform(0, b, 0)) for b in range(2)]
     assert got == want
+
+
+@pytest.mark.parametrize("kw", [dict(temperature=0.0, repetition_penalty=1.5, frequency_penalty=0.3),
+                                dict(temperature=0.9, top_k=30, top_p=0.95, repetition_penalty=1.3, presence_penalty=0.4)])
+def test_recent_tokens_kept_on_the_device(kw):
+    """The kernel keeps the recent tokens in a ring of its own: over 200 steps (the window of 64 wraps
+    three times) it samples what it samples when the caller hands it the last 64 tokens; two rows use
+    states that are not their row numbers; a step run twice gives the same token twice."""
+    from mivi_v4_b200.ops import kernels as K
+    V, B, steps_n = 97, 2, 200
+    g = torch.Generator().manual_seed(3)
+    base = torch.randn(B, V, generator=g)
+    ring = torch.full((6, K.RECENT_RING), -7, dtype=torch.int32, device=DEV)       # stale contents
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    work = torch.empty(B, K.sample_scratch_width(V), device=DEV)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    streams = torch.tensor([11, 12], dtype=torch.int32, device=DEV)
+    history = [[], []]
+    for s in range(steps_n):
+        logits = (base + 0.3 * torch.randn(B, V, generator=g)).to(DEV)
+        st = torch.tensor([s, s], dtype=torch.int32, device=DEV)
+        K.sample(logits, work, out, seed=5, streams=streams, steps=st, ring=ring, ring_rows=rows, **kw)
+        got = out.tolist()
+        if s % 37 == 5:                                   # the same step once more: the same tokens
+            K.sample(logits, work, out, seed=5, streams=streams, steps=st, ring=ring, ring_rows=rows, **kw)
+            assert out.tolist() == got
+        want = run_kernel(logits.cpu(), 5, [11, 12], [s, s], [h[-64:] for h in history], **kw)
+        assert got == want, (s, got, want)
+        for b in range(B):
+            history[b].append(got[b])
+    assert len(set(history[0])) > 5                       # the penalties did spread the tokens
