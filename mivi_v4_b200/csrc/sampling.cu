@@ -63,6 +63,8 @@ struct Shared {
     unsigned sel_remaining;
     unsigned long long sel_mass_above;
     int result;
+    float cval[1024];                  // what top-k left, in index order, when it fits: values ...
+    int cidx[1024];                    // ... and their indices
 };
 
 __device__ float block_max(float v, Shared& sh) {
@@ -141,7 +143,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     __shared__ Shared sh;
     const int b = blockIdx.x, tid = threadIdx.x;
     const float* src = logits + (size_t)b * ld;
-    const int seg = (V + THREADS - 1) / THREADS, VP = seg * THREADS;
+    int seg = (V + THREADS - 1) / THREADS;
+    const int VP = seg * THREADS;
+    bool compact = false;
     float* x = work + (size_t)b * VP;                  // element i at x[(i % seg) * THREADS + i / seg]
 
     // The recent tokens of a row come from the caller (recent, n_recent) or from a ring that this kernel
@@ -284,13 +288,37 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             __syncthreads();
         }
         const unsigned cut = sh.sel_prefix;
-        for (int i = tid; i < VP; i += THREADS)
-            if (order_key(x[i]) < cut) x[i] = -INFINITY;
+        // What is left (top_k values and their ties) usually fits one element a thread: each thread counts
+        // the survivors of its run, a prefix sum gives their places in index order, and the rest of the
+        // kernel walks a list of at most 1,024 elements in shared memory instead of the whole row.
+        unsigned long long keepers = 0;
+        for (int k = 0; k < seg; ++k) {
+            float& v = x[(size_t)k * THREADS + tid];
+            if (order_key(v) < cut) v = -INFINITY;
+            else if (v != -INFINITY) ++keepers;
+        }
+        unsigned long long n_left;
+        unsigned long long at = block_excl_scan(keepers, sh, &n_left);
+        if (n_left <= THREADS) {
+            sh.cval[tid] = -INFINITY;
+            sh.cidx[tid] = 0;
+            __syncthreads();
+            for (int k = 0; k < seg && keepers; ++k) {
+                const float v = x[(size_t)k * THREADS + tid];
+                if (v != -INFINITY) {
+                    sh.cval[at] = v;
+                    sh.cidx[at] = tid * seg + k;
+                    ++at;
+                }
+            }
+            compact = true;
+        }
         __syncthreads();
     }
 
-    // 6. softmax masses in fixed point; each thread owns a run of indices
-    float* xr = x + tid;                               // this thread's run: xr[k * THREADS], index tid * seg + k
+    // 6. softmax masses in fixed point; each thread owns a run of indices (or one element of the list)
+    float* xr = compact ? sh.cval + tid : x + tid;     // this thread's run: xr[k * THREADS], index tid * seg + k
+    if (compact) seg = 1;
     unsigned long long mine = 0;
     for (int k = 0; k < seg; ++k) {
         const float v = xr[(size_t)k * THREADS];
@@ -378,7 +406,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             const unsigned long long qv = fixed40(xr[(size_t)k * THREADS]);
             if (qv == 0) continue;
             c += qv;
-            if (r < c) { sh.result = tid * seg + k; break; }
+            if (r < c) { sh.result = compact ? sh.cidx[tid] : tid * seg + k; break; }
         }
     }
     __syncthreads();
