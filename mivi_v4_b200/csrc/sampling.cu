@@ -133,15 +133,125 @@ __device__ __forceinline__ void block_argmax_first(float best, int besti, Shared
     }
 }
 
-__global__ void __launch_bounds__(THREADS)
-sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
-              float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
-              float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
-              unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
-              int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out) {
-    mv_pdl_begin();
-    __shared__ Shared sh;
-    const int b = blockIdx.x, tid = threadIdx.x;
+// The end of a row's sampling, from values that temperature, min-p and top-k have been through: softmax
+// masses, nucleus, draw.  Thread t owns the run xr[k * THREADS], k < seg, of indices t * seg + k - or, with
+// ``compact``, the one element sh.cval[t] of the list of what top-k left, whose index is sh.cidx[t].
+__device__ void sample_tail(Shared& sh, float* xr, int seg, bool compact, float mx, float top_p,
+                            unsigned long long seed, unsigned long long stream_id, int my_step,
+                            const float* __restrict__ src, float inv_t, int V, int* out_b, int* my_ring) {
+    const int tid = threadIdx.x;
+    // 6. softmax masses in fixed point; each thread owns a run of indices (or one element of the list)
+    unsigned long long mine = 0;
+    for (int k = 0; k < seg; ++k) {
+        const float v = xr[(size_t)k * THREADS];
+        const float e = v == -INFINITY ? 0.f : expf(v - mx);
+        xr[(size_t)k * THREADS] = e;
+        mine += fixed40(e);
+    }
+    unsigned long long total;
+    block_excl_scan(mine, sh, &total);
+
+    // 7. nucleus: the value at which the descending mass reaches top_p
+    float cut_e = 0.f;                    // keep e > cut_e, and the first n_take of e == cut_e
+    unsigned long long n_take = ~0ull;
+    unsigned long long kept = total;
+    if (top_p < 1.0f) {
+        const unsigned long long target = (unsigned long long)((double)top_p * (double)total);
+        if (tid == 0) { sh.sel_prefix = 0; sh.sel_mass_above = 0; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            if (tid < 256) { sh.mass[tid] = 0; sh.cnt[tid] = 0; }
+            __syncthreads();
+            const unsigned prefix = sh.sel_prefix;
+            const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+            for (int k = 0; k < seg; ++k) {
+                const float e = xr[(size_t)k * THREADS];
+                const unsigned key = __float_as_uint(e);          // e >= 0: bit order is value order
+                if (e > 0.f && (key & himask) == prefix) {
+                    atomicAdd(&sh.mass[(key >> shift) & 255u], fixed40(e));
+                    atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long above = sh.sel_mass_above;
+                int bin = 255;
+                for (; bin > 0; --bin) {
+                    if (sh.cnt[bin] && above + sh.mass[bin] >= target) break;
+                    above += sh.mass[bin];
+                }
+                sh.sel_prefix = prefix | ((unsigned)bin << shift);
+                sh.sel_mass_above = above;
+            }
+            __syncthreads();
+        }
+        cut_e = __uint_as_float(sh.sel_prefix);
+        const unsigned long long above = sh.sel_mass_above;
+        const unsigned long long qc = fixed40(cut_e);
+        if (qc == 0 || cut_e <= 0.f) {
+            n_take = ~0ull;               // nothing left to cut: keep all
+            cut_e = 0.f;
+        } else {
+            const unsigned long long need = target > above ? target - above : 1;
+            n_take = (need + qc - 1) / qc;
+            if (n_take == 0) n_take = 1;
+        }
+        // rank of this thread's first tie, in index order
+        unsigned long long ties = 0;
+        for (int k = 0; k < seg; ++k) ties += (xr[(size_t)k * THREADS] == cut_e && cut_e > 0.f) ? 1 : 0;
+        unsigned long long tie_total;
+        unsigned long long tie_rank = block_excl_scan(ties, sh, &tie_total);
+        mine = 0;
+        for (int k = 0; k < seg; ++k) {
+            const float e = xr[(size_t)k * THREADS];
+            bool keep = e > cut_e;
+            if (e == cut_e && cut_e > 0.f) { keep = tie_rank < n_take; ++tie_rank; }
+            if (!keep) xr[(size_t)k * THREADS] = 0.f;
+            else mine += fixed40(e);
+        }
+        block_excl_scan(mine, sh, &kept);
+    }
+
+    // 8. the draw: first kept index whose running mass exceeds u * kept
+    const unsigned k24 = draw24(seed, stream_id, (unsigned long long)my_step);
+    const unsigned long long lo = kept * (unsigned long long)k24;
+    const unsigned long long hi = __umul64hi(kept, (unsigned long long)k24);
+    const unsigned long long r = (hi << 40) | (lo >> 24);
+    unsigned long long dummy;
+    const unsigned long long before = block_excl_scan(mine, sh, &dummy);
+    if (tid == 0) sh.result = -1;
+    __syncthreads();
+    if (mine > 0 && before <= r && r < before + mine) {
+        unsigned long long c = before;
+        for (int k = 0; k < seg; ++k) {
+            const unsigned long long qv = fixed40(xr[(size_t)k * THREADS]);
+            if (qv == 0) continue;
+            c += qv;
+            if (r < c) { sh.result = compact ? sh.cidx[tid] : tid * seg + k; break; }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int res = sh.result;
+        if (res < 0) {                    // all mass below the fixed-point resolution: fall back to the maximum
+            res = 0;
+            for (int i = 0; i < V; ++i)
+                if (src[i] * inv_t == mx) { res = i; break; }
+        }
+        *out_b = res;
+        if (my_ring) my_ring[my_step & (RING - 1)] = res;
+    }
+}
+
+// One row, by one block of 1024 threads: see the head of the file.  ``tiles``: 32 x 33 floats a warp.
+__device__ void sample_row(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
+                           float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
+                           float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
+                           unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
+                           int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out, int b,
+                           Shared& sh, float* tiles) {
+
+    const int tid = threadIdx.x;
     const float* src = logits + (size_t)b * ld;
     int seg = (V + THREADS - 1) / THREADS;
     const int VP = seg * THREADS;
@@ -183,7 +293,6 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     // The copy, read by index and written to its place, both coalesced: a warp moves tiles of 32 threads'
     // runs x 32 elements through a 32 x 33 tile of its own in shared memory.
     {
-        extern __shared__ float tiles[];
         const int warp = tid >> 5, lane = tid & 31;
         float* tile = tiles + warp * (32 * 33);
         const int t0 = warp * 32;                       // the warp's threads: t0 .. t0 + 31
@@ -316,110 +425,21 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
         __syncthreads();
     }
 
-    // 6. softmax masses in fixed point; each thread owns a run of indices (or one element of the list)
-    float* xr = compact ? sh.cval + tid : x + tid;     // this thread's run: xr[k * THREADS], index tid * seg + k
-    if (compact) seg = 1;
-    unsigned long long mine = 0;
-    for (int k = 0; k < seg; ++k) {
-        const float v = xr[(size_t)k * THREADS];
-        const float e = v == -INFINITY ? 0.f : expf(v - mx);
-        xr[(size_t)k * THREADS] = e;
-        mine += fixed40(e);
-    }
-    unsigned long long total;
-    block_excl_scan(mine, sh, &total);
+    sample_tail(sh, compact ? sh.cval + tid : x + tid, compact ? 1 : seg, compact, mx, top_p, seed,
+                (unsigned long long)(streams ? streams[b] : b), my_step, src, inv_t, V, out + b, my_ring);
+}
 
-    // 7. nucleus: the value at which the descending mass reaches top_p
-    float cut_e = 0.f;                    // keep e > cut_e, and the first n_take of e == cut_e
-    unsigned long long n_take = ~0ull;
-    unsigned long long kept = total;
-    if (top_p < 1.0f) {
-        const unsigned long long target = (unsigned long long)((double)top_p * (double)total);
-        if (tid == 0) { sh.sel_prefix = 0; sh.sel_mass_above = 0; }
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            if (tid < 256) { sh.mass[tid] = 0; sh.cnt[tid] = 0; }
-            __syncthreads();
-            const unsigned prefix = sh.sel_prefix;
-            const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int k = 0; k < seg; ++k) {
-                const float e = xr[(size_t)k * THREADS];
-                const unsigned key = __float_as_uint(e);          // e >= 0: bit order is value order
-                if (e > 0.f && (key & himask) == prefix) {
-                    atomicAdd(&sh.mass[(key >> shift) & 255u], fixed40(e));
-                    atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
-                }
-            }
-            __syncthreads();
-            if (tid == 0) {
-                unsigned long long above = sh.sel_mass_above;
-                int bin = 255;
-                for (; bin > 0; --bin) {
-                    if (sh.cnt[bin] && above + sh.mass[bin] >= target) break;
-                    above += sh.mass[bin];
-                }
-                sh.sel_prefix = prefix | ((unsigned)bin << shift);
-                sh.sel_mass_above = above;
-            }
-            __syncthreads();
-        }
-        cut_e = __uint_as_float(sh.sel_prefix);
-        const unsigned long long above = sh.sel_mass_above;
-        const unsigned long long qc = fixed40(cut_e);
-        if (qc == 0 || cut_e <= 0.f) {
-            n_take = ~0ull;               // nothing left to cut: keep all
-            cut_e = 0.f;
-        } else {
-            const unsigned long long need = target > above ? target - above : 1;
-            n_take = (need + qc - 1) / qc;
-            if (n_take == 0) n_take = 1;
-        }
-        // rank of this thread's first tie, in index order
-        unsigned long long ties = 0;
-        for (int k = 0; k < seg; ++k) ties += (xr[(size_t)k * THREADS] == cut_e && cut_e > 0.f) ? 1 : 0;
-        unsigned long long tie_total;
-        unsigned long long tie_rank = block_excl_scan(ties, sh, &tie_total);
-        mine = 0;
-        for (int k = 0; k < seg; ++k) {
-            const float e = xr[(size_t)k * THREADS];
-            bool keep = e > cut_e;
-            if (e == cut_e && cut_e > 0.f) { keep = tie_rank < n_take; ++tie_rank; }
-            if (!keep) xr[(size_t)k * THREADS] = 0.f;
-            else mine += fixed40(e);
-        }
-        block_excl_scan(mine, sh, &kept);
-    }
-
-    // 8. the draw: first kept index whose running mass exceeds u * kept
-    const unsigned k24 = draw24(seed, (unsigned long long)(streams ? streams[b] : b),
-                                (unsigned long long)(steps ? steps[b] : 0));
-    const unsigned long long lo = kept * (unsigned long long)k24;
-    const unsigned long long hi = __umul64hi(kept, (unsigned long long)k24);
-    const unsigned long long r = (hi << 40) | (lo >> 24);
-    unsigned long long dummy;
-    const unsigned long long before = block_excl_scan(mine, sh, &dummy);
-    if (tid == 0) sh.result = -1;
-    __syncthreads();
-    if (mine > 0 && before <= r && r < before + mine) {
-        unsigned long long c = before;
-        for (int k = 0; k < seg; ++k) {
-            const unsigned long long qv = fixed40(xr[(size_t)k * THREADS]);
-            if (qv == 0) continue;
-            c += qv;
-            if (r < c) { sh.result = compact ? sh.cidx[tid] : tid * seg + k; break; }
-        }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int res = sh.result;
-        if (res < 0) {                    // all mass below the fixed-point resolution: fall back to the maximum
-            res = 0;
-            for (int i = 0; i < V; ++i)
-                if (src[i] * inv_t == mx) { res = i; break; }
-        }
-        out[b] = res;
-        if (my_ring) my_ring[my_step & (RING - 1)] = res;
-    }
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
+              float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
+              float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
+              unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
+              int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out) {
+    mv_pdl_begin();
+    __shared__ Shared sh;
+    extern __shared__ float tiles[];
+    sample_row(logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen, pres_pen, freq_pen, recent, n_recent,
+               seed, streams, steps, ring, ring_row, out, (int)blockIdx.x, sh, tiles);
 }
 
 }  // namespace
