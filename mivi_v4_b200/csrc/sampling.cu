@@ -23,7 +23,11 @@
 // run and for every thread layout.  The nucleus is the shortest prefix in
 // descending probability (ties: lower index first) whose mass reaches top_p;
 // the draw walks the kept tokens in index order.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -442,6 +446,186 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
                seed, streams, steps, ring, ring_row, out, (int)blockIdx.x, sh, tiles);
 }
 
+
+// ---------------------------------------------------------------------------
+// The same for the usual case of a small top_k (1 ... 1024), by a CLUSTER of 8 blocks a row: the row's
+// values are spread over the registers of 8,192 threads (8 each at a vocabulary of 65,536), so penalties,
+// temperature, min-p and the four passes of the top-k radix select touch no memory at all; the blocks
+// exchange a maximum, four histograms and their survivor counts through distributed shared memory.  What
+// top-k leaves is gathered, in index order, into the first block's list, and that block runs sample_tail.
+// Every block takes the same decisions from the same sums, so there is one cluster barrier a step.  If more
+// than 1,024 values survive (a wall of ties at the k-th value) the first block does the whole row the slow way.
+// ---------------------------------------------------------------------------
+constexpr int CL = 8;
+constexpr int VPT_MAX = 16;            // values a thread: vocabularies up to 8 * 1024 * 16
+
+struct ClusterShared {
+    unsigned cnt[2][256];              // this block's radix histogram; two buffers, used in turn
+    unsigned tot[256];                 // the cluster's histogram, which every block sums for itself
+    float bmax;                        // this block's maximum
+    unsigned keep;                     // how many of this block's values top-k left
+    unsigned sel_prefix, sel_remaining;
+};
+
+__global__ void __launch_bounds__(THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
+                      float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
+                      float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
+                      unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
+                      int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out) {
+    mv_pdl_begin();
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ Shared sh;
+    __shared__ ClusterShared cs;
+    extern __shared__ float tiles[];
+    const int rank = (int)cluster.block_rank(), b = blockIdx.x / CL, tid = threadIdx.x;
+    const float* src = logits + (size_t)b * ld;
+    const int vpt = (V + CL * THREADS - 1) / (CL * THREADS);
+    const int i0 = (rank * THREADS + tid) * vpt;          // this thread's indices: i0 ... i0 + vpt - 1
+
+    float v[VPT_MAX];
+#pragma unroll
+    for (int k = 0; k < VPT_MAX; ++k) v[k] = (k < vpt && i0 + k < V) ? src[i0 + k] : -INFINITY;
+
+    // 1. penalties, once per distinct recent token, by the thread that holds the token's logit
+    int* my_ring = ring ? ring + (size_t)ring_row[b] * RING : nullptr;
+    const int my_step = steps ? steps[b] : 0;
+    const int nr = my_ring ? min(my_step, RECENT_MAX) : (n_recent ? min(n_recent[b], RECENT_MAX) : 0);
+    const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
+    if (pen) {
+        auto rc_at = [&](int j) {
+            return my_ring ? my_ring[(my_step - 1 - j) & (RING - 1)] : recent[(size_t)b * RECENT_MAX + j];
+        };
+        for (int j = 0; j < nr; ++j) {
+            const int tok = rc_at(j), k0 = tok - i0;
+            if (k0 < 0 || k0 >= vpt || tok >= V) continue;
+            bool first = true;
+            int count = 0;
+            for (int jj = 0; jj < nr; ++jj) {
+                if (rc_at(jj) == tok) {
+                    if (jj < j) first = false;
+                    ++count;
+                }
+            }
+            if (!first) continue;
+#pragma unroll
+            for (int k = 0; k < VPT_MAX; ++k) {
+                if (k == k0) {
+                    float x = v[k];
+                    if (rep_pen > 0.f && rep_pen != 1.f) x = x > 0.f ? x / rep_pen : x * rep_pen;
+                    if (pres_pen != 0.f) x -= pres_pen;
+                    if (freq_pen != 0.f) x -= freq_pen * (float)count;
+                    v[k] = x;
+                }
+            }
+        }
+    }
+
+    // 3. temperature, maximum over the cluster
+    const float inv_t = 1.0f / temperature;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT_MAX; ++k) {
+        v[k] *= inv_t;
+        mx = fmaxf(mx, v[k]);
+    }
+    mx = block_max(mx, sh);
+    if (tid == 0) cs.bmax = mx;
+    if (rank == 0) {                                      // the list that the survivors will be gathered into
+        sh.cval[tid] = -INFINITY;
+        sh.cidx[tid] = 0;
+    }
+    cluster.sync();
+#pragma unroll
+    for (int rr = 0; rr < CL; ++rr) mx = fmaxf(mx, *cluster.map_shared_rank(&cs.bmax, rr));
+
+    // 4. min-p
+    if (min_p > 0.f && min_p < 1.f) {
+        const float thr = mx + logf(min_p);
+#pragma unroll
+        for (int k = 0; k < VPT_MAX; ++k)
+            if (v[k] < thr) v[k] = -INFINITY;
+    }
+
+    // 5. top-k: radix select of the k-th largest value over the cluster, ties at it are kept
+    unsigned prefix = 0, remaining = (unsigned)top_k;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass, buf = pass & 1;
+        if (tid < 256) cs.cnt[buf][tid] = 0;
+        __syncthreads();
+        const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+#pragma unroll
+        for (int k = 0; k < VPT_MAX; ++k) {
+            if (k < vpt) {
+                const unsigned key = order_key(v[k]);
+                if ((key & himask) == prefix) atomicAdd(&cs.cnt[buf][(key >> shift) & 255u], 1u);
+            }
+        }
+        cluster.sync();                                   // (a block barrier too)
+        if (tid < 256) {
+            unsigned t = 0;
+#pragma unroll
+            for (int rr = 0; rr < CL; ++rr) t += *cluster.map_shared_rank(&cs.cnt[buf][tid], rr);
+            cs.tot[tid] = t;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned rem = remaining;
+            int bin = 255;
+            for (; bin > 0; --bin) {
+                if (cs.tot[bin] >= rem) break;
+                rem -= cs.tot[bin];
+            }
+            cs.sel_prefix = prefix | ((unsigned)bin << shift);
+            cs.sel_remaining = rem;
+        }
+        __syncthreads();
+        prefix = cs.sel_prefix;
+        remaining = cs.sel_remaining;
+    }
+    const unsigned cut = prefix;
+    unsigned long long keepers = 0;
+#pragma unroll
+    for (int k = 0; k < VPT_MAX; ++k) {
+        if (order_key(v[k]) < cut) v[k] = -INFINITY;
+        else if (v[k] != -INFINITY) ++keepers;
+    }
+    unsigned long long n_block;
+    unsigned long long at = block_excl_scan(keepers, sh, &n_block);
+    if (tid == 0) cs.keep = (unsigned)n_block;
+    cluster.sync();
+    unsigned base = 0, n_left = 0;
+#pragma unroll
+    for (int rr = 0; rr < CL; ++rr) {
+        const unsigned c = *cluster.map_shared_rank(&cs.keep, rr);
+        if (rr < rank) base += c;
+        n_left += c;
+    }
+    if (n_left <= (unsigned)THREADS) {
+        // the survivors, in index order (blocks, then threads, then a thread's values), into the first block's list
+        float* cval0 = cluster.map_shared_rank(sh.cval, 0);
+        int* cidx0 = cluster.map_shared_rank(sh.cidx, 0);
+        unsigned place = base + (unsigned)at;
+#pragma unroll
+        for (int k = 0; k < VPT_MAX; ++k) {
+            if (v[k] != -INFINITY) {
+                cval0[place] = v[k];
+                cidx0[place] = i0 + k;
+                ++place;
+            }
+        }
+    }
+    cluster.sync();                                       // after it nobody touches another block's memory
+    if (rank != 0) return;
+    if (n_left <= (unsigned)THREADS) {
+        sample_tail(sh, sh.cval + tid, 1, true, mx, top_p, seed, (unsigned long long)(streams ? streams[b] : b), my_step,
+                    src, inv_t, V, out + b, my_ring);
+    } else {
+        sample_row(logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen, pres_pen, freq_pen, recent, n_recent,
+                   seed, streams, steps, ring, ring_row, out, b, sh, tiles);
+    }
+}
+
 }  // namespace
 
 MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int V, float temperature,
@@ -454,6 +638,36 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
     if (!attr_set) {
         cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
         attr_set = true;
+    }
+    // a small top_k over a vocabulary that 8,192 threads can hold: the cluster kernel
+    if (temperature > 0.f && top_k > 0 && top_k < V && top_k <= THREADS && V <= CL * THREADS * VPT_MAX) {
+        static bool attr2_set = false;
+        if (!attr2_set) {
+            cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
+            attr2_set = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)B * CL);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = TILES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = CL;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+        if (mv_pdl_enabled()) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = na;
+        cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
+                           pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out);
+        return mv_launch_status();
     }
     mv_launch(sample_kernel, B, THREADS, TILES, stream, logits, ld, work, V, temperature, top_k, top_p, min_p,
               rep_pen, pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out);

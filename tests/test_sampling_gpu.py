@@ -41,7 +41,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("kw", CASES, ids=[str(i) for i in range(len(CASES))])
-@pytest.mark.parametrize("V", [301, 4100])
+@pytest.mark.parametrize("V", [301, 4100, 65536])
 def test_sample_matches_plain(kw, V):
     g = torch.Generator().manual_seed(V)
     B = 6
@@ -119,3 +119,20 @@ def test_recent_tokens_kept_on_the_device(kw):
         for b in range(B):
             history[b].append(got[b])
     assert len(set(history[0])) > 5                       # the penalties did spread the tokens
+
+
+@pytest.mark.parametrize("V", [4100, 70000])
+def test_top_k_with_a_wall_of_ties(V):
+    """More values tie at the k-th place than the kernel's list of survivors holds (rows of equal
+    logits, and a row with 2,000 equal maxima): the row is then sampled the slow way, with the same result."""
+    kw = dict(temperature=1.0, top_k=5, top_p=0.9)
+    logits = torch.zeros(3, V)
+    logits[1, ::2] = 1.0
+    g = torch.Generator().manual_seed(1)
+    logits[2] = torch.randn(V, generator=g)
+    logits[2, 100:2100] = 9.0
+    seed, streams, steps = 7, [0, 1, 2], [3, 4, 5]
+    got = run_kernel(logits, seed, streams, steps, [[], [], []], **kw)
+    for b in range(3):
+        want = P.plain_sample(logits[b], recent=[], u=P.plain_uniform(seed, streams[b], steps[b]), **kw)
+        assert got[b] == want, (b, got[b], want)
