@@ -114,6 +114,84 @@ __device__ unsigned long long block_excl_scan(unsigned long long v, Shared& sh, 
     return sh.wsum[warp] + inc - v;
 }
 
+// Walking 256 radix bins from the top by ONE WARP (every lane calls these, lane l holds bins 8l ... 8l+7)
+// instead of one thread: the sums of the bins above a lane come from a shuffle scan, each lane walks its own
+// eight bins with them, and the highest lane that finds the bin wins - the bin a single thread would find.
+//
+// select_count: the highest bin b >= 1 with cnt[b] >= rem - (sum of the bins above b); bin 0 if there is none.
+// rem_out: rem less the sum of the bins above the chosen one.
+__device__ __forceinline__ void select_count(const unsigned* cnt, unsigned rem, unsigned& bin_out, unsigned& rem_out) {
+    const int lane = threadIdx.x & 31;
+    unsigned c[8], s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { c[i] = cnt[8 * lane + i]; s += c[i]; }
+    unsigned t = s;                                       // sum over this lane and the lanes above it
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned u = __shfl_down_sync(0xffffffffu, t, o);
+        if (lane + o < 32) t += u;
+    }
+    unsigned above = t - s;
+    int found = -1;
+    unsigned left = 0;
+#pragma unroll
+    for (int i = 7; i >= 0; --i) {
+        const int b = 8 * lane + i;
+        if (found < 0 && b > 0 && above < rem) {
+            if (c[i] >= rem - above) { found = b; left = rem - above; }
+            else above += c[i];
+        }
+    }
+    const unsigned hits = __ballot_sync(0xffffffffu, found >= 0);
+    if (hits) {
+        const int src = 31 - __clz(hits);
+        bin_out = (unsigned)__shfl_sync(0xffffffffu, found, src);
+        rem_out = __shfl_sync(0xffffffffu, left, src);
+    } else {
+        const unsigned all = __shfl_sync(0xffffffffu, t, 0), c0 = __shfl_sync(0xffffffffu, c[0], 0);
+        bin_out = 0;
+        rem_out = rem - (all - c0);
+    }
+}
+// select_mass: the highest bin b >= 1 that holds something (cnt[b] > 0) and whose mass brings the mass above
+// it (above0 plus the bins above b) to the target; bin 0 if there is none.  above_out: the mass above it.
+__device__ __forceinline__ void select_mass(const unsigned* cnt, const unsigned long long* mass,
+                                            unsigned long long above0, unsigned long long target, unsigned& bin_out,
+                                            unsigned long long& above_out) {
+    const int lane = threadIdx.x & 31;
+    unsigned long long m[8], s = 0;
+    unsigned c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { c[i] = cnt[8 * lane + i]; m[i] = mass[8 * lane + i]; s += m[i]; }
+    unsigned long long t = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long u = __shfl_down_sync(0xffffffffu, t, o);
+        if (lane + o < 32) t += u;
+    }
+    unsigned long long above = above0 + (t - s);
+    int found = -1;
+    unsigned long long at = 0;
+#pragma unroll
+    for (int i = 7; i >= 0; --i) {
+        const int b = 8 * lane + i;
+        if (found < 0 && b > 0) {
+            if (c[i] && above + m[i] >= target) { found = b; at = above; }
+            else above += m[i];
+        }
+    }
+    const unsigned hits = __ballot_sync(0xffffffffu, found >= 0);
+    if (hits) {
+        const int src = 31 - __clz(hits);
+        bin_out = (unsigned)__shfl_sync(0xffffffffu, found, src);
+        above_out = __shfl_sync(0xffffffffu, at, src);
+    } else {
+        const unsigned long long all = __shfl_sync(0xffffffffu, t, 0), m0 = __shfl_sync(0xffffffffu, m[0], 0);
+        bin_out = 0;
+        above_out = above0 + (all - m0);
+    }
+}
+
 // The largest value of the block and, among equal ones, its smallest index, to *dst.
 __device__ __forceinline__ void block_argmax_first(float best, int besti, Shared& sh, int* dst) {
     const int tid = threadIdx.x;
@@ -177,15 +255,15 @@ __device__ void sample_tail(Shared& sh, float* xr, int seg, bool compact, float 
                 }
             }
             __syncthreads();
-            if (tid == 0) {
-                unsigned long long above = sh.sel_mass_above;
-                int bin = 255;
-                for (; bin > 0; --bin) {
-                    if (sh.cnt[bin] && above + sh.mass[bin] >= target) break;
-                    above += sh.mass[bin];
+            if (tid < 32) {
+                unsigned bin;
+                unsigned long long above;
+                select_mass(sh.cnt, sh.mass, sh.sel_mass_above, target, bin, above);
+                __syncwarp();
+                if (tid == 0) {
+                    sh.sel_prefix = prefix | (bin << shift);
+                    sh.sel_mass_above = above;
                 }
-                sh.sel_prefix = prefix | ((unsigned)bin << shift);
-                sh.sel_mass_above = above;
             }
             __syncthreads();
         }
@@ -388,15 +466,14 @@ __device__ void sample_row(const float* __restrict__ logits, long long ld, float
                 if ((key & himask) == prefix) atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
             }
             __syncthreads();
-            if (tid == 0) {
-                unsigned rem = sh.sel_remaining;
-                int bin = 255;
-                for (; bin > 0; --bin) {
-                    if (sh.cnt[bin] >= rem) break;
-                    rem -= sh.cnt[bin];
+            if (tid < 32) {
+                unsigned bin, rem;
+                select_count(sh.cnt, sh.sel_remaining, bin, rem);
+                __syncwarp();
+                if (tid == 0) {
+                    sh.sel_prefix = prefix | (bin << shift);
+                    sh.sel_remaining = rem;
                 }
-                sh.sel_prefix = prefix | ((unsigned)bin << shift);
-                sh.sel_remaining = rem;
             }
             __syncthreads();
         }
@@ -569,15 +646,13 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __r
             cs.tot[tid] = t;
         }
         __syncthreads();
-        if (tid == 0) {
-            unsigned rem = remaining;
-            int bin = 255;
-            for (; bin > 0; --bin) {
-                if (cs.tot[bin] >= rem) break;
-                rem -= cs.tot[bin];
+        if (tid < 32) {
+            unsigned bin, rem;
+            select_count(cs.tot, remaining, bin, rem);
+            if (tid == 0) {
+                cs.sel_prefix = prefix | (bin << shift);
+                cs.sel_remaining = rem;
             }
-            cs.sel_prefix = prefix | ((unsigned)bin << shift);
-            cs.sel_remaining = rem;
         }
         __syncthreads();
         prefix = cs.sel_prefix;
