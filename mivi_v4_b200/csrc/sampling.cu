@@ -192,6 +192,24 @@ __device__ __forceinline__ void select_mass(const unsigned* cnt, const unsigned 
     }
 }
 
+// *p += x on a 64-bit word of shared memory by two native 32-bit atomics (the 64-bit one is a compare-and-swap
+// loop): the add that wraps the low word carries into the high word.  Exact once all adds have been made.
+__device__ __forceinline__ void add64(unsigned long long* p, unsigned long long x) {
+    unsigned* w = reinterpret_cast<unsigned*>(p);
+    const unsigned xl = (unsigned)x, xh = (unsigned)(x >> 32);
+    const unsigned old = atomicAdd(w, xl);
+    const unsigned up = xh + ((old + xl < old) ? 1u : 0u);
+    if (up) atomicAdd(w + 1, up);
+}
+// mass[bin] += q and cnt[bin] += 1 where ``on``
+__device__ __forceinline__ void hist_add(unsigned long long* mass, unsigned* cnt, bool on, unsigned bin,
+                                         unsigned long long q) {
+    if (on) {
+        add64(&mass[bin], q);
+        atomicAdd(&cnt[bin], 1u);
+    }
+}
+
 // The largest value of the block and, among equal ones, its smallest index, to *dst.
 __device__ __forceinline__ void block_argmax_first(float best, int besti, Shared& sh, int* dst) {
     const int tid = threadIdx.x;
@@ -249,10 +267,7 @@ __device__ void sample_tail(Shared& sh, float* xr, int seg, bool compact, float 
             for (int k = 0; k < seg; ++k) {
                 const float e = xr[(size_t)k * THREADS];
                 const unsigned key = __float_as_uint(e);          // e >= 0: bit order is value order
-                if (e > 0.f && (key & himask) == prefix) {
-                    atomicAdd(&sh.mass[(key >> shift) & 255u], fixed40(e));
-                    atomicAdd(&sh.cnt[(key >> shift) & 255u], 1u);
-                }
+                hist_add(sh.mass, sh.cnt, e > 0.f && (key & himask) == prefix, (key >> shift) & 255u, fixed40(e));
             }
             __syncthreads();
             if (tid < 32) {
@@ -532,6 +547,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
 // top-k leaves is gathered, in index order, into the first block's list, and that block runs sample_tail.
 // Every block takes the same decisions from the same sums, so there is one cluster barrier a step.  If more
 // than 1,024 values survive (a wall of ties at the k-th value) the first block does the whole row the slow way.
+// Without top_k the row stays in the registers to the end (cluster_tail): masses, the nucleus' four passes
+// and the draw exchange a block's sums and histograms the same way.
 // ---------------------------------------------------------------------------
 constexpr int CL = 8;
 constexpr int VPT_MAX = 16;            // values a thread: vocabularies up to 8 * 1024 * 16
@@ -542,7 +559,158 @@ struct ClusterShared {
     float bmax;                        // this block's maximum
     unsigned keep;                     // how many of this block's values top-k left
     unsigned sel_prefix, sel_remaining;
+    // without top-k (cluster_tail)
+    unsigned long long mass[2][256];   // this block's histogram of masses, as cnt
+    unsigned long long mtot[256];      // the cluster's
+    unsigned long long xch[3];         // this block's sums, one place for each exchange
+    unsigned long long sel_above;
+    int result;                        // the first block's: the drawn index, written by the block that finds it
 };
+
+// A sum over the cluster of one value a block (thread 0 of each block passes it on): the total, and in
+// ``below`` the sum of the blocks before this one.  Each call has a place of its own, so none waits for the last.
+__device__ __forceinline__ unsigned long long cluster_sum(cg::cluster_group& cluster, ClusterShared& cs, int place,
+                                                          unsigned long long mine, int rank,
+                                                          unsigned long long& below) {
+    if (threadIdx.x == 0) cs.xch[place] = mine;
+    cluster.sync();
+    unsigned long long total = 0;
+    below = 0;
+#pragma unroll
+    for (int rr = 0; rr < CL; ++rr) {
+        const unsigned long long c = *cluster.map_shared_rank(&cs.xch[place], rr);
+        if (rr < rank) below += c;
+        total += c;
+    }
+    return total;
+}
+
+// sample_tail for a row that lies in the registers of the cluster (no top-k): v holds this thread's values
+// after temperature and min-p, indices i0 ... i0 + vpt - 1, in the order (block, thread, k).  The same sums
+// in the same fixed point as sample_tail, so the same token.
+__device__ __forceinline__ void cluster_tail(cg::cluster_group& cluster, Shared& sh, ClusterShared& cs,
+                                             float (&v)[VPT_MAX], int vpt, int i0, int rank, float mx, float top_p,
+                                             unsigned long long seed, unsigned long long stream_id, int my_step,
+                                             const float* __restrict__ src, float inv_t, int V, int* out_b,
+                                             int* my_ring) {
+    const int tid = threadIdx.x;
+    unsigned long long mine = 0;
+#pragma unroll
+    for (int k = 0; k < VPT_MAX; ++k) {
+        const float e = v[k] == -INFINITY ? 0.f : expf(v[k] - mx);
+        v[k] = e;
+        mine += fixed40(e);
+    }
+    if (rank == 0 && tid == 0) cs.result = -1;
+    unsigned long long in_block, below;
+    unsigned long long at = block_excl_scan(mine, sh, &in_block);
+    const unsigned long long total = cluster_sum(cluster, cs, 0, in_block, rank, below);
+    unsigned long long kept = total;
+
+    if (top_p < 1.0f) {
+        const unsigned long long target = (unsigned long long)((double)top_p * (double)total);
+        unsigned prefix = 0;
+        unsigned long long above = 0;
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass, buf = pass & 1;
+            if (tid < 256) { cs.mass[buf][tid] = 0; cs.cnt[buf][tid] = 0; }
+            __syncthreads();
+            const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+#pragma unroll
+            for (int k = 0; k < VPT_MAX; ++k) {
+                if (k < vpt) {
+                    const unsigned key = __float_as_uint(v[k]);
+                    hist_add(cs.mass[buf], cs.cnt[buf], v[k] > 0.f && (key & himask) == prefix, (key >> shift) & 255u,
+                             fixed40(v[k]));
+                }
+            }
+            cluster.sync();
+            if (tid < 256) {
+                unsigned c = 0;
+                unsigned long long m = 0;
+#pragma unroll
+                for (int rr = 0; rr < CL; ++rr) {
+                    c += *cluster.map_shared_rank(&cs.cnt[buf][tid], rr);
+                    m += *cluster.map_shared_rank(&cs.mass[buf][tid], rr);
+                }
+                cs.tot[tid] = c;
+                cs.mtot[tid] = m;
+            }
+            __syncthreads();
+            if (tid < 32) {
+                unsigned bin;
+                unsigned long long ab;
+                select_mass(cs.tot, cs.mtot, above, target, bin, ab);
+                if (tid == 0) {
+                    cs.sel_prefix = prefix | (bin << shift);
+                    cs.sel_above = ab;
+                }
+            }
+            __syncthreads();
+            prefix = cs.sel_prefix;
+            above = cs.sel_above;
+        }
+        float cut_e = __uint_as_float(prefix);
+        unsigned long long n_take;
+        const unsigned long long qc = fixed40(cut_e);
+        if (qc == 0 || cut_e <= 0.f) {
+            n_take = ~0ull;
+            cut_e = 0.f;
+        } else {
+            const unsigned long long need = target > above ? target - above : 1;
+            n_take = (need + qc - 1) / qc;
+            if (n_take == 0) n_take = 1;
+        }
+        unsigned long long ties = 0;
+#pragma unroll
+        for (int k = 0; k < VPT_MAX; ++k) ties += (v[k] == cut_e && cut_e > 0.f) ? 1 : 0;
+        unsigned long long ties_block, ties_below;
+        unsigned long long tie_rank = block_excl_scan(ties, sh, &ties_block);
+        cluster_sum(cluster, cs, 1, ties_block, rank, ties_below);
+        tie_rank += ties_below;
+        mine = 0;
+#pragma unroll
+        for (int k = 0; k < VPT_MAX; ++k) {
+            const float e = v[k];
+            bool keep = e > cut_e;
+            if (e == cut_e && cut_e > 0.f) { keep = tie_rank < n_take; ++tie_rank; }
+            if (!keep) v[k] = 0.f;
+            else mine += fixed40(e);
+        }
+        at = block_excl_scan(mine, sh, &in_block);
+        kept = cluster_sum(cluster, cs, 2, in_block, rank, below);
+    }
+
+    const unsigned k24 = draw24(seed, stream_id, (unsigned long long)my_step);
+    const unsigned long long lo = kept * (unsigned long long)k24;
+    const unsigned long long hi = __umul64hi(kept, (unsigned long long)k24);
+    const unsigned long long r = (hi << 40) | (lo >> 24);
+    const unsigned long long before = below + at;
+    if (mine > 0 && before <= r && r < before + mine) {
+        unsigned long long c = before;
+        int found = -1;
+#pragma unroll
+        for (int k = 0; k < VPT_MAX; ++k) {
+            const unsigned long long qv = fixed40(v[k]);
+            if (found < 0 && qv != 0) {
+                c += qv;
+                if (r < c) found = i0 + k;
+            }
+        }
+        *cluster.map_shared_rank(&cs.result, 0) = found;
+    }
+    cluster.sync();                                       // after it nobody touches another block's memory
+    if (rank == 0 && tid == 0) {
+        int res = cs.result;
+        if (res < 0) {                    // all mass below the fixed-point resolution: fall back to the maximum
+            res = 0;
+            for (int i = 0; i < V; ++i)
+                if (src[i] * inv_t == mx) { res = i; break; }
+        }
+        *out_b = res;
+        if (my_ring) my_ring[my_step & (RING - 1)] = res;
+    }
+}
 
 __global__ void __launch_bounds__(THREADS)
 sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
@@ -622,6 +790,12 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __r
 #pragma unroll
         for (int k = 0; k < VPT_MAX; ++k)
             if (v[k] < thr) v[k] = -INFINITY;
+    }
+
+    if (top_k <= 0 || top_k >= V) {                       // no top-k: the row stays in the cluster's registers
+        cluster_tail(cluster, sh, cs, v, vpt, i0, rank, mx, top_p, seed, (unsigned long long)(streams ? streams[b] : b),
+                     my_step, src, inv_t, V, out + b, my_ring);
+        return;
     }
 
     // 5. top-k: radix select of the k-th largest value over the cluster, ties at it are kept
@@ -714,8 +888,9 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
         cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
         attr_set = true;
     }
-    // a small top_k over a vocabulary that 8,192 threads can hold: the cluster kernel
-    if (temperature > 0.f && top_k > 0 && top_k < V && top_k <= THREADS && V <= CL * THREADS * VPT_MAX) {
+    // no top_k, or a small one, over a vocabulary that 8,192 threads can hold: the cluster kernel
+    const bool no_k = top_k <= 0 || top_k >= V;
+    if (temperature > 0.f && (no_k || top_k <= THREADS) && V <= CL * THREADS * VPT_MAX) {
         static bool attr2_set = false;
         if (!attr2_set) {
             cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);

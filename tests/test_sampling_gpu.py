@@ -121,11 +121,15 @@ def test_recent_tokens_kept_on_the_device(kw):
     assert len(set(history[0])) > 5                       # the penalties did spread the tokens
 
 
-@pytest.mark.parametrize("V", [4100, 70000])
-def test_top_k_with_a_wall_of_ties(V):
+@pytest.mark.parametrize("kw", [dict(temperature=1.0, top_k=5, top_p=0.9), dict(temperature=1.0, top_p=0.9),
+                                dict(temperature=0.7), dict(temperature=1.0, top_k=2000, top_p=0.33333)],
+                         ids=["top_k_top_p", "top_p", "temperature", "large_top_k"])
+@pytest.mark.parametrize("V", [4100, 70000, 131072, 140001])
+def test_top_k_with_a_wall_of_ties(V, kw):
     """More values tie at the k-th place than the kernel's list of survivors holds (rows of equal
-    logits, and a row with 2,000 equal maxima): the row is then sampled the slow way, with the same result."""
-    kw = dict(temperature=1.0, top_k=5, top_p=0.9)
+    logits, and a row with 2,000 equal maxima): the row is then sampled the slow way, with the same result.
+    Without top_k the nucleus' edge falls into the wall, and the ties are counted in index order across
+    the blocks that share a row; the largest vocabulary is one that those blocks cannot hold."""
     logits = torch.zeros(3, V)
     logits[1, ::2] = 1.0
     g = torch.Generator().manual_seed(1)
