@@ -565,6 +565,9 @@ struct ClusterShared {
     unsigned long long xch[3];         // this block's sums, one place for each exchange
     unsigned long long sel_above;
     int result;                        // the first block's: the drawn index, written by the block that finds it
+    int rec[RECENT_MAX];               // the recent tokens, newest first
+    int pen_tok[RECENT_MAX];           // each distinct one at its first place (-1 elsewhere) ...
+    int pen_cnt[RECENT_MAX];           // ... and how often it occurs
 };
 
 // A sum over the cluster of one value a block (thread 0 of each block passes it on): the total, and in
@@ -737,22 +740,30 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __r
     const int my_step = steps ? steps[b] : 0;
     const int nr = my_ring ? min(my_step, RECENT_MAX) : (n_recent ? min(n_recent[b], RECENT_MAX) : 0);
     const bool pen = nr > 0 && ((rep_pen > 0.f && rep_pen != 1.f) || pres_pen != 0.f || freq_pen != 0.f);
-    if (pen) {
-        auto rc_at = [&](int j) {
-            return my_ring ? my_ring[(my_step - 1 - j) & (RING - 1)] : recent[(size_t)b * RECENT_MAX + j];
-        };
-        for (int j = 0; j < nr; ++j) {
-            const int tok = rc_at(j), k0 = tok - i0;
-            if (k0 < 0 || k0 >= vpt || tok >= V) continue;
-            bool first = true;
+    if (pen) {                                            // (pen and nr are the same for the whole block)
+        // the recent tokens into shared memory, each distinct one once with its count: 64 loads side by side
+        // instead of 64 one after another in every thread
+        if (tid < RECENT_MAX) cs.rec[tid] = tid < nr ? (my_ring ? my_ring[(my_step - 1 - tid) & (RING - 1)]
+                                                                : recent[(size_t)b * RECENT_MAX + tid]) : -1;
+        __syncthreads();
+        if (tid < nr) {
+            const int tok = cs.rec[tid];
+            bool first = tok >= 0 && tok < V;
             int count = 0;
-            for (int jj = 0; jj < nr; ++jj) {
-                if (rc_at(jj) == tok) {
-                    if (jj < j) first = false;
+            for (int j = 0; j < nr; ++j) {
+                if (cs.rec[j] == tok) {
+                    if (j < tid) first = false;
                     ++count;
                 }
             }
-            if (!first) continue;
+            cs.pen_tok[tid] = first ? tok : -1;
+            cs.pen_cnt[tid] = count;
+        }
+        __syncthreads();
+        for (int j = 0; j < nr; ++j) {
+            const int tok = cs.pen_tok[j], k0 = tok - i0;
+            if (tok < 0 || k0 < 0 || k0 >= vpt) continue;
+            const int count = cs.pen_cnt[j];
 #pragma unroll
             for (int k = 0; k < VPT_MAX; ++k) {
                 if (k == k0) {
