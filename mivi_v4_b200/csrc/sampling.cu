@@ -550,7 +550,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
 // Without top_k the row stays in the registers to the end (cluster_tail): masses, the nucleus' four passes
 // and the draw exchange a block's sums and histograms the same way.
 // ---------------------------------------------------------------------------
-constexpr int CL = 8;
+constexpr int CL_MAX = 8;             // blocks a row: 8, or 4 when more rows come than the GPU holds clusters of 8 at once
 constexpr int VPT_MAX = 16;            // values a thread: vocabularies up to 8 * 1024 * 16
 
 struct ClusterShared {
@@ -572,6 +572,7 @@ struct ClusterShared {
 
 // A sum over the cluster of one value a block (thread 0 of each block passes it on): the total, and in
 // ``below`` the sum of the blocks before this one.  Each call has a place of its own, so none waits for the last.
+template <int CL>
 __device__ __forceinline__ unsigned long long cluster_sum(cg::cluster_group& cluster, ClusterShared& cs, int place,
                                                           unsigned long long mine, int rank,
                                                           unsigned long long& below) {
@@ -591,6 +592,7 @@ __device__ __forceinline__ unsigned long long cluster_sum(cg::cluster_group& clu
 // sample_tail for a row that lies in the registers of the cluster (no top-k): v holds this thread's values
 // after temperature and min-p, indices i0 ... i0 + vpt - 1, in the order (block, thread, k).  The same sums
 // in the same fixed point as sample_tail, so the same token.
+template <int CL>
 __device__ __forceinline__ void cluster_tail(cg::cluster_group& cluster, Shared& sh, ClusterShared& cs,
                                              float (&v)[VPT_MAX], int vpt, int i0, int rank, float mx, float top_p,
                                              unsigned long long seed, unsigned long long stream_id, int my_step,
@@ -607,7 +609,7 @@ __device__ __forceinline__ void cluster_tail(cg::cluster_group& cluster, Shared&
     if (rank == 0 && tid == 0) cs.result = -1;
     unsigned long long in_block, below;
     unsigned long long at = block_excl_scan(mine, sh, &in_block);
-    const unsigned long long total = cluster_sum(cluster, cs, 0, in_block, rank, below);
+    const unsigned long long total = cluster_sum<CL>(cluster, cs, 0, in_block, rank, below);
     unsigned long long kept = total;
 
     if (top_p < 1.0f) {
@@ -669,7 +671,7 @@ __device__ __forceinline__ void cluster_tail(cg::cluster_group& cluster, Shared&
         for (int k = 0; k < VPT_MAX; ++k) ties += (v[k] == cut_e && cut_e > 0.f) ? 1 : 0;
         unsigned long long ties_block, ties_below;
         unsigned long long tie_rank = block_excl_scan(ties, sh, &ties_block);
-        cluster_sum(cluster, cs, 1, ties_block, rank, ties_below);
+        cluster_sum<CL>(cluster, cs, 1, ties_block, rank, ties_below);
         tie_rank += ties_below;
         mine = 0;
 #pragma unroll
@@ -681,7 +683,7 @@ __device__ __forceinline__ void cluster_tail(cg::cluster_group& cluster, Shared&
             else mine += fixed40(e);
         }
         at = block_excl_scan(mine, sh, &in_block);
-        kept = cluster_sum(cluster, cs, 2, in_block, rank, below);
+        kept = cluster_sum<CL>(cluster, cs, 2, in_block, rank, below);
     }
 
     const unsigned k24 = draw24(seed, stream_id, (unsigned long long)my_step);
@@ -715,6 +717,7 @@ __device__ __forceinline__ void cluster_tail(cg::cluster_group& cluster, Shared&
     }
 }
 
+template <int CL>
 __global__ void __launch_bounds__(THREADS)
 sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
                       float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
@@ -804,7 +807,7 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __r
     }
 
     if (top_k <= 0 || top_k >= V) {                       // no top-k: the row stays in the cluster's registers
-        cluster_tail(cluster, sh, cs, v, vpt, i0, rank, mx, top_p, seed, (unsigned long long)(streams ? streams[b] : b),
+        cluster_tail<CL>(cluster, sh, cs, v, vpt, i0, rank, mx, top_p, seed, (unsigned long long)(streams ? streams[b] : b),
                      my_step, src, inv_t, V, out + b, my_ring);
         return;
     }
@@ -899,23 +902,30 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
         cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
         attr_set = true;
     }
-    // no top_k, or a small one, over a vocabulary that 8,192 threads can hold: the cluster kernel
+    // no top_k, or a small one, over a vocabulary that the cluster's threads can hold: the cluster kernel.
+    // Up to 16 rows take 8 blocks each; more rows than that would come in waves (measured at 24 rows of
+    // 65,536: 50 us with 8 blocks a row, 31 us with 4), so they take 4 blocks each if the vocabulary fits
+    // (MIVI_SAMPLE_CLUSTER forces 4 or 8).
     const bool no_k = top_k <= 0 || top_k >= V;
-    if (temperature > 0.f && (no_k || top_k <= THREADS) && V <= CL * THREADS * VPT_MAX) {
-        static bool attr2_set = false;
-        if (!attr2_set) {
-            cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
-            attr2_set = true;
+    if (temperature > 0.f && (no_k || top_k <= THREADS) && V <= CL_MAX * THREADS * VPT_MAX) {
+        static const int forced = [] { const char* e = getenv("MIVI_SAMPLE_CLUSTER"); return e ? atoi(e) : 0; }();
+        int cl = (B > 16 && V <= 4 * THREADS * VPT_MAX) ? 4 : 8;
+        if ((forced == 4 && V <= 4 * THREADS * VPT_MAX) || forced == 8) cl = forced;
+        auto kernel = cl == 4 ? sample_cluster_kernel<4> : sample_cluster_kernel<8>;
+        static bool attr2_set[2] = {false, false};
+        if (!attr2_set[cl == 4]) {
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES);
+            attr2_set[cl == 4] = true;
         }
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)B * CL);
+        cfg.gridDim = dim3((unsigned)B * cl);
         cfg.blockDim = dim3(THREADS);
         cfg.dynamicSmemBytes = TILES;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         int na = 0;
         attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = CL;
+        attr[na].val.clusterDim.x = cl;
         attr[na].val.clusterDim.y = 1;
         attr[na].val.clusterDim.z = 1;
         ++na;
@@ -926,7 +936,7 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
         }
         cfg.attrs = attr;
         cfg.numAttrs = na;
-        cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
+        cudaLaunchKernelEx(&cfg, kernel, logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
                            pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out);
         return mv_launch_status();
     }

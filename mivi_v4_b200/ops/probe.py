@@ -141,11 +141,53 @@ def prefill_step(a) -> int:
     return 0
 
 
+def sample(a) -> int:
+    """The sampling kernel alone on ``--batch`` rows of ``--vocab`` logits, by sampling mode; each mode is
+    timed as ten launches replayed from a CUDA graph, as generation runs it."""
+    dev = "cuda:0"
+    B, V = a.batch, a.vocab
+    logits = torch.randn(B, V, device=dev) * 2
+    work = torch.empty(B, K.sample_scratch_width(V), device=dev)
+    out = torch.empty(B, dtype=torch.int32, device=dev)
+    ring = torch.randint(0, V, (B, K.RECENT_RING), dtype=torch.int32, device=dev)
+    rows = torch.arange(B, dtype=torch.int32, device=dev)
+    streams = torch.arange(B, dtype=torch.int32, device=dev)
+    steps = torch.full((B,), 100, dtype=torch.int32, device=dev)
+    modes = {"greedy": dict(temperature=0.0),
+             "temperature": dict(temperature=0.7),
+             "temperature, top_p": dict(temperature=0.7, top_p=0.9),
+             "temperature, top_k": dict(temperature=0.2, top_k=40),
+             "temperature, top_k, top_p": dict(temperature=0.2, top_k=40, top_p=0.9),
+             "the reference's defaults (and a repetition penalty over the ring)":
+                 dict(temperature=0.2, top_k=40, top_p=0.9, repetition_penalty=1.05, ring=ring, ring_rows=rows),
+             "temperature, top_k 2000, top_p (one block a row)": dict(temperature=0.7, top_k=2000, top_p=0.9)}
+    print(f"sampling, {B} rows of {V} logits")
+    for name, kw in modes.items():
+        run = lambda: K.sample(logits, work, out, seed=1, streams=streams, steps=steps, **kw)
+        run()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(10):
+                run()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"  {e0.elapsed_time(e1) * 1000 / (10 * a.reps):7.1f} us  {name}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mivi_v4_b200.ops.probe")
     ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc_swap", "gemm_tc", "attention_decode", "attention_prefill",
-                                      "attention_prefill_tc", "attention_decode_tc",
+                                      "attention_prefill_tc", "attention_decode_tc", "sample",
                                        "decode_step", "prefill_step"])
+    ap.add_argument("--vocab", type=int, default=65536)
     ap.add_argument("--config", default=None, help="config.json for decode_step (default: bench.py's)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--m", type=int, default=8)
@@ -168,6 +210,9 @@ def main(argv=None) -> int:
         return decode_step(a)
     if a.kernel == "prefill_step":
         return prefill_step(a)
+
+    if a.kernel == "sample":
+        return sample(a)
 
     if a.kernel.startswith("gemm"):
         fn = getattr(K, a.kernel)

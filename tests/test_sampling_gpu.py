@@ -140,3 +140,21 @@ def test_top_k_with_a_wall_of_ties(V, kw):
     for b in range(3):
         want = P.plain_sample(logits[b], recent=[], u=P.plain_uniform(seed, streams[b], steps[b]), **kw)
         assert got[b] == want, (b, got[b], want)
+
+
+@pytest.mark.parametrize("kw", [dict(temperature=0.2, top_k=40, top_p=0.9, repetition_penalty=1.05),
+                                dict(temperature=0.8, top_p=0.9), dict(temperature=1.1)],
+                         ids=["defaults", "top_p", "temperature"])
+@pytest.mark.parametrize("V", [4100, 30001])
+def test_many_rows(V, kw):
+    """More rows than take eight blocks each: they are sampled by four blocks a row, with the same tokens."""
+    g = torch.Generator().manual_seed(V + 1)
+    B = 20
+    logits = torch.randn(B, V, generator=g) * 2.5
+    logits[3] = torch.round(logits[3] * 2) / 2
+    seed, streams, steps = 77, list(range(100, 100 + B)), [3 * b for b in range(B)]
+    recent = [[(7 * b + j) % V for j in range(b)] for b in range(B)]
+    got = run_kernel(logits, seed, streams, steps, recent, **kw)
+    for b in range(B):
+        want = P.plain_sample(logits[b], recent=recent[b][-64:], u=P.plain_uniform(seed, streams[b], steps[b]), **kw)
+        assert got[b] == want, (b, got[b], want)
