@@ -52,6 +52,26 @@ struct NormLink {
     int emit_stride;
 };
 
+// The gated short convolution of a decode step as the epilogue of its input projection (the CONV
+// kernels): W is [3 N, K] with the rows of B, C and x one after another; a block takes 16 channels,
+// that is 16 rows out of each third, so that one lane ends up with B, C and x of one channel and
+// can finish it: B * x, the k taps over the sequence's k-1 kept values, the shift of those, C *.
+struct ConvTail {
+    const float* taps;                 // [N][k]
+    const float* conv_bias;            // [N] or null
+    float* state;                      // [slots][k - 1][N], the last k-1 values of B * x per sequence
+    const int* slots;                  // [M]: the slot of token m's sequence (one token a sequence)
+    int k;
+};
+
+// What the NEXT product of the step will read (or null): once a block has its own weights, its
+// threads ask the L2 cache for their share of these lines, so that HBM keeps streaming through
+// this kernel's reduce, its tail and the next launch instead of pausing there.
+struct Ahead {
+    const void* w;
+    long long bytes;
+};
+
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -69,18 +89,20 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 // NT: n-tiles of 8 tokens; RT: tiles of 16 weight rows per warp; UNROLL: k-steps
 // of 32 whose W loads are issued together.  gridDim.x = K slices (= cluster
 // size), gridDim.y = row tiles.
-template <int NT, int RT, int UNROLL, int WARPS>
+// CONV (RT == 3): the three row tiles of a warp are N rows apart, N counts channels, see ConvTail.
+template <int NT, int RT, int UNROLL, int WARPS, bool CONV>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K,
-                    int ldo, const NormLink link) {
+                    int ldo, const NormLink link, const ConvTail tail, const Ahead ahead) {
+    static_assert(!CONV || RT == 3, "the convolution epilogue takes B, C and x: three row tiles");
     constexpr int ROWS = RT * 16, COLS = NT * 8, LDR = COLS + 1;
     extern __shared__ float sm[];
     float* red = sm;                                   // [WARPS][ROWS][LDR] partial sums of the warps
     float* csum = sm + WARPS * ROWS * LDR;             // [COLS][ROWS] their sum: this block's share
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.y * ROWS;
+    const int n0 = blockIdx.y * (CONV ? 16 : ROWS);
     const int slices = gridDim.x, slice = blockIdx.x;
 
     float acc[RT][NT][4];
@@ -95,8 +117,13 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     const __nv_bfloat16* wrow[RT][2];
 #pragma unroll
     for (int r = 0; r < RT; ++r) {
-        wrow[r][0] = W + (size_t)min(n0 + r * 16 + g, N - 1) * K;
-        wrow[r][1] = W + (size_t)min(n0 + r * 16 + g + 8, N - 1) * K;
+        if constexpr (CONV) {
+            wrow[r][0] = W + ((size_t)r * N + min(n0 + g, N - 1)) * K;
+            wrow[r][1] = W + ((size_t)r * N + min(n0 + g + 8, N - 1)) * K;
+        } else {
+            wrow[r][0] = W + (size_t)min(n0 + r * 16 + g, N - 1) * K;
+            wrow[r][1] = W + (size_t)min(n0 + r * 16 + g + 8, N - 1) * K;
+        }
     }
     const __nv_bfloat16* xrow[NT];
     bool xok[NT];
@@ -153,13 +180,19 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     // send out its own first loads.  (Earlier would let its blocks take the place of blocks of
     // this kernel that have not started yet.)
     mv_pdl_launch_dependents();
+    if (ahead.w) {
+        const unsigned n_lines = (unsigned)(ahead.bytes >> 7);
+        const unsigned n_threads = gridDim.x * gridDim.y * blockDim.x;
+        for (unsigned l = (blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x; l < n_lines; l += n_threads)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)ahead.w + ((size_t)l << 7)));
+    }
 
     // What the epilogue's first item (most warps have at most one) will want from global memory is asked
     // for now and not touched until then: the answers arrive while the sums go through shared memory
     // and the cluster barrier.
     const int m_first = slice + slices * warp;
     const int n_lane = n0 + lane;
-    const bool lane_ok = lane < ROWS && n_lane < N;
+    const bool lane_ok = !CONV && lane < ROWS && n_lane < N;
     float early_old = 0.f, early_g = 0.f, early_part[4] = {0.f, 0.f, 0.f, 0.f};
     if (m_first < M) {
         if (mode == 2 && lane_ok) early_old = ((const float*)out)[(size_t)m_first * ldo + n_lane];
@@ -207,6 +240,64 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
         __syncthreads();
         share[0] = csum;
     }
+    if constexpr (CONV) {
+        // rows 0-15 of the tile are B, 16-31 C, 32-47 x of channels n0 .. n0+15.  Lanes 0-15 sum B and x
+        // of their channel, lanes 16-31 C (and x once more, unused); C then crosses by a shuffle.
+        const int c = n0 + (lane & 15);
+        const bool c_ok = c < N;
+        const int k = tail.k;
+        for (int m = slice + slices * warp; m < M; m += slices * WARPS) {
+            float part1[8], part2[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                part1[s] = s < slices ? share[s][m * ROWS + lane] : 0.f;
+                part2[s] = s < slices ? share[s][m * ROWS + 32 + (lane & 15)] : 0.f;
+            }
+            float v1 = 0.f, v2 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                v1 += part1[s];
+                v2 += part2[s];
+            }
+            if (link.scale_part) {
+                float e[4] = {0.f, 0.f, 0.f, 0.f};
+                if (m == m_first) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) e[q] = early_part[q];
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (lane + 32 * q < link.n_scale_part)
+                            e[q] = link.scale_part[(size_t)m * link.scale_stride + lane + 32 * q];
+                }
+                float ss = (e[0] + e[1]) + (e[2] + e[3]);
+                for (int p = lane + 128; p < link.n_scale_part; p += 32)
+                    ss += link.scale_part[(size_t)m * link.scale_stride + p];
+                ss = mv_warp_sum(ss);
+                const float rs = 1.0f / sqrtf(ss * link.inv_dim + link.eps);
+                v1 *= rs;
+                v2 *= rs;
+            }
+            if (bias && c_ok) {
+                v1 += bias[(lane < 16 ? 0 : N) + c];
+                v2 += bias[2 * N + c];
+            }
+            const float gate_c = __shfl_down_sync(0xffffffffu, v1, 16);
+            if (lane < 16 && c_ok) {
+                const float bx = v1 * v2;
+                float* st = tail.state + (size_t)tail.slots[m] * (k - 1) * N;
+                float y = tail.conv_bias ? tail.conv_bias[c] : 0.f;
+                for (int j = 0; j < k - 1; ++j) {
+                    const float v = st[(size_t)j * N + c];
+                    y = fmaf(tail.taps[c * k + j], v, y);
+                    if (j > 0) st[(size_t)(j - 1) * N + c] = v;         // shift towards the older end
+                }
+                if (k > 1) st[(size_t)(k - 2) * N + c] = bx;
+                y = fmaf(tail.taps[c * k + (k - 1)], bx, y);
+                ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(gate_c * y);
+            }
+        }
+    } else
     for (int m = slice + slices * warp; m < M; m += slices * WARPS) {
         const int r = lane;                         // ROWS is 16 or 32
         const int n = n0 + r;
@@ -266,21 +357,23 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     if (slices > 1) mv_cluster_sync_relaxed();
 }
 
-template <int NT, int RT, int UNROLL, int WARPS>
+template <int NT, int RT, int UNROLL, int WARPS, bool CONV = false>
 int launch(const void* W, const void* X, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-           const NormLink& link, cudaStream_t stream) {
+           const NormLink& link, const ConvTail& tail, const Ahead& ahead, cudaStream_t stream) {
     constexpr int ROWS = RT * 16, LDR = NT * 8 + 1;
     const int ksteps = (K + 31) / 32;
-    const int tiles = (N + ROWS - 1) / ROWS;
+    const int tiles = CONV ? (N + 15) / 16 : (N + ROWS - 1) / ROWS;
     // slices of K: every warp should still have UNROLL k-steps, and there is no point in many
     // more blocks than the GPU holds at once (about 8 per SM)
     int slices = ksteps / (WARPS * UNROLL);
     slices = slices < 1 ? 1 : (slices > 8 ? 8 : slices);
-    while (slices > 1 && (long long)tiles * slices > 148 * 8) slices >>= 1;
+    // (the convolution kernel holds three row tiles a warp: its registers leave room for 5 blocks;
+    // with more blocks than fit at once it measured 12.8 us on [3 x 2048, 2048] against 8.9 us)
+    while (slices > 1 && (long long)tiles * slices > 148 * (CONV ? 5 : 8)) slices >>= 1;
     const size_t smem = (size_t)(WARPS + 1) * ROWS * LDR * sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(gemm_small_m_kernel<NT, RT, UNROLL, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(gemm_small_m_kernel<NT, RT, UNROLL, WARPS, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              160 * 1024);
         attr_set = true;
     }
@@ -305,8 +398,8 @@ int launch(const void* W, const void* X, const float* bias, void* out, int mode,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaLaunchKernelEx(&cfg, gemm_small_m_kernel<NT, RT, UNROLL, WARPS>, (const __nv_bfloat16*)W, (const __nv_bfloat16*)X, bias,
-                       out, mode, M, N, K, ldo, link);
+    cudaLaunchKernelEx(&cfg, gemm_small_m_kernel<NT, RT, UNROLL, WARPS, CONV>, (const __nv_bfloat16*)W,
+                       (const __nv_bfloat16*)X, bias, out, mode, M, N, K, ldo, link, tail, ahead);
     return mv_launch_status();
 }
 
@@ -322,11 +415,12 @@ MV_API int mv_gemm_small_m_tile_rows(int N, int mode) { return (N >= 32 * 2 * 14
 // scale_part (or null): [M][scale_stride] of which n_scale_part sums of squares per token; every token's
 // results are multiplied by rsqrt(sum / dim + eps) before bias and activation.  emit_x (or null, mode 2
 // only, ldo == N): receives bf16(out_new * emit_g), and emit_part [M][emit_stride] the sums of out_new^2
-// per tile of mv_gemm_small_m_tile_rows(N, 2) rows.
+// per tile of mv_gemm_small_m_tile_rows(N, 2) rows.  next_w (or null), next_bytes: memory that the
+// step's next product will read, to be requested into L2 meanwhile.
 MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void* out, int mode, int M,
                            int N, int K, int ldo, const float* scale_part, int n_scale_part, int scale_stride,
                            int dim, float eps, const float* emit_g, void* emit_x, float* emit_part,
-                           int emit_stride, cudaStream_t stream) {
+                           int emit_stride, const void* next_w, long long next_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
@@ -350,7 +444,7 @@ MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void
     }
     const int nt = (M + 7) / 8;
     const bool wide = mv_gemm_small_m_tile_rows(N, mode) == 32;
-#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, link, stream)
+#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, link, ConvTail{}, Ahead{next_w, next_bytes}, stream)
     // few tokens: small blocks, many per SM; many tokens: large blocks, so that X is re-read less
     switch (nt) {
         case 1: if (wide) MV_GO(1, 2, 2, 4); else MV_GO(1, 1, 4, 4);
@@ -359,4 +453,30 @@ MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void
         default: if (wide) MV_GO(8, 2, 2, 16); else MV_GO(8, 1, 4, 16);
     }
 #undef MV_GO
+}
+
+// The input projection of a gated short convolution and the convolution's decode step in one kernel,
+// for steps in which each of M <= 8 sequences brings one token: W [3 H, K] (rows of B, then C, then x),
+// bias [3 H] or null, taps [H][k], conv_bias [H] or null, state [slots][k - 1][H] (read, shifted and
+// written for the M sequences in slots[0..M)), z bfloat16 [M, H] = C * conv(B * x).  scale_part as in
+// mv_gemm_small_m.  Needs K a multiple of 8 and 16-byte aligned X and W.
+MV_API int mv_gemm_small_m_shortconv(const void* X, const void* W, const float* bias, const float* taps,
+                                     const float* conv_bias, float* state, const int* slots, void* z, int M,
+                                     int H, int K, int k, const float* scale_part, int n_scale_part,
+                                     int scale_stride, int dim, float eps, const void* next_w,
+                                     long long next_bytes, cudaStream_t stream) {
+    if (M <= 0 || H <= 0) return 0;
+    if (M > 8 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || k < 1 || !taps || !slots || (k > 1 && !state))
+        return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
+    NormLink link = {};
+    if (scale_part) {
+        link.scale_part = scale_part;
+        link.n_scale_part = n_scale_part;
+        link.scale_stride = scale_stride;
+        link.inv_dim = 1.0f / (float)dim;
+        link.eps = eps;
+    }
+    ConvTail tail = {taps, conv_bias, state, slots, k};
+    return launch<1, 3, 2, 4, true>(W, X, bias, z, 1, M, H, K, H, link, tail, Ahead{next_w, next_bytes}, stream);
 }

@@ -239,12 +239,16 @@ class Engine:
             if entry is None:
                 # first time: run the step for real on a workspace of its own (which sizes every
                 # buffer), then record the same launches for the steps to come
+                # (the real run also notes which weights the products read, in order; recorded, each
+                # product of few rows then asks the L2 cache for its successor's weights)
+                from ..ops import linear as L
                 gws = Workspace(self.device)
                 ctx = context(gws)
-                logits = self.model.forward(ctx, self.cache)
+                with L.recording() as order:
+                    logits = self.model.forward(ctx, self.cache)
                 n0 = K.launch_count()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph), L.looking_ahead(order):
                     captured = self.model.forward(ctx, self.cache)
                 n_kernels = K.launch_count() - n0
                 K.add_launches(-n_kernels)                # recorded, not run

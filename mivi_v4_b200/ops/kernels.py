@@ -43,8 +43,9 @@ _SIGNATURES = {
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
-        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P],
+        "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P],
         "mv_gemm_small_m_tile_rows": [_I, _I],
+        "mv_gemm_small_m_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -210,10 +211,11 @@ def gemm_small_m_tile_rows(N: int, mode: int) -> int:
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
                  accumulate: bool = False, swiglu: bool = False, scale: Optional[NormLink] = None,
-                 emit: Optional[NormLink] = None) -> torch.Tensor:
+                 emit: Optional[NormLink] = None, ahead: Optional[tuple] = None) -> torch.Tensor:
     """out = x @ w.T for at most 64 rows of x, bfloat16 operands: the
     weight-streaming tensor-core kernel of the decode step.  ``scale`` / ``emit``: the
-    two ends of a :class:`NormLink`."""
+    two ends of a :class:`NormLink`.  ``ahead``: (address, bytes) of what the step's next
+    product will read; the kernel asks the L2 cache for it once it has its own weights."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
@@ -238,7 +240,44 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
     link = _link_args(x, M, N, K, mode, scale, emit, -(-N // gemm_small_m_tile_rows(N, 2)))
     _check(_fn("bf16", "mv_gemm_small_m")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, *link, _stream()), "mv_gemm_small_m")
+        out.data_ptr(), mode, M, N, K, ldo, *link, *(ahead or (None, 0)), _stream()), "mv_gemm_small_m")
+    return out
+
+
+SHORTCONV_FUSED_MAX_ROWS = 8
+
+
+def gemm_small_m_shortconv(x: torch.Tensor, w_in: torch.Tensor, b_in: Optional[torch.Tensor], taps: torch.Tensor,
+                           b_conv: Optional[torch.Tensor], state: torch.Tensor, slots: torch.Tensor,
+                           out: torch.Tensor, *, scale: Optional[NormLink] = None,
+                           ahead: Optional[tuple] = None) -> torch.Tensor:
+    """A decode step's gated short convolution together with its input projection, in one kernel:
+    [B | C | x] = x @ w_in.T (+ b_in), out = C * conv(B * x) with the sequences' kept values in
+    ``state`` [n_slots, k-1, H], which it shifts and updates for the rows' sequences (``slots[m]`` is
+    row m's).  At most 8 rows, one a sequence; bfloat16 operands; ``scale`` and ``ahead`` as in
+    ``gemm_small_m``."""
+    M, K = x.shape
+    H, k = taps.shape
+    if tuple(w_in.shape) != (3 * H, K):
+        raise KernelError(f"shortconv: in_proj weight is {tuple(w_in.shape)}, expected [{3 * H}, {K}]")
+    if x.dtype != torch.bfloat16 or w_in.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_small_m_shortconv: operands must be bfloat16, got {x.dtype} and {w_in.dtype}")
+    if not 1 <= M <= SHORTCONV_FUSED_MAX_ROWS or K % 8:
+        raise KernelError(f"gemm_small_m_shortconv: needs 1..{SHORTCONV_FUSED_MAX_ROWS} rows and K a multiple "
+                          f"of 8, got M={M}, K={K}")
+    if not 1 <= k <= MAX_CONV_K:
+        raise KernelError(f"shortconv: convolution width {k} is outside 1..{MAX_CONV_K}")
+    _need(state, "shortconv state", torch.float32)
+    if state.dim() != 3 or state.shape[1] != k - 1 or state.shape[2] != H:
+        raise KernelError(f"shortconv: state shape {tuple(state.shape)}, expected [slots, {k - 1}, {H}]")
+    if slots.numel() < M:
+        raise KernelError(f"shortconv: {slots.numel()} slots for {M} rows")
+    sp, n_sp, s_stride, dim, eps = _link_args(x, M, 3 * H, K, 1, scale, None, 0)[:5]
+    _check(_fn("bf16", "mv_gemm_small_m_shortconv")(
+        _need(x, "gemm x"), _need(w_in, "gemm w"), _need(b_in, "in_proj bias", torch.float32, (3 * H,), True),
+        _need(taps, "shortconv taps", torch.float32), _need(b_conv, "shortconv bias", torch.float32, (H,), True),
+        state.data_ptr(), _need(slots, "slots", torch.int32), _need(out, "shortconv out", torch.bfloat16, (M, H)),
+        M, H, K, k, sp, n_sp, s_stride, dim, eps, *(ahead or (None, 0)), _stream()), "mv_gemm_small_m_shortconv")
     return out
 
 

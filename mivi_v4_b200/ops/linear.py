@@ -9,6 +9,7 @@ stores in 32-bit stays so; a bfloat16 activation is widened for it.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Optional
 
 import torch
@@ -20,6 +21,70 @@ import os
 
 _DECODE_GEMM = os.environ.get("MIVI_DECODE_GEMM", "auto")
 MMA_MAX_ROWS = 8
+
+
+class WeightOrder:
+    """The weights that the products of a step read, in order.  A step that will be replayed
+    many times (a decode step) is first run once with ``recording()``; recorded again under
+    ``looking_ahead()``, each product of few rows is told what the next product will read and
+    asks the L2 cache for it while it finishes.  A step whose products come in another order
+    than the recorded one simply gets no hints from the first difference on."""
+
+    def __init__(self):
+        self.seen = []           # (address, bytes) of each product's weight
+        self.at = None           # position while looking ahead; None while recording
+
+    def next_after(self, w: torch.Tensor):
+        here = (w.data_ptr(), w.numel() * w.element_size())
+        if self.at is None:
+            self.seen.append(here)
+            return None
+        i = self.at
+        if i < 0 or i >= len(self.seen) or self.seen[i] != here:
+            self.at = -1         # not the recorded order: no more hints
+            return None
+        self.at = i + 1
+        ptr, size = self.seen[(i + 1) % len(self.seen)]       # after the last one comes the next step's first
+        size = min(size, _AHEAD_BYTES)
+        return (ptr, size) if size >= 128 else None
+
+
+_order: Optional[WeightOrder] = None
+# The most that one product requests ahead (MIVI_AHEAD_MB, 0 turns it off).  Measured on decode steps
+# of the 1.2B-parameter shape at 8 sequences: 735 us without, 729 with 2 MB, 712 with 8, 714 with 16,
+# 746 with 32, 760 with 64 (the requests then stand in the way of the kernel's own last loads and stores).
+_AHEAD_BYTES = int(float(os.environ.get("MIVI_AHEAD_MB", "8")) * (1 << 20))
+
+
+@contextlib.contextmanager
+def recording():
+    """Products issued inside note their weights; yields the ``WeightOrder``."""
+    global _order
+    prev, _order = _order, WeightOrder()
+    try:
+        yield _order
+    finally:
+        _order = prev
+
+
+@contextlib.contextmanager
+def looking_ahead(order: WeightOrder):
+    """Products issued inside, if they come in ``order``'s order, prefetch their successor's weights."""
+    global _order
+    prev, _order = _order, order
+    order.at = 0 if _AHEAD_BYTES > 0 and order.seen else -1
+    try:
+        yield
+    finally:
+        _order = prev
+
+
+def _ahead(w: torch.Tensor, fn) -> dict:
+    """The ``ahead`` argument for a product with ``w``, if its kernel takes one."""
+    if _order is None:
+        return {}
+    nxt = _order.next_after(w)
+    return {"ahead": nxt} if nxt is not None and fn is K.gemm_small_m else {}
 
 
 def _small_m(m: int):
@@ -50,16 +115,40 @@ def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bflo
             and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
 
 
+_FUSED_CONV = os.environ.get("MIVI_FUSED_CONV", "1") != "0"
+
+
+def shortconv_decode_fused_ok(n_rows: int, x: torch.Tensor, w_in: torch.Tensor) -> bool:
+    """Whether a decode step's gated short convolution can run as the epilogue of its input
+    projection (``kernels.gemm_small_m_shortconv``): the steps whose products take the
+    register-streaming kernel, bfloat16 operands.  One launch less a layer; MIVI_FUSED_CONV=0
+    keeps the two kernels."""
+    return (_FUSED_CONV and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
+            and tensor_core_ok(x, w_in))
+
+
+def linear_shortconv_decode(x: torch.Tensor, w_in: torch.Tensor, b_in, taps, b_conv, state, slots, out, *,
+                            scale: Optional[K.NormLink] = None) -> torch.Tensor:
+    """The input projection and the convolution of a decode step in one kernel; needs
+    ``shortconv_decode_fused_ok``."""
+    ahead = {}
+    if _order is not None:
+        nxt = _order.next_after(w_in)
+        ahead = {"ahead": nxt} if nxt is not None else {}
+    return K.gemm_small_m_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
+
+
 def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, *,
                   scale: Optional[K.NormLink] = None) -> torch.Tensor:
     """out = silu(gate) * up where [gate | up] = x @ w_grouped.T and the rows of
     ``w_grouped`` alternate in groups of 16 (gate rows, then the up rows of the
     same features): the activation runs in the product's epilogue, so gate and
     up never go to memory.  Needs ``tensor_core_ok``."""
-    if scale is not None:
-        return _small_m(x.shape[0])(x, w_grouped, out, swiglu=True, scale=scale)
-    if x.shape[0] <= K.SMALL_M_MAX:
-        return _small_m(x.shape[0])(x, w_grouped, out, swiglu=True)
+    if scale is not None or x.shape[0] <= K.SMALL_M_MAX:
+        fn = _small_m(x.shape[0])
+        return fn(x, w_grouped, out, swiglu=True, scale=scale, **_ahead(w_grouped, fn))
+    if _order is not None:
+        _order.next_after(w_grouped)
     return K.gemm_tc(x, w_grouped, out, swiglu=True)
 
 
@@ -73,12 +162,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
     if scale is not None or emit is not None:
         if not norm_link_ok(x.shape[0], w, x.dtype) or x.data_ptr() % 16:
             raise K.KernelError("linear: these operands cannot carry a norm; ask norm_link_ok first")
-        return _small_m(x.shape[0])(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit)
+        fn = _small_m(x.shape[0])
+        return fn(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit, **_ahead(w, fn))
     if w.dtype == torch.float32 and x.dtype != torch.float32:
         x = x.float()
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         if x.shape[0] <= K.SMALL_M_MAX:
-            return _small_m(x.shape[0])(x, w, out, bias=bias, accumulate=accumulate)
+            fn = _small_m(x.shape[0])
+            return fn(x, w, out, bias=bias, accumulate=accumulate, **_ahead(w, fn))
+        if _order is not None:
+            _order.next_after(w)
         return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate)
+    if _order is not None:
+        _order.next_after(w)
     return K.gemm_simt(x, w, out, bias=bias, accumulate=accumulate)

@@ -8,7 +8,7 @@ import torch
 
 from ..cache.needs import KVNeed, StateNeed
 from ..ops import kernels as K
-from ..ops.linear import linear, norm_link_ok
+from ..ops.linear import linear, linear_shortconv_decode, norm_link_ok, shortconv_decode_fused_ok
 from .base import Part
 from .registry import register
 from .spec import ParamSpec
@@ -52,9 +52,15 @@ class ShortConv(Part):
 
     def forward(self, u, resid, step, view, scale=None, emit=None) -> None:
         N, H = u.shape
+        z = step.ws.get("mix", (N, H), step.dtype)
+        if step.is_decode and N == step.n_seqs and shortconv_decode_fused_ok(N, u, self.w_in):
+            # a few sequences, one token each: the convolution is the projection's epilogue
+            linear_shortconv_decode(u, self.w_in, self.b_in, self.taps, self.b_conv, view.state, step.slots, z,
+                                    scale=scale)
+            linear(z, self.w_out, resid, bias=self.b_out, accumulate=True, emit=emit)
+            return
         p = step.ws.get("proj", (N, 3 * H), torch.float32)
         linear(u, self.w_in, p, bias=self.b_in, scale=scale)
-        z = step.ws.get("mix", (N, H), step.dtype)
         K.shortconv(p, self.taps, self.b_conv, view.state, step.positions, step.seq_of, step.cu,
                     step.slots, step.starts, step.lens, z, step.n_seqs, decode=step.is_decode)
         linear(z, self.w_out, resid, bias=self.b_out, accumulate=True, emit=emit)

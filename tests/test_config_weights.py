@@ -189,3 +189,28 @@ def test_sharded_folder(tmp_path):
     json.dump({"weight_map": wm}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
     m = load_model(d, "float32", "cpu")
     assert torch.equal(m.embedding.weight, t["model.embed_tokens.weight"].float())
+
+
+def test_weight_order_hints_follow_the_recorded_order():
+    """The order of a step's products is noted once; replayed in that order each product learns its
+    successor's weights (the last one the first's), capped in size; any other order ends the hints."""
+    import torch
+    from mivi_v4_b200.ops import linear as L
+    ws = [torch.zeros(n, 64, dtype=torch.bfloat16) for n in (4, 100000, 8, 2)]
+    with L.recording() as order:
+        for w in ws:
+            assert L._order.next_after(w) is None
+    assert L._order is None and len(order.seen) == 4
+    with L.looking_ahead(order):
+        got = [L._order.next_after(w) for w in ws]
+    assert got[0] == (ws[1].data_ptr(), min(100000 * 128, L._AHEAD_BYTES))
+    assert got[1] == (ws[2].data_ptr(), 8 * 128)
+    assert got[3] == (ws[0].data_ptr(), 4 * 128)              # the next step begins with the first again
+    with L.looking_ahead(order):
+        assert L._order.next_after(ws[0]) is not None
+        assert L._order.next_after(ws[2]) is None             # not the recorded successor
+        assert L._order.next_after(ws[3]) is None             # and nothing after it
+    with L.looking_ahead(order):                              # a step with more products than recorded
+        for w in ws:
+            L._order.next_after(w)
+        assert L._order.next_after(ws[0]) is None

@@ -540,3 +540,61 @@ def test_shortconv_long_steps(out_dtype, H, k, bias):
                 done[s] += n
         for a, b_ in zip(got, want):
             assert torch.allclose(torch.cat(a).double().cpu(), b_, rtol=tol, atol=tol), cuts
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("H,Kd,k,bias,scaled", [(16, 8, 3, False, False), (200, 72, 4, True, True), (40, 2048, 1, True, False),
+                                                (2048, 2048, 3, False, True), (24, 8200, 7, False, False)])
+def test_gemm_small_m_shortconv(M, H, Kd, k, bias, scaled):
+    """The decode step's convolution as the epilogue of its input projection: several steps in a
+    row over slots in any order, against a float64 expression and against the two separate kernels
+    (same outputs within rounding, same kind of state)."""
+    from mivi_v4_b200.ops.kernels import NormLink
+    g = torch.Generator().manual_seed(H + Kd + k + M)
+    w_in = (torch.randn(3 * H, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16).to(DEV)
+    taps = torch.randn(H, k, generator=g).to(DEV)
+    b_in = torch.randn(3 * H, generator=g).to(DEV) if bias else None
+    b_conv = torch.randn(H, generator=g).to(DEV) if bias else None
+    slots = ints([5, 0, 7, 2, 1, 6, 3, 4][:M])
+    state = torch.zeros(9, k - 1, H, device=DEV)
+    state_two = torch.zeros_like(state)
+    hist = torch.zeros(M, k - 1, H, dtype=torch.float64)           # the plain side's kept values of B * x
+    n_part = 3
+    for step in range(k + 2):
+        x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).to(DEV)
+        link = None
+        if scaled:
+            # the rows come with partial sums of squares whose total sets a scale per row
+            parts = torch.rand(M, n_part + 2, generator=g).to(DEV) * Kd
+            link = NormLink(norm=None, weight=torch.ones(Kd, device=DEV), eps=1e-5, dim=Kd, xg=x, partials=parts, n_partials=n_part)
+            rs = 1.0 / torch.sqrt(parts[:, :n_part].double().sum(1) / Kd + 1e-5)
+        p = x.double() @ w_in.double().T
+        if scaled:
+            p = p * rs[:, None]
+        if bias:
+            p = p + b_in.double()
+        p = p.cpu()
+        bx = p[:, :H] * p[:, 2 * H:]
+        y = taps[:, k - 1].double().cpu() * bx
+        for j in range(k - 1):
+            y = y + taps[:, j].double().cpu() * hist[:, j]
+        if bias:
+            y = y + b_conv.double().cpu()
+        want = p[:, H:2 * H] * y
+        hist = torch.cat([hist[:, 1:], bx[:, None]], dim=1) if k > 1 else hist
+
+        out = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K().gemm_small_m_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=link)
+        tol = dict(rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+        assert torch.allclose(out.double().cpu(), want, **tol), step
+        # the separate kernels
+        p32 = torch.empty(M, 3 * H, device=DEV)
+        K().gemm_small_m(x, w_in, p32, bias=b_in, scale=link)
+        out_two = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K().shortconv(p32, taps, b_conv, state_two, None, None, None, slots, None, None, out_two, M, decode=True)
+        assert torch.allclose(out.float(), out_two.float(), rtol=2e-2, atol=2e-2 * float(want.abs().max())), step
+        if k > 1:
+            assert torch.allclose(state, state_two, rtol=1e-4, atol=1e-4 * float(bx.abs().max())), step
+            assert torch.allclose(state[slots.long()].double().cpu(), hist, rtol=1e-3, atol=1e-3 * float(bx.abs().max()))
+    untouched = [s for s in range(9) if s not in slots.tolist()]
+    assert not state[untouched].any()                               # other sequences' state is left alone
