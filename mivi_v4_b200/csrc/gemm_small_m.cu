@@ -64,6 +64,25 @@ struct ConvTail {
     int k;
 };
 
+// The preparation of q, k and v as the epilogue of their fused projection (the HEADS kernels, head
+// size 64): W is [(nh + 2 nkv) 64, K], query heads, then key heads, then value heads; a block takes
+// one head, and a warp finishes it for one token with two elements a lane: RMSNorm over the head
+// (q and k), rotation by the token's position (q and k), then q goes out in bfloat16 and k and v
+// into the token's row of its sequence's cache page.
+struct HeadTail {
+    const float* wq;                   // [64] norm weight of the query heads, or null: no norm
+    const float* wk;                   // the same for the key heads
+    const float* inv_freq;             // [32] or null: no rotation
+    const int* positions;              // [M]
+    const int* seq_of;                 // [M] row of the page table
+    const int* page_table;
+    __nv_bfloat16* pool;               // [page][K, V][kv head][page_size][64]
+    __nv_bfloat16* q_out;              // [M][nh * 64]
+    long long page_stride;
+    float eps;
+    int half_split, table_stride, page_shift, nh, nkv;
+};
+
 // What the NEXT product of the step will read (or null): once a block has its own weights, its
 // threads ask the L2 cache for their share of these lines, so that HBM keeps streaming through
 // this kernel's reduce, its tail and the next launch instead of pausing there.
@@ -89,13 +108,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 // NT: n-tiles of 8 tokens; RT: tiles of 16 weight rows per warp; UNROLL: k-steps
 // of 32 whose W loads are issued together.  gridDim.x = K slices (= cluster
 // size), gridDim.y = row tiles.
-// CONV (RT == 3): the three row tiles of a warp are N rows apart, N counts channels, see ConvTail.
-template <int NT, int RT, int UNROLL, int WARPS, bool CONV>
+// TAIL 1 (RT == 3): the three row tiles of a warp are N rows apart, N counts channels, see ConvTail.
+// TAIL 2 (RT == 4): a tile is one head, see HeadTail.
+template <int NT, int RT, int UNROLL, int WARPS, int TAIL>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K,
-                    int ldo, const NormLink link, const ConvTail tail, const Ahead ahead) {
+                    int ldo, const NormLink link, const ConvTail tail, const HeadTail heads, const Ahead ahead) {
+    constexpr bool CONV = TAIL == 1, HEADS = TAIL == 2;
     static_assert(!CONV || RT == 3, "the convolution epilogue takes B, C and x: three row tiles");
+    static_assert(!HEADS || RT == 4, "the head epilogue takes heads of 64 rows");
     constexpr int ROWS = RT * 16, COLS = NT * 8, LDR = COLS + 1;
     extern __shared__ float sm[];
     float* red = sm;                                   // [WARPS][ROWS][LDR] partial sums of the warps
@@ -192,7 +214,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     // and the cluster barrier.
     const int m_first = slice + slices * warp;
     const int n_lane = n0 + lane;
-    const bool lane_ok = !CONV && lane < ROWS && n_lane < N;
+    const bool lane_ok = TAIL == 0 && lane < ROWS && n_lane < N;
     float early_old = 0.f, early_g = 0.f, early_part[4] = {0.f, 0.f, 0.f, 0.f};
     if (m_first < M) {
         if (mode == 2 && lane_ok) early_old = ((const float*)out)[(size_t)m_first * ldo + n_lane];
@@ -297,6 +319,83 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
                 ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(gate_c * y);
             }
         }
+    } else if constexpr (HEADS) {
+        const int hs = blockIdx.y;                  // head slot: nh query heads, nkv key heads, nkv value heads
+        const bool is_q = hs < heads.nh, is_k = !is_q && hs < heads.nh + heads.nkv;
+        // the lane's two elements: neighbours, or half a head apart (the two ways of pairing for the rotation)
+        const int r0 = heads.half_split ? lane : 2 * lane, r1 = heads.half_split ? lane + 32 : 2 * lane + 1;
+        const float* w = is_q ? heads.wq : (is_k ? heads.wk : nullptr);
+        float w0 = 1.f, w1 = 1.f, freq = 0.f;
+        if (w) {
+            w0 = w[r0];
+            w1 = w[r1];
+        }
+        const bool rotate = heads.inv_freq && (is_q || is_k);
+        if (rotate) freq = heads.inv_freq[lane];
+        for (int m = slice + slices * warp; m < M; m += slices * WARPS) {
+            float pa[8], pb[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                pa[s] = s < slices ? share[s][m * ROWS + r0] : 0.f;
+                pb[s] = s < slices ? share[s][m * ROWS + r1] : 0.f;
+            }
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                a += pa[s];
+                b += pb[s];
+            }
+            const int pos = heads.positions[m];
+            if (link.scale_part) {
+                float e[4] = {0.f, 0.f, 0.f, 0.f};
+                if (m == m_first) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) e[q] = early_part[q];
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (lane + 32 * q < link.n_scale_part)
+                            e[q] = link.scale_part[(size_t)m * link.scale_stride + lane + 32 * q];
+                }
+                float ss = (e[0] + e[1]) + (e[2] + e[3]);
+                for (int p = lane + 128; p < link.n_scale_part; p += 32)
+                    ss += link.scale_part[(size_t)m * link.scale_stride + p];
+                ss = mv_warp_sum(ss);
+                const float rs = 1.0f / sqrtf(ss * link.inv_dim + link.eps);
+                a *= rs;
+                b *= rs;
+            }
+            if (w) {
+                float ss = fmaf(a, a, b * b);
+                ss = mv_warp_sum(ss);
+                const float scale = 1.0f / sqrtf(ss / (float)ROWS + heads.eps);
+                a = a * scale * w0;
+                b = b * scale * w1;
+            }
+            if (rotate) {
+                float sn, cs;
+                sincosf((float)pos * freq, &sn, &cs);
+                const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+                a = ra;
+                b = rb;
+            }
+            __nv_bfloat16* dst;
+            if (is_q) {
+                dst = heads.q_out + ((size_t)m * heads.nh + hs) * ROWS;
+            } else {
+                const int page_size = 1 << heads.page_shift;
+                const int page = heads.page_table[(size_t)heads.seq_of[m] * heads.table_stride + (pos >> heads.page_shift)];
+                const int g2 = is_k ? hs - heads.nh : hs - heads.nh - heads.nkv;
+                dst = heads.pool + (size_t)page * heads.page_stride + (size_t)(pos & (page_size - 1)) * ROWS +
+                      ((size_t)(is_k ? 0 : 1) * heads.nkv + g2) * page_size * ROWS;
+            }
+            if (heads.half_split) {
+                dst[r0] = __float2bfloat16_rn(a);
+                dst[r1] = __float2bfloat16_rn(b);
+            } else {
+                mv_store2(dst + r0, a, b);
+            }
+        }
     } else
     for (int m = slice + slices * warp; m < M; m += slices * WARPS) {
         const int r = lane;                         // ROWS is 16 or 32
@@ -357,9 +456,10 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __
     if (slices > 1) mv_cluster_sync_relaxed();
 }
 
-template <int NT, int RT, int UNROLL, int WARPS, bool CONV = false>
+template <int NT, int RT, int UNROLL, int WARPS, int TAIL = 0>
 int launch(const void* W, const void* X, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-           const NormLink& link, const ConvTail& tail, const Ahead& ahead, cudaStream_t stream) {
+           const NormLink& link, const ConvTail& tail, const HeadTail& heads, const Ahead& ahead, cudaStream_t stream) {
+    constexpr bool CONV = TAIL == 1;
     constexpr int ROWS = RT * 16, LDR = NT * 8 + 1;
     const int ksteps = (K + 31) / 32;
     const int tiles = CONV ? (N + 15) / 16 : (N + ROWS - 1) / ROWS;
@@ -369,11 +469,11 @@ int launch(const void* W, const void* X, const float* bias, void* out, int mode,
     slices = slices < 1 ? 1 : (slices > 8 ? 8 : slices);
     // (the convolution kernel holds three row tiles a warp: its registers leave room for 5 blocks;
     // with more blocks than fit at once it measured 12.8 us on [3 x 2048, 2048] against 8.9 us)
-    while (slices > 1 && (long long)tiles * slices > 148 * (CONV ? 5 : 8)) slices >>= 1;
+    while (slices > 1 && (long long)tiles * slices > 148 * (TAIL == 1 ? 5 : TAIL == 2 ? 4 : 8)) slices >>= 1;
     const size_t smem = (size_t)(WARPS + 1) * ROWS * LDR * sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(gemm_small_m_kernel<NT, RT, UNROLL, WARPS, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(gemm_small_m_kernel<NT, RT, UNROLL, WARPS, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              160 * 1024);
         attr_set = true;
     }
@@ -398,8 +498,8 @@ int launch(const void* W, const void* X, const float* bias, void* out, int mode,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaLaunchKernelEx(&cfg, gemm_small_m_kernel<NT, RT, UNROLL, WARPS, CONV>, (const __nv_bfloat16*)W,
-                       (const __nv_bfloat16*)X, bias, out, mode, M, N, K, ldo, link, tail, ahead);
+    cudaLaunchKernelEx(&cfg, gemm_small_m_kernel<NT, RT, UNROLL, WARPS, TAIL>, (const __nv_bfloat16*)W,
+                       (const __nv_bfloat16*)X, bias, out, mode, M, N, K, ldo, link, tail, heads, ahead);
     return mv_launch_status();
 }
 
@@ -444,7 +544,7 @@ MV_API int mv_gemm_small_m(const void* X, const void* W, const float* bias, void
     }
     const int nt = (M + 7) / 8;
     const bool wide = mv_gemm_small_m_tile_rows(N, mode) == 32;
-#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, link, ConvTail{}, Ahead{next_w, next_bytes}, stream)
+#define MV_GO(NT, RT, U, WARPS) return launch<NT, RT, U, WARPS>(W, X, bias, out, mode, M, N, K, ldo, link, ConvTail{}, HeadTail{}, Ahead{next_w, next_bytes}, stream)
     // few tokens: small blocks, many per SM; many tokens: large blocks, so that X is re-read less
     switch (nt) {
         case 1: if (wide) MV_GO(1, 2, 2, 4); else MV_GO(1, 1, 4, 4);
@@ -478,5 +578,50 @@ MV_API int mv_gemm_small_m_shortconv(const void* X, const void* W, const float* 
         link.eps = eps;
     }
     ConvTail tail = {taps, conv_bias, state, slots, k};
-    return launch<1, 3, 2, 4, true>(W, X, bias, z, 1, M, H, K, H, link, tail, Ahead{next_w, next_bytes}, stream);
+    return launch<1, 3, 2, 4, 1>(W, X, bias, z, 1, M, H, K, H, link, tail, HeadTail{}, Ahead{next_w, next_bytes}, stream);
+}
+
+// The fused q/k/v projection of an attention layer and the preparation of its heads in one kernel, for
+// steps of M <= 8 tokens and heads of 64: W [(nh + 2 nkv) 64, K]; wq, wk [64] or null (no norm);
+// inv_freq [32] or null (no rotation); half_split: pairs (i, i + 32) instead of (2i, 2i + 1); the
+// token's position and page-table row; pool bfloat16 [pages][2][nkv][page_size][64] with page_stride
+// elements a page; q_out bfloat16 [M, nh 64].  scale_part and next_w as in mv_gemm_small_m.
+MV_API int mv_gemm_small_m_heads(const void* X, const void* W, const float* wq, const float* wk, float eps,
+                                 const float* inv_freq, int half_split, const int* positions, const int* seq_of,
+                                 const int* page_table, int table_stride, int page_size, void* pool,
+                                 long long page_stride, void* q_out, int M, int nh, int nkv, int K,
+                                 const float* scale_part, int n_scale_part, int scale_stride, int dim, float eps_norm,
+                                 const void* next_w, long long next_bytes, cudaStream_t stream) {
+    if (M <= 0 || nh <= 0) return 0;
+    if (M > 8 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || nkv < 0 || !positions || !q_out ||
+        (nkv > 0 && (!seq_of || !page_table || !pool || page_size <= 0 || (page_size & (page_size - 1)))))
+        return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
+    NormLink link = {};
+    if (scale_part) {
+        link.scale_part = scale_part;
+        link.n_scale_part = n_scale_part;
+        link.scale_stride = scale_stride;
+        link.inv_dim = 1.0f / (float)dim;
+        link.eps = eps_norm;
+    }
+    HeadTail heads = {};
+    heads.wq = wq;
+    heads.wk = wk;
+    heads.inv_freq = inv_freq;
+    heads.positions = positions;
+    heads.seq_of = seq_of;
+    heads.page_table = page_table;
+    heads.pool = (__nv_bfloat16*)pool;
+    heads.q_out = (__nv_bfloat16*)q_out;
+    heads.page_stride = page_stride;
+    heads.eps = eps;
+    heads.half_split = half_split;
+    heads.table_stride = table_stride;
+    while ((1 << heads.page_shift) < page_size) ++heads.page_shift;
+    heads.nh = nh;
+    heads.nkv = nkv;
+    const int N = (nh + 2 * nkv) * 64;
+    return launch<1, 4, 2, 4, 2>(W, X, nullptr, q_out, 1, M, N, K, N, link, ConvTail{}, heads,
+                                 Ahead{next_w, next_bytes}, stream);
 }

@@ -46,6 +46,8 @@ _SIGNATURES = {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P],
         "mv_gemm_small_m_tile_rows": [_I, _I],
         "mv_gemm_small_m_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q, _P],
+        "mv_gemm_small_m_heads": [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
+                                  _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -279,6 +281,43 @@ def gemm_small_m_shortconv(x: torch.Tensor, w_in: torch.Tensor, b_in: Optional[t
         state.data_ptr(), _need(slots, "slots", torch.int32), _need(out, "shortconv out", torch.bfloat16, (M, H)),
         M, H, K, k, sp, n_sp, s_stride, dim, eps, *(ahead or (None, 0)), _stream()), "mv_gemm_small_m_shortconv")
     return out
+
+
+HEADS_FUSED_HEAD_DIM = 64
+
+
+def gemm_small_m_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                       eps: float, inv_freq: Optional[torch.Tensor], half_split: bool, positions, seq_of,
+                       page_table, pool: torch.Tensor, q_out: torch.Tensor, nh: int, nkv: int, *,
+                       scale: Optional[NormLink] = None, ahead: Optional[tuple] = None) -> torch.Tensor:
+    """The fused q/k/v projection together with what ``qk_prepare`` does, in one kernel, for steps of
+    at most 8 tokens, heads of 64 and a bfloat16 cache: q comes out normed and rotated in ``q_out``,
+    k (normed, rotated) and v go into the tokens' rows of the paged cache.  ``scale`` and ``ahead``
+    as in ``gemm_small_m``."""
+    M, K = x.shape
+    hd = HEADS_FUSED_HEAD_DIM
+    if tuple(w_qkv.shape) != ((nh + 2 * nkv) * hd, K):
+        raise KernelError(f"gemm_small_m_heads: weight is {tuple(w_qkv.shape)}, expected "
+                          f"[{(nh + 2 * nkv) * hd}, {K}] ({nh} + 2 x {nkv} heads of {hd})")
+    if x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_small_m_heads: operands and cache must be bfloat16, got {x.dtype}, "
+                          f"{w_qkv.dtype} and {pool.dtype}")
+    if not 1 <= M <= SHORTCONV_FUSED_MAX_ROWS or K % 8:
+        raise KernelError(f"gemm_small_m_heads: needs 1..{SHORTCONV_FUSED_MAX_ROWS} rows and K a multiple "
+                          f"of 8, got M={M}, K={K}")
+    page_size = pool.shape[3]
+    _check_kv(pool, nkv, hd, page_size, "gemm_small_m_heads")
+    _need(page_table, "page table", torch.int32)
+    sp, n_sp, s_stride, dim, eps_norm = _link_args(x, M, (nh + 2 * nkv) * hd, K, 1, scale, None, 0)[:5]
+    _check(_fn("bf16", "mv_gemm_small_m_heads")(
+        _need(x, "gemm x"), _need(w_qkv, "gemm w"), _need(wq, "q norm weight", torch.float32, (hd,), True),
+        _need(wk, "k norm weight", torch.float32, (hd,), True), float(eps),
+        _need(inv_freq, "inv_freq", torch.float32, (hd // 2,), True), int(half_split),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        page_table.data_ptr(), page_table.shape[1], page_size, _need(pool, "cache pool"), pool.stride(0),
+        _need(q_out, "q out", torch.bfloat16, (M, nh * hd)), M, nh, nkv, K, sp, n_sp, s_stride, dim, eps_norm,
+        *(ahead or (None, 0)), _stream()), "mv_gemm_small_m_heads")
+    return q_out
 
 
 def _link_args(x, M: int, N: int, K: int, mode: int, scale: Optional[NormLink], emit: Optional[NormLink],

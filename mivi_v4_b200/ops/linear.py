@@ -138,6 +138,28 @@ def linear_shortconv_decode(x: torch.Tensor, w_in: torch.Tensor, b_in, taps, b_c
     return K.gemm_small_m_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
 
 
+_FUSED_QK = os.environ.get("MIVI_FUSED_QK", "1") != "0"
+
+
+def heads_fused_ok(n_rows: int, x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int, pool: torch.Tensor) -> bool:
+    """Whether the preparation of q, k and v (per-head norm, rotation, append to the cache) can run
+    as the epilogue of their projection (``kernels.gemm_small_m_heads``): steps whose products take
+    the register-streaming kernel, heads of 64, bfloat16 cache.  MIVI_FUSED_QK=0 keeps the two kernels."""
+    return (_FUSED_QK and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
+            and head_dim == K.HEADS_FUSED_HEAD_DIM and pool.dtype == torch.bfloat16 and tensor_core_ok(x, w_qkv))
+
+
+def linear_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq, wk, eps: float, inv_freq, half_split: bool, positions,
+                 seq_of, page_table, pool, q_out, nh: int, nkv: int, *, scale: Optional[K.NormLink] = None):
+    """The q/k/v projection and the preparation of its heads in one kernel; needs ``heads_fused_ok``."""
+    ahead = {}
+    if _order is not None:
+        nxt = _order.next_after(w_qkv)
+        ahead = {"ahead": nxt} if nxt is not None else {}
+    return K.gemm_small_m_heads(x, w_qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, pool,
+                                q_out, nh, nkv, scale=scale, **ahead)
+
+
 def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, *,
                   scale: Optional[K.NormLink] = None) -> torch.Tensor:
     """out = silu(gate) * up where [gate | up] = x @ w_grouped.T and the rows of

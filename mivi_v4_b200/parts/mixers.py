@@ -8,7 +8,8 @@ import torch
 
 from ..cache.needs import KVNeed, StateNeed
 from ..ops import kernels as K
-from ..ops.linear import linear, linear_shortconv_decode, norm_link_ok, shortconv_decode_fused_ok
+from ..ops.linear import (heads_fused_ok, linear, linear_heads, linear_shortconv_decode, norm_link_ok,
+                          shortconv_decode_fused_ok)
 from .base import Part
 from .registry import register
 from .spec import ParamSpec
@@ -131,17 +132,22 @@ class GroupedQueryAttention(Part):
         if view.writable == self.shared_kv:
             raise RuntimeError("a shared_kv attention layer must read another layer's cache, and only it may")
         width = (nh + (0 if self.shared_kv else 2 * nkv)) * hd
-        qkv = step.ws.get("proj", (N, width), torch.float32)
-        linear(u, self.w_qkv, qkv, scale=scale)
         q = step.ws.get("q", (N, nh * hd), step.dtype)
         rot = self.position.rotary(u.device)
         inv_freq, half_split = rot if rot is not None else (None, False)
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
-        if self.shared_kv:
-            K.qk_prepare_q_only(qkv, self.q_norm, eps, inv_freq, half_split, step.positions, q, nh, hd)
+        if not self.shared_kv and heads_fused_ok(N, u, self.w_qkv, hd, view.pool):
+            # a few tokens: norm, rotation and the append to the cache are the projection's epilogue
+            linear_heads(u, self.w_qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
+                         step.seq_of, view.page_table, view.pool, q, nh, nkv, scale=scale)
         else:
-            K.qk_prepare(qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
-                         step.seq_of, view.page_table, view.pool, q, nh, nkv, hd)
+            qkv = step.ws.get("proj", (N, width), torch.float32)
+            linear(u, self.w_qkv, qkv, scale=scale)
+            if self.shared_kv:
+                K.qk_prepare_q_only(qkv, self.q_norm, eps, inv_freq, half_split, step.positions, q, nh, hd)
+            else:
+                K.qk_prepare(qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
+                             step.seq_of, view.page_table, view.pool, q, nh, nkv, hd)
         o = step.ws.get("mix", (N, nh * hd), step.dtype)
         if N <= K.DECODE_ATTENTION_MAX_TOKENS and K.attention_decode_tc_supported(step.dtype, hd, view.pool,
                                                                                  self.window, nh, nkv):

@@ -598,3 +598,56 @@ def test_gemm_small_m_shortconv(M, H, Kd, k, bias, scaled):
             assert torch.allclose(state[slots.long()].double().cpu(), hist, rtol=1e-3, atol=1e-3 * float(bx.abs().max()))
     untouched = [s for s in range(9) if s not in slots.tolist()]
     assert not state[untouched].any()                               # other sequences' state is left alone
+
+
+@pytest.mark.parametrize("style", ["interleaved", "half_split"])
+@pytest.mark.parametrize("nh,nkv,Kd,eps,theta,normed,scaled", [
+    (4, 2, 64, 1e-5, 1e4, True, False), (3, 1, 200, 1e-6, 1e6, True, True), (5, 5, 2048, 1e-5, 5e4, False, False),
+    (32, 8, 2048, 1e-5, 1e6, True, True), (2, 2, 8200, 1e-5, 1e6, True, False)])
+def test_gemm_small_m_heads(style, nh, nkv, Kd, eps, theta, normed, scaled):
+    """Norm, rotation and append as the epilogue of the q/k/v projection (heads of 64): against the
+    plain expressions on a float64 product, and against the two separate kernels."""
+    from mivi_v4_b200.ops.kernels import NormLink
+    hd, page = 64, 16
+    pool = torch.zeros(8, 2, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    pool_two = torch.zeros_like(pool)
+    table = ints([[3, 5, 1], [6, 0, 0], [2, 7, 4]])
+    toks = [(0, p) for p in (0, 15, 16, 39)] + [(1, 6), (2, 47), (2, 31)]
+    M = len(toks)
+    x = rnd(M, Kd, dtype=torch.bfloat16)
+    w = (rnd((nh + 2 * nkv) * hd, Kd, seed=1) * (2.0 / math.sqrt(Kd))).to(torch.bfloat16)
+    wq, wk = (rnd(hd) + 1.0, rnd(hd, seed=1) + 1.0) if normed else (None, None)
+    inv = (1.0 / (torch.tensor(theta, dtype=torch.float64) ** (2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)))
+    inv_d = inv.float().to(DEV)
+    positions, seq_of = ints([p for _, p in toks]), ints([b for b, _ in toks])
+    link = None
+    qkv = x.double() @ w.double().T
+    if scaled:
+        parts = torch.rand(M, 6, device=DEV) * Kd
+        link = NormLink(norm=None, weight=torch.ones(Kd, device=DEV), eps=1e-5, dim=Kd, xg=x, partials=parts, n_partials=4)
+        qkv = qkv * (1.0 / torch.sqrt(parts[:, :4].double().sum(1) / Kd + 1e-5))[:, None]
+    qkv = qkv.cpu()
+    q_out = torch.empty(M, nh * hd, dtype=torch.bfloat16, device=DEV)
+    K().gemm_small_m_heads(x, w, wq, wk, eps, inv_d, style == "half_split", positions, seq_of, table, pool, q_out,
+                           nh, nkv, scale=link)
+    pos = torch.tensor([p for _, p in toks])
+    qh, kh = qkv[:, :nh * hd].reshape(-1, nh, hd), qkv[:, nh * hd:(nh + nkv) * hd].reshape(-1, nkv, hd)
+    if normed:
+        qh, kh = P.plain_rms_norm(qh, wq.double().cpu(), eps), P.plain_rms_norm(kh, wk.double().cpu(), eps)
+    qw, kw = P.plain_rope(qh, pos, theta, style), P.plain_rope(kh, pos, theta, style)
+    vw = qkv[:, (nh + nkv) * hd:].reshape(-1, nkv, hd)
+    tol = dict(rtol=2e-2, atol=2e-2 * float(qw.abs().max()))
+    assert torch.allclose(q_out.double().cpu().reshape(-1, nh, hd), qw, **tol)
+    tab = table.cpu()
+    for i, (b, p) in enumerate(toks):
+        pg = int(tab[b, p // page])
+        assert torch.allclose(pool[pg, 0, :, p % page].double().cpu(), kw[i], **tol)
+        assert torch.allclose(pool[pg, 1, :, p % page].double().cpu(), vw[i], **tol)
+    assert int((pool != 0).sum()) <= M * 2 * nkv * hd     # nothing was written anywhere else
+    # the separate kernels
+    p32 = torch.empty(M, (nh + 2 * nkv) * hd, device=DEV)
+    K().gemm_small_m(x, w, p32, scale=link)
+    q_two = torch.empty_like(q_out)
+    K().qk_prepare(p32, wq, wk, eps, inv_d, style == "half_split", positions, seq_of, table, pool_two, q_two, nh, nkv, hd)
+    assert torch.allclose(q_out.float(), q_two.float(), rtol=2e-2, atol=tol["atol"])
+    assert torch.allclose(pool.float(), pool_two.float(), rtol=2e-2, atol=tol["atol"])
