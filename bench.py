@@ -49,7 +49,14 @@ def peaks():
             with open(path) as f:
                 d = json.load(f)
             out = dict(FALLBACK_PEAKS)
-            out.update({k: float(v) for k, v in d.items() if isinstance(v, (int, float))})
+
+            def walk(node):
+                for k, v in node.items():
+                    if isinstance(v, dict):
+                        walk(v)
+                    elif k in out and isinstance(v, (int, float)) and v > 0:
+                        out[k] = float(v)
+            walk(d)
             return out, "measured"
         except (OSError, ValueError):
             pass
@@ -293,25 +300,28 @@ def main() -> int:
     nums = model_numbers(model, cfg)
     pk, pk_src = peaks()
 
+    # the clocks are sampled over all the timed regions of this run (the K decode steps alone are
+    # shorter than one sampling period)
     with ClockSampler() as clk:
         ms, launches, ctx_mean = time_decode(model, args.batch, args.steps, warmup)
+        value = args.batch * 1000.0 / ms
+        step_bytes = nums["weight_bytes"] + args.batch * (ctx_mean * nums["kv_bytes_per_token"] + nums["conv_state_bytes"])
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+
+        pre_ms = time_prefill(model, reps=5, warmup=3)
+        pre_flops = (PREFILL_TOKENS * nums["gemm_flops_per_token"] + nums["head_flops_per_row"]
+                     + nums["attn_flops"](PREFILL_TOKENS))
+        prefill = {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+                   "frac": pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+
+        points, e2e = {}, None
+        if not args.no_points:
+            for b in (1, 64):
+                pms, _, _ = time_decode(model, b, max(8, args.steps // 2), warmup)
+                points[f"decode_b{b}"] = b * 1000.0 / pms
+            e, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup)
+            e2e = {"value": e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     clocks = clk.summary()
-    value = args.batch * 1000.0 / ms
-    step_bytes = nums["weight_bytes"] + args.batch * (ctx_mean * nums["kv_bytes_per_token"] + nums["conv_state_bytes"])
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-
-    pre_ms = time_prefill(model, reps=5, warmup=3)
-    pre_flops = PREFILL_TOKENS * nums["gemm_flops_per_token"] + nums["head_flops_per_row"] + nums["attn_flops"](PREFILL_TOKENS)
-    prefill = {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
-               "frac": pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
-
-    points, e2e = {}, None
-    if not args.no_points:
-        for b in (1, 64):
-            pms, _, _ = time_decode(model, b, max(8, args.steps // 2), warmup)
-            points[f"decode_b{b}"] = b * 1000.0 / pms
-        e, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup)
-        e2e = {"value": e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
     c = model.config
     line = {
