@@ -28,6 +28,45 @@ MV_API int mv_embed(const void* table, int table_dtype, const int* tok, float* x
     return mv_launch_status();
 }
 
+// The same, and the first norm of the first layer handed to the product that follows (steps of few
+// tokens): xg = bf16(x * g), and per warp the sum of its elements' squares, one partial sum a warp;
+// the product multiplies its results by rsqrt(sum of the partials / H + eps).
+template <typename T>
+__global__ void embed_link_kernel(const T* __restrict__ table, const int* __restrict__ tok, float* __restrict__ x,
+                                  int H, const float* __restrict__ g, __nv_bfloat16* __restrict__ xg,
+                                  float* __restrict__ part, int part_stride) {
+    mv_pdl_begin();
+    const int n = blockIdx.x;
+    const T* row = table + (size_t)tok[n] * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = mv_to_f32(row[h]);
+        x[(size_t)n * H + h] = v;
+        xg[(size_t)n * H + h] = __float2bfloat16_rn(v * g[h]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = mv_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) part[(size_t)n * part_stride + (threadIdx.x >> 5)] = ss;
+}
+
+static inline int embed_threads(int H) { return H >= 1024 ? 256 : 128; }
+
+// How many partial sums a row mv_embed_link writes.
+MV_API int mv_embed_link_partials(int H) { return embed_threads(H) / 32; }
+
+MV_API int mv_embed_link(const void* table, int table_dtype, const int* tok, float* x, int N, int H, const float* g,
+                         void* xg, float* part, int part_stride, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (!g || !xg || !part || part_stride < embed_threads(H) / 32) return (int)cudaErrorInvalidValue;
+    if (table_dtype == MV_DT_BF16)
+        mv_launch(embed_link_kernel<__nv_bfloat16>, N, embed_threads(H), 0, stream, (const __nv_bfloat16*)table, tok, x, H,
+                  g, (__nv_bfloat16*)xg, part, part_stride);
+    else
+        mv_launch(embed_link_kernel<float>, N, embed_threads(H), 0, stream, (const float*)table, tok, x, H, g,
+                  (__nv_bfloat16*)xg, part, part_stride);
+    return mv_launch_status();
+}
+
 // ------------------------------------------------------------------ rmsnorm
 // y[i, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w, r = rows ? rows[i] : i.
 // Statistics in 32-bit whatever the output type.

@@ -11,7 +11,24 @@ import torch
 from .. import architectures  # noqa: F401  (registers the architectures that ship with the package)
 from ..cache import CachePlan, plan_cache
 from ..config import architecture_for
+from ..ops.linear import end_norms_carried
 from ..parts import ModelSpec, ParamSpec, build
+
+
+class _AfterLastBlock:
+    """What the last block sees as the block after it: the final norm, offered as a link when the
+    head's product can carry it (a step of few tokens with every row's logits wanted)."""
+
+    def __init__(self, model):
+        self.model = model
+
+    def entry_link(self, step):
+        m = self.model
+        if (step.carry_norms and end_norms_carried(step.n_tokens) and step.out_rows_all
+                and hasattr(m.final_norm, "link") and hasattr(m.head, "carries_norm")
+                and m.head.carries_norm(step, m.embedding)):
+            return m.final_norm.link(step, "final")
+        return None
 
 
 class Model:
@@ -81,18 +98,31 @@ class Model:
         """Run the step's tokens through every scheduled block and return the
         logits at ``step.out_rows`` (float32 [n_out, vocab]), or None if no
         logits are wanted."""
-        x = self.embedding.forward(step)
+        # In steps of few tokens the norms between products ride on those products; so do the two at
+        # the ends: the embedding writes the first block's first norm, the head applies the final one.
+        first = self.blocks[self.schedule[0].block] if self.schedule else None
+        link = first.entry_link(step) if (hasattr(first, "entry_link") and getattr(self.embedding, "emits_norm", False)
+                                          and end_norms_carried(step.n_tokens)) else None
+        if link is not None:
+            x = self.embedding.forward(step, emit=link)
+            step.leave_link(link)
+        else:
+            x = self.embedding.forward(step)
         for pos, entry in enumerate(self.schedule):
             block = self.blocks[entry.block]
             view = cache.view(pos, step.page_tables)
             if hasattr(block, "entry_link"):
                 # a block that can hand its last norm on to the next one is told which block that is
-                nxt = self.blocks[self.schedule[pos + 1].block] if pos + 1 < len(self.schedule) else None
+                nxt = self.blocks[self.schedule[pos + 1].block] if pos + 1 < len(self.schedule) else \
+                    (_AfterLastBlock(self) if step.n_out else None)
                 block.forward(x, step, view, after=nxt)
             else:
                 block.forward(x, step, view)
         if step.n_out == 0:
             return None
+        link = step.take_link(self.final_norm)
+        if link is not None:
+            return self.head.forward(link.xg, step, self.embedding, scale=link)
         f = step.ws.get("final", (step.n_out, self.hidden_size), step.dtype)
         self.final_norm.forward(x, f, rows=step.out_rows)
         return self.head.forward(f, step, self.embedding)

@@ -106,6 +106,7 @@ class StepContext:
         self.n_seqs = len(slots)
         self.n_tokens = sum(self.host_lens)
         self.n_out = len(out_rows)
+        self.out_rows_all = list(out_rows) == list(range(self.n_tokens))     # every row's logits, in order
         self.is_decode = all(n == 1 for n in self.host_lens)
         self.max_len = max(self.host_lens, default=0)
         self.max_context = max((s + n for s, n in zip(starts, self.host_lens)), default=0)

@@ -31,6 +31,8 @@ _P, _I, _F, _Q, _UQ = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_lo
 _SIGNATURES = {
     "core": {
         "mv_embed": [_P, _I, _P, _P, _I, _I, _P],
+        "mv_embed_link": [_P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P],
+        "mv_embed_link_partials": [_I],
         "mv_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "mv_swiglu": [_P, _P, _I, _I, _I, _I, _P],
         "mv_gemm_simt": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -122,10 +124,26 @@ def _check(code: int, name: str) -> None:
 
 
 # --------------------------------------------------------------------------
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[n, :] = table[tokens[n], :] widened to float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor,
+          emit: Optional["NormLink"] = None) -> torch.Tensor:
+    """out[n, :] = table[tokens[n], :] widened to float32.  ``emit``: a :class:`NormLink` whose rows
+    bf16(out * weight) and partial sums of squares the kernel writes too, for the product after it."""
     N = tokens.numel()
     V, H = table.shape
+    if emit is not None:
+        n_part = int(_fn("core", "mv_embed_link_partials")(H))
+        _need(emit.partials, "norm partials", torch.float32)
+        if emit.dim != H or emit.partials.dim() != 2 or emit.partials.shape[0] < N or emit.partials.shape[1] < n_part:
+            raise KernelError(f"embed: a norm link of width {emit.dim} with partials "
+                              f"{tuple(emit.partials.shape)} cannot take {N} rows of {H}")
+        _check(_fn("core", "mv_embed_link")(
+            _need(table, "embedding table"), _dt(table), _need(tokens, "tokens", torch.int32),
+            _need(out, "embedding out", torch.float32, (N, H)), N, H,
+            _need(emit.weight, "norm weight", torch.float32, (H,)),
+            _need(emit.xg, "normed rows", torch.bfloat16, (N, H)), emit.partials.data_ptr(), emit.partials.shape[1],
+            _stream()), "mv_embed_link")
+        emit.n_partials = n_part
+        return out
     _check(_fn("core", "mv_embed")(
         _need(table, "embedding table"), _dt(table), _need(tokens, "tokens", torch.int32),
         _need(out, "embedding out", torch.float32, (N, H)), N, H, _stream()), "mv_embed")

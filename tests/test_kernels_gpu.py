@@ -651,3 +651,33 @@ def test_gemm_small_m_heads(style, nh, nkv, Kd, eps, theta, normed, scaled):
     K().qk_prepare(p32, wq, wk, eps, inv_d, style == "half_split", positions, seq_of, table, pool_two, q_two, nh, nkv, hd)
     assert torch.allclose(q_out.float(), q_two.float(), rtol=2e-2, atol=tol["atol"])
     assert torch.allclose(pool.float(), pool_two.float(), rtol=2e-2, atol=tol["atol"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,H,N", [(37, 24, 5), (301, 200, 3), (50, 2048, 8)])
+def test_embed_hands_on_the_first_norm(dtype, V, H, N):
+    """The embedding kernel can also write what the product after it needs to apply the first norm
+    itself: the rows bf16(x * weight) and partial sums of x^2 that add up to each row's sum."""
+    from mivi_v4_b200.ops.kernels import NormLink
+    table = rnd(V, H, dtype=dtype)
+    tok = ints([V - 1, 0, 7][:N] + [3] * max(0, N - 3))
+    g = rnd(H, seed=3) + 1.0
+    link = NormLink(norm=None, weight=g, eps=1e-5, dim=H, xg=torch.empty(N, H, dtype=torch.bfloat16, device=DEV),
+                    partials=torch.full((N + 1, -(-H // 64) * 4), 7.0, device=DEV))
+    out = torch.empty(N, H, device=DEV)
+    K().embed(table, tok, out, link)
+    want = table[tok.long()].float()
+    assert torch.equal(out, want)
+    assert torch.equal(link.xg, (want * g).to(torch.bfloat16))
+    assert link.n_partials in (4, 8)
+    sums = link.partials[:N, :link.n_partials].double().sum(1)
+    assert torch.allclose(sums, (want.double() ** 2).sum(1), rtol=1e-5)
+    assert bool((link.partials[N] == 7.0).all())                      # no row beyond the step's
+    # and a product that takes the link gives what the norm kernel and a plain product give
+    w = rnd(48, H, dtype=torch.bfloat16, seed=5)
+    if H % 8 == 0:
+        y = torch.empty(N, 48, device=DEV)
+        K().gemm_small_m(link.xg, w, y, scale=link)
+        normed = P.plain_rms_norm(want.double(), g.double(), 1e-5)
+        ref = normed @ w.double().T
+        assert torch.allclose(y.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
