@@ -248,7 +248,7 @@ class Engine:
                     logits = self.model.forward(ctx, self.cache)
                 n0 = K.launch_count()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph), L.looking_ahead(order):
+                with torch.cuda.graph(graph), L.looking_ahead(order, self.model.weight_extents()):
                     captured = self.model.forward(ctx, self.cache)
                 n_kernels = K.launch_count() - n0
                 K.add_launches(-n_kernels)                # recorded, not run

@@ -72,21 +72,24 @@ class Model:
             p.load_named(named)
         self.dtype, self.device = dtype, torch.device(device)
 
-    def weight_bytes(self) -> int:
-        """Bytes of every tensor that one step reads (each counted once)."""
-        seen, total = set(), 0
+    def weight_extents(self) -> Dict[int, int]:
+        """Address -> bytes of every tensor that the parts hold (each once): the memory that lives
+        as long as the model does."""
+        seen: Dict[int, int] = {}
 
         def walk(p):
-            nonlocal total
             for v in vars(p).values():
                 if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
-                    seen.add(v.data_ptr())
-                    total += v.numel() * v.element_size()
+                    seen[v.data_ptr()] = v.numel() * v.element_size()
             for sub in p.nested().values():
                 walk(sub)
         for p in self.parts():
             walk(p)
-        return total
+        return seen
+
+    def weight_bytes(self) -> int:
+        """Bytes of every tensor that one step reads (each counted once)."""
+        return sum(self.weight_extents().values())
 
     # ---- cache --------------------------------------------------------------
     def cache_plan(self) -> CachePlan:

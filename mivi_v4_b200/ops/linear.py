@@ -33,6 +33,7 @@ class WeightOrder:
     def __init__(self):
         self.seen = []           # (address, bytes) of each product's weight
         self.at = None           # position while looking ahead; None while recording
+        self.lasting = None      # address -> bytes of memory that outlives the recording, or None: any
 
     def next_after(self, w: torch.Tensor):
         here = (w.data_ptr(), w.numel() * w.element_size())
@@ -45,6 +46,8 @@ class WeightOrder:
             return None
         self.at = i + 1
         ptr, size = self.seen[(i + 1) % len(self.seen)]       # after the last one comes the next step's first
+        if self.lasting is not None and self.lasting.get(ptr, 0) < size:
+            return None          # not a tensor of the model: it may be gone when the recording is replayed
         size = min(size, _AHEAD_BYTES)
         return (ptr, size) if size >= 128 else None
 
@@ -68,11 +71,14 @@ def recording():
 
 
 @contextlib.contextmanager
-def looking_ahead(order: WeightOrder):
-    """Products issued inside, if they come in ``order``'s order, prefetch their successor's weights."""
+def looking_ahead(order: WeightOrder, lasting: Optional[dict] = None):
+    """Products issued inside, if they come in ``order``'s order, prefetch their successor's weights.
+    ``lasting``: address -> bytes of the tensors that will still be there whenever the launches recorded
+    inside are replayed (a model's parameters); other weights are not requested ahead."""
     global _order
     prev, _order = _order, order
     order.at = 0 if _AHEAD_BYTES > 0 and order.seen else -1
+    order.lasting = lasting
     try:
         yield
     finally:

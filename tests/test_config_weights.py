@@ -210,6 +210,9 @@ def test_weight_order_hints_follow_the_recorded_order():
         assert L._order.next_after(ws[0]) is not None
         assert L._order.next_after(ws[2]) is None             # not the recorded successor
         assert L._order.next_after(ws[3]) is None             # and nothing after it
+    with L.looking_ahead(order, {ws[1].data_ptr(): 100000 * 128, ws[2].data_ptr(): 8}):
+        got = [L._order.next_after(w) for w in ws]            # only memory that is known to last, whole tensors
+    assert got[0] is not None and got[1] is None and got[2] is None and got[3] is None
     with L.looking_ahead(order):                              # a step with more products than recorded
         for w in ws:
             L._order.next_after(w)
