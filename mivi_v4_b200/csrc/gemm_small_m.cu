@@ -30,6 +30,12 @@
 // that consumes those rows then multiplies each token's results by rsqrt(sum / dim + eps), summing
 // the tile sums in a fixed order ("scale"): W (x g s) = s W (x g), and the statistics stay float32.
 //
+// Two more epilogues finish a mixer's elementwise work where the values already are, which saves the
+// step a launch a layer: the gated short convolution of a decode step after its input projection
+// (ConvTail; crates/mivi-model/src/ssm.rs:81-140) and the preparation of q, k and v after their
+// projection (HeadTail; crates/mivi-model/src/transformer.rs:81-108).  And a product can be told what
+// the step's next product will read (Ahead): it then asks the L2 cache for the beginning of it.
+//
 // What it replaces in the reference: quantized_matvec, one output row per
 // dot product over the input (crates/mivi-quant/src/lib.rs:75-135).
 #include <cooperative_groups.h>
