@@ -218,5 +218,11 @@ def cmd_replay(a) -> int:
 
 def main(argv=None) -> int:
     a = build_parser().parse_args(argv)
+    if a.command in ("generate", "bench", "replay"):
+        import torch
+        if not torch.cuda.is_available():
+            print(f"{a.command}: no CUDA device; this library runs on a GPU only (there is no CPU path)",
+                  file=sys.stderr)
+            return 2
     return {"replay": cmd_replay, "generate": cmd_generate, "info": cmd_info, "random": cmd_random, "doctor": cmd_doctor,
             "bench": cmd_bench}[a.command](a)
