@@ -21,6 +21,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -63,13 +64,51 @@ def peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+class NvmlSampler(threading.Thread):
+    """Reads the SM clock and the clock event reasons of the benchmark's GPU through NVML every 20 ms
+    (reading only; nothing is set).  Any failure ends the thread quietly: nvidia-smi's samples remain."""
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
+
+    def __init__(self, period: float = 0.02):
+        super().__init__(daemon=True)
+        self.period, self.stop_flag = period, threading.Event()
+        self.sm, self.max_sm, self.reasons = [], None, set()
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                import torch
+                handle = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(0).uuid))
+            except Exception:  # noqa: BLE001
+                handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            read_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop_flag.is_set():
+                self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                mask = int(read_reasons(handle))
+                self.reasons.update(name for bit, name in self.REASONS if mask & bit)
+                self.stop_flag.wait(self.period)
+        except Exception:  # noqa: BLE001
+            pass
+
+    def stop(self):
+        self.stop_flag.set()
+        self.join(timeout=2)
+
+
 class ClockSampler:
-    """nvidia-smi in the background while the timed region runs."""
+    """The GPU's clocks while the timed regions run: NVML in a thread of this process, and
+    nvidia-smi in the background as the second source (it needs a second or two before its first line)."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __enter__(self):
+        self.nvml = NvmlSampler()
+        self.nvml.start()
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.proc = subprocess.Popen(
@@ -80,6 +119,7 @@ class ClockSampler:
         return self
 
     def __exit__(self, *exc):
+        self.nvml.stop()
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -108,8 +148,13 @@ class ClockSampler:
             os.unlink(self.file.name)
         except OSError:
             pass
+        source = "nvidia-smi"
+        if len(self.nvml.sm) > len(sm) and self.nvml.max_sm:
+            # the denser record; what nvidia-smi saw of the reasons is kept too
+            sm, mx, source = list(self.nvml.sm), [self.nvml.max_sm], "nvml"
+            reasons |= self.nvml.reasons
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": source}
 
 
 def model_numbers(model, cfg):

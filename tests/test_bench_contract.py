@@ -57,3 +57,39 @@ def test_benchmark_configuration_is_the_named_one():
     assert (c.head_dim, c.ff_dim, c.vocab_size, c.conv_L_cache) == (64, 8192, 65536, 3)
     assert list(c.attn_layer_ids) == [2, 5, 8, 10, 12, 14] and c.tie_embedding
     assert bench.CONTEXT == 4096 and bench.PROMPT == 512 and bench.PREFILL_TOKENS == 2048
+
+
+def test_clock_record_prefers_the_denser_source(monkeypatch):
+    """With NVML readable the clocks come from it (a sample every 20 ms); without, from nvidia-smi;
+    with neither the record is empty, never an error."""
+    import time
+    import types
+
+    import torch  # noqa: F401  (the sampler's thread imports it; first imports take seconds)
+    sys.path.insert(0, ROOT)
+    import bench
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: "h"
+
+    def by_uuid(u):
+        raise RuntimeError("unknown")
+    fake.nvmlDeviceGetHandleByUUID = by_uuid
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, k: 1965
+    clocks = iter([1965, 1950, 1900] + [1965] * 10000)
+    fake.nvmlDeviceGetClockInfo = lambda h, k: next(clocks)
+    fake.nvmlDeviceGetCurrentClocksThrottleReasons = lambda h: 0x4 | 0x1          # power cap, and "idle" (not kept)
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    with bench.ClockSampler() as c:
+        time.sleep(0.25)
+    rec = c.summary()
+    assert rec["source"] == "nvml" and rec["samples"] >= 5
+    assert rec["sm_mhz"] == 1965.0 and rec["sm_max_mhz"] == 1965.0 and rec["reasons"] == ["sw_power_cap"]
+
+    broken = types.ModuleType("pynvml")                                        # NVML that cannot start
+    monkeypatch.setitem(sys.modules, "pynvml", broken)
+    with bench.ClockSampler() as c:
+        time.sleep(0.05)
+    rec = c.summary()
+    assert rec["samples"] == 0 and rec["sm_mhz"] is None and rec["reasons"] == []
