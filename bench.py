@@ -78,10 +78,19 @@ class NvmlSampler(threading.Thread):
         try:
             import pynvml
             pynvml.nvmlInit()
+            handle = None
             try:
                 import torch
-                handle = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(0).uuid))
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(0).uuid)
+                for form in (uuid, uuid.encode()):            # the binding's versions differ in which they take
+                    try:
+                        handle = pynvml.nvmlDeviceGetHandleByUUID(form)
+                        break
+                    except Exception:  # noqa: BLE001
+                        continue
             except Exception:  # noqa: BLE001
+                pass
+            if handle is None:
                 handle = pynvml.nvmlDeviceGetHandleByIndex(0)
             self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
             read_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
@@ -149,10 +158,14 @@ class ClockSampler:
         except OSError:
             pass
         source = "nvidia-smi"
-        if len(self.nvml.sm) > len(sm) and self.nvml.max_sm:
-            # the denser record; what nvidia-smi saw of the reasons is kept too
-            sm, mx, source = list(self.nvml.sm), [self.nvml.max_sm], "nvml"
-            reasons |= self.nvml.reasons
+        try:
+            nvml_sm = [float(v) for v in list(self.nvml.sm)]
+            if len(nvml_sm) > len(sm) and self.nvml.max_sm:
+                # the denser record; what nvidia-smi saw of the reasons is kept too
+                sm, mx, source = nvml_sm, [float(self.nvml.max_sm)], "nvml"
+                reasons |= set(self.nvml.reasons)
+        except Exception:  # noqa: BLE001
+            pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm), "source": source}
 
