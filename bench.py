@@ -73,23 +73,24 @@ class NvmlSampler(threading.Thread):
         super().__init__(daemon=True)
         self.period, self.stop_flag = period, threading.Event()
         self.sm, self.max_sm, self.reasons = [], None, set()
+        self.uuid = None
+        try:                                  # asked here, in the caller's thread: the sampling thread calls NVML only
+            import torch
+            self.uuid = "GPU-" + str(torch.cuda.get_device_properties(0).uuid)
+        except Exception:  # noqa: BLE001
+            pass
 
     def run(self):
         try:
             import pynvml
             pynvml.nvmlInit()
             handle = None
-            try:
-                import torch
-                uuid = "GPU-" + str(torch.cuda.get_device_properties(0).uuid)
-                for form in (uuid, uuid.encode()):            # the binding's versions differ in which they take
-                    try:
-                        handle = pynvml.nvmlDeviceGetHandleByUUID(form)
-                        break
-                    except Exception:  # noqa: BLE001
-                        continue
-            except Exception:  # noqa: BLE001
-                pass
+            for form in ((self.uuid, self.uuid.encode()) if self.uuid else ()):
+                try:                                      # the binding's versions differ in which form they take
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(form)
+                    break
+                except Exception:  # noqa: BLE001
+                    continue
             if handle is None:
                 handle = pynvml.nvmlDeviceGetHandleByIndex(0)
             self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
