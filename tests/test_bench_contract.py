@@ -65,7 +65,7 @@ def test_clock_record_prefers_the_denser_source(monkeypatch):
     import time
     import types
 
-    import torch  # noqa: F401  (the sampler's thread imports it; first imports take seconds)
+    import torch  # noqa: F401  (the sampler asks it for the GPU's UUID; a first import takes seconds)
     sys.path.insert(0, ROOT)
     import bench
     fake = types.ModuleType("pynvml")
