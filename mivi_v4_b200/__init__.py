@@ -8,10 +8,11 @@ random weights to generated tokens, with hand-written sm_100a kernels, a true
     new_tokens = engine.generate([[1, 2, 3], [4, 5]], max_new_tokens=32, sampling=SamplingParams.greedy())
 """
 from .config import ConfigError, Lfm2Config, known_architectures, register_architecture
-from .engine import Engine, Model, StepError, load_model, random_model
+from .engine import Engine, GenerationError, Model, StepError, load_model, random_model
+from .ops.kernels import KernelError
 from .sampling import SamplingParams
 from .weights import WeightsError, write_random_model
 
 __all__ = ["ConfigError", "Lfm2Config", "known_architectures", "register_architecture", "Engine", "Model",
-           "StepError", "load_model", "random_model", "SamplingParams", "WeightsError", "write_random_model"]
+           "StepError", "GenerationError", "KernelError", "load_model", "random_model", "SamplingParams", "WeightsError", "write_random_model"]
 __version__ = "0.1.0"

@@ -67,6 +67,7 @@ class IndexPool:
         free = sorted(self._free)
         if len(set(free)) != len(free):
             raise CacheError(f"a {self.what} is on the free list twice")
+        on_list = set(free)
         for i in range(self.n):
-            if self._held[i] == (i in set(free)):
+            if self._held[i] == (i in on_list):
                 raise CacheError(f"{self.what} {i} is {'held and free' if self._held[i] else 'lost'}")

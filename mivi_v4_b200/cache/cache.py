@@ -13,14 +13,18 @@ a layer map (crates/mivi-kv/src/cache.rs:109-141) and keeps the convolution
 state per layer in its run state (crates/mivi-core/src/arena.rs:56,82,105);
 both have one sequence.  Slots, pages and groups are this library's own.
 
-All bookkeeping is host-side Python over plain lists; only the storage lives
-on the device.  Nothing here launches a kernel except zeroing a slot's state.
+All bookkeeping is on the host; only the storage lives on the device.  Nothing
+here launches a kernel except zeroing a slot's state.  Beside the page lists of
+each sequence the cache keeps the same facts as arrays over all slots (lengths,
+page tables), so that a decode step of many sequences reads and advances them
+without a loop over the sequences.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
+import numpy as np
 import torch
 
 from .allocator import CacheError, IndexPool
@@ -97,10 +101,9 @@ class StateView:
 
 
 class _Slot:
-    __slots__ = ("length", "pages")
+    __slots__ = ("pages",)
 
     def __init__(self, n_groups: int):
-        self.length = 0
         # per KV group: page of each page-sized block of the sequence (None once given back)
         self.pages: List[List[Optional[int]]] = [[] for _ in range(n_groups)]
 
@@ -120,6 +123,13 @@ class SequenceCache:
         self.kv_groups: List[int] = [i for i, g in enumerate(plan.groups) if isinstance(g.need, KVNeed)]
         self.state_groups: List[int] = [i for i, g in enumerate(plan.groups) if isinstance(g.need, StateNeed)]
         self.pages: Dict[int, IndexPool] = {g: IndexPool(n_pages, "page") for g in self.kv_groups}
+        self.windowed: List[int] = [g for g in self.kv_groups if plan.groups[g].need.window > 0]
+        # the same bookkeeping as arrays over all slots: length, assigned or not, blocks that have a page
+        # entry, and per KV group the page of each block (0 where there is none)
+        self._len = np.zeros(max(n_slots, 1), dtype=np.int64)
+        self._assigned = np.zeros(max(n_slots, 1), dtype=bool)
+        self._nblk = np.zeros(max(n_slots, 1), dtype=np.int64)
+        self._table: Dict[int, np.ndarray] = {g: np.zeros((max(n_slots, 1), 8), dtype=np.int32) for g in self.kv_groups}
         self.storage: Dict[int, torch.Tensor] = {}
         for gi, g in enumerate(plan.groups):
             if isinstance(g.need, KVNeed):
@@ -146,6 +156,13 @@ class SequenceCache:
             new = torch.zeros((old.shape[0], n_slots) + tuple(old.shape[2:]), dtype=old.dtype, device=old.device)
             new[:, :old.shape[1]] = old
             self.storage[gi] = new
+        add = n_slots - self._len.shape[0]
+        if add > 0:
+            self._len = np.concatenate([self._len, np.zeros(add, dtype=np.int64)])
+            self._assigned = np.concatenate([self._assigned, np.zeros(add, dtype=bool)])
+            self._nblk = np.concatenate([self._nblk, np.zeros(add, dtype=np.int64)])
+            for g, t in self._table.items():
+                self._table[g] = np.concatenate([t, np.zeros((add, t.shape[1]), dtype=np.int32)])
         self.slots.grow(n_slots)
 
     # ---- slots --------------------------------------------------------------
@@ -153,6 +170,9 @@ class SequenceCache:
         """A fresh sequence: a slot of length 0 with zeroed state."""
         s = self.slots.take()
         self._seq[s] = _Slot(len(self.plan.groups))
+        self._len[s], self._nblk[s], self._assigned[s] = 0, 0, True
+        for t in self._table.values():
+            t[s] = 0
         for gi in self.state_groups:
             self.storage[gi][:, s].zero_()
         return s
@@ -167,10 +187,12 @@ class SequenceCache:
                 if p is not None:
                     self.pages[gi].give(p)
         del self._seq[slot]
+        self._len[slot], self._nblk[slot], self._assigned[slot] = 0, 0, False
         self.slots.give(slot)
 
     def length(self, slot: int) -> int:
-        return self._get(slot).length
+        self._get(slot)
+        return int(self._len[slot])
 
     def active_slots(self) -> List[int]:
         return sorted(self._seq)
@@ -185,39 +207,79 @@ class SequenceCache:
     def pages_needed(self, slot: int, n_tokens: int) -> int:
         """Most pages that any KV group must add for ``n_tokens`` more tokens."""
         seq = self._get(slot)
-        blocks = -(-(seq.length + n_tokens) // self.page_size)
+        blocks = -(-(int(self._len[slot]) + n_tokens) // self.page_size)
         return max((blocks - len(seq.pages[gi]) for gi in self.kv_groups), default=0)
 
     def reserve(self, slot: int, n_tokens: int) -> None:
         """Make room for ``n_tokens`` more tokens of this sequence in every KV
         group.  Takes all pages or none."""
         seq = self._get(slot)
-        blocks = -(-(seq.length + n_tokens) // self.page_size)
+        length = int(self._len[slot])
+        blocks = -(-(length + n_tokens) // self.page_size)
         for gi in self.kv_groups:
             want = blocks - len(seq.pages[gi])
             if want > self.pages[gi].free_count:
                 raise CacheError(
                     f"the cache is full: slot {slot} needs {want} more page(s) of {self.page_size} tokens "
-                    f"for {seq.length}+{n_tokens} tokens, {self.pages[gi].free_count} of "
+                    f"for {length}+{n_tokens} tokens, {self.pages[gi].free_count} of "
                     f"{self.n_pages} are free")
         for gi in self.kv_groups:
+            table = self._table[gi]
+            if blocks > table.shape[1]:
+                table = np.concatenate([table, np.zeros((table.shape[0], max(blocks, 2 * table.shape[1]) - table.shape[1]),
+                                                        dtype=np.int32)], axis=1)
+                self._table[gi] = table
             while len(seq.pages[gi]) < blocks:
-                seq.pages[gi].append(self.pages[gi].take())
+                page = self.pages[gi].take()
+                table[slot, len(seq.pages[gi])] = page
+                seq.pages[gi].append(page)
+        if self.kv_groups:
+            self._nblk[slot] = blocks
 
     def advance(self, slot: int, n_tokens: int) -> None:
         """The step's kernels are enqueued: the sequence is ``n_tokens`` longer.
         Groups with a window give back the pages that no later token reads."""
         seq = self._get(slot)
-        seq.length += n_tokens
-        for gi in self.kv_groups:
+        self._len[slot] += n_tokens
+        self._give_back(slot, seq)
+
+    def _give_back(self, slot: int, seq: _Slot) -> None:
+        length = int(self._len[slot])
+        for gi in self.windowed:
             window = self.plan.groups[gi].need.window
-            if window <= 0:
-                continue
-            first_needed = max(0, seq.length - window + 1)     # the next token reads keys from here on
+            first_needed = max(0, length - window + 1)     # the next token reads keys from here on
             for blk in range(min(first_needed // self.page_size, len(seq.pages[gi]))):
                 if seq.pages[gi][blk] is not None:
                     self.pages[gi].give(seq.pages[gi][blk])
                     seq.pages[gi][blk] = None
+                    self._table[gi][slot, blk] = 0
+
+    # ---- the same for many sequences at once (arrays of slots) ---------------------------
+    def are_assigned(self, slots: np.ndarray) -> bool:
+        return bool(slots.size) and 0 <= int(slots.min()) and int(slots.max()) < self._assigned.shape[0] \
+            and bool(self._assigned[slots].all())
+
+    def lengths_of(self, slots: np.ndarray) -> np.ndarray:
+        return self._len[slots]
+
+    def blocks_of(self, slots: np.ndarray) -> np.ndarray:
+        """Blocks of each sequence that have an entry in its page table (the same in every KV group)."""
+        return self._nblk[slots]
+
+    def table_rows(self, group: int, slots: np.ndarray, width: int) -> np.ndarray:
+        """``page_rows`` as an array [len(slots), width]."""
+        table = self._table[group]
+        if width > table.shape[1]:
+            table = np.concatenate([table, np.zeros((table.shape[0], width - table.shape[1]), dtype=np.int32)], axis=1)
+            self._table[group] = table
+        return table[slots, :width]
+
+    def advance_each_by_one(self, slots: np.ndarray) -> None:
+        """``advance(slot, 1)`` for every slot of the array (which names each slot once)."""
+        self._len[slots] += 1
+        if self.windowed:
+            for s in slots.tolist():
+                self._give_back(s, self._seq[s])
 
     def page_rows(self, group: int, slots: Sequence[int], width: Optional[int] = None) -> List[List[int]]:
         """Page table of these sequences for one KV group, padded with page 0
@@ -249,7 +311,7 @@ class SequenceCache:
         for gi, g in enumerate(self.plan.groups):
             st = self.storage[gi]
             if isinstance(g.need, KVNeed):
-                L = seq.length
+                L = int(self._len[slot])
                 rows = torch.zeros((g.n_layers, 2, L, g.need.n_kv_heads, g.need.head_dim), dtype=st.dtype,
                                    device=st.device)
                 for blk, page in enumerate(seq.pages[gi]):
@@ -274,3 +336,9 @@ class SequenceCache:
                 raise CacheError("a page belongs to two sequences")
             if len(held) != self.pages[gi].held_count:
                 raise CacheError(f"{self.pages[gi].held_count} pages are held but sequences own {len(held)}")
+            for s, seq in self._seq.items():
+                row = [0 if p is None else p for p in seq.pages[gi]]
+                if self._table[gi][s, :len(row)].tolist() != row or int(self._nblk[s]) != len(row):
+                    raise CacheError(f"the page table of slot {s} and its page list disagree")
+        if [i for i in range(self.slots.n) if self._assigned[i]] != sorted(self._seq):
+            raise CacheError("the array of assigned slots and the assigned sequences disagree")

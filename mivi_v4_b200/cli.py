@@ -66,6 +66,8 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--out", required=True)
     r.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--init", default="baseline", choices=["baseline", "loud"],
+                   help="baseline: N(0, 0.02) matrices; loud: standard deviation 1/sqrt(columns)")
 
     sub.add_parser("doctor", help="GPU, compiler and kernel-library report")
 
@@ -143,7 +145,7 @@ def cmd_random(a) -> int:
     from . import write_random_model
     with open(a.config) as f:
         cfg = json.load(f)
-    print(write_random_model(a.out, cfg, a.seed, a.store_dtype))
+    print(write_random_model(a.out, cfg, a.seed, a.store_dtype, a.init))
     return 0
 
 
@@ -205,15 +207,8 @@ def cmd_bench(a) -> int:
 
 
 def cmd_replay(a) -> int:
-    import os
-    import runpy
-    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
-    sys.argv = [script, "--model", a.model, "--dtype", a.dtype, "--out", a.out, "--max-tokens", str(a.max_tokens)]
-    try:
-        runpy.run_path(script, run_name="__main__")
-    except SystemExit as e:
-        return int(e.code or 0)
-    return 0
+    from .replay import main as replay_main
+    return replay_main(["--model", a.model, "--dtype", a.dtype, "--out", a.out, "--max-tokens", str(a.max_tokens)])
 
 
 def main(argv=None) -> int:

@@ -223,3 +223,11 @@ MV_API int mv_swiglu(const float* gu, void* h, int h_dtype, int N, int F, int gr
         mv_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gu, (float*)h, total, F, group);
     return mv_launch_status();
 }
+
+// ------------------------------------------------------------- small copies
+// A few bytes from the device to pinned host memory on ``stream`` (the error flag's
+// way to the host; recorded into a CUDA graph like any launch).
+MV_API int mv_copy_to_host(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+    if (bytes <= 0) return 0;
+    return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost, stream);
+}

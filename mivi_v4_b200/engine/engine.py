@@ -8,12 +8,14 @@ benchmark all drive this function.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from collections import OrderedDict
+from typing import List, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch
 
-from ..cache import CacheError, KVNeed, SequenceCache
+from ..cache import CacheError, SequenceCache
+from ..ops import kernels as K
 from ..sampling import Sampler, SamplingParams
 from .generate import Request, run_generation
 from .model import Model
@@ -27,9 +29,30 @@ class StepError(ValueError):
     vocabulary, a wanted place outside the step's tokens, a full cache."""
 
 
+class _Recorded:
+    """A decode step of one shape (sequences, page-table widths), recorded as a CUDA graph over the
+    engine's decode workspace: the graph, where its logits land, and the host copy of the step's
+    integer arrays with the place of each array in it."""
+    __slots__ = ("graph", "logits", "n_kernels", "flat", "spans", "generation")
+
+    def __init__(self, graph, logits, n_kernels, flat, spans, generation):
+        self.graph, self.logits, self.n_kernels = graph, logits, n_kernels
+        self.flat, self.spans, self.generation = flat, spans, generation
+
+
+def _width_for(blocks: int) -> int:
+    """Page-table width of a recorded decode step: the next power of two, at least 8 pages, so that a
+    sequence that grows to n pages passes through about log2(n) recordings."""
+    w = 8
+    while w < blocks:
+        w *= 2
+    return w
+
+
 class Engine:
     def __init__(self, model: Model, *, max_tokens: int, max_batch: Optional[int] = None,
-                 page_size: int = 64, max_step_tokens: int = 8192, cuda_graphs: bool = True):
+                 page_size: int = 64, max_step_tokens: int = 8192, cuda_graphs: bool = True,
+                 max_graphs: int = 64):
         if model.dtype is None:
             raise ValueError("the model has no weights yet; use load_model()")
         if model.device.type != "cuda":
@@ -50,12 +73,18 @@ class Engine:
         self.max_positions = model.spec.max_positions
         self.steps_run = 0
         self.h2d_bytes = 0
-        # decode steps (one token per sequence, last logits wanted) replay a captured CUDA graph;
-        # key: (sequences, page-table widths) -> (graph, private workspace, logits, kernels in the graph)
+        # Decode steps (one token per sequence, last logits wanted) replay a recorded CUDA graph, one per
+        # shape (sequences, page-table widths).  All recordings work in ONE workspace and allocate from
+        # one graph memory pool, so a recording costs its launch records only; the least recently used
+        # go when there are more than ``max_graphs``.  When the workspace has to move a buffer (a
+        # larger batch than any before), the recordings made before name stale addresses and are dropped.
         self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
-        self._graphs: Dict[tuple, tuple] = {}
+        self.max_graphs = max(1, int(max_graphs))
+        self._graphs: "OrderedDict[tuple, _Recorded]" = OrderedDict()
+        self._gws = Workspace(self.device)
+        self._graph_pool = None
         self.graph_replays = 0
-        self._prepared: Optional[dict] = None             # a decode step laid out ahead of its tokens
+        self.graphs_recorded = 0
 
     # ---- sequences ------------------------------------------------------------
     def open(self) -> int:
@@ -63,7 +92,6 @@ class Engine:
         if self.cache.slots.free_count == 0 and self.cache.n_slots < self.total_pages:
             self.cache.grow_slots(min(self.total_pages, max(2 * self.cache.n_slots, 1)))
             self._graphs.clear()                          # the state storage moved
-            self._prepared = None
         return self.cache.assign()
 
     def close(self, slot: int) -> None:
@@ -73,6 +101,16 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def graph_keys(self) -> List[tuple]:
+        """The decode-step shapes recorded so far: (sequences, ((cache group, page-table width), ...))."""
+        return list(self._graphs)
+
+    def check_errors(self) -> None:
+        """Raise ``KernelError`` if a kernel of a step that the host has waited for reported a fault
+        (a bounded wait that ran out).  Costs nothing; call it where the host has just read a step's
+        results.  ``generate`` does so with every step's tokens."""
+        K.raise_seen_device_errors(self.device)
+
     # ---- the step function -----------------------------------------------------
     def step(self, items: Sequence[Tuple[int, Sequence[int]]], want: Want = "last",
              copy: bool = True) -> Optional[torch.Tensor]:
@@ -80,24 +118,20 @@ class Engine:
 
         ``want``: "last" (the last token of every sequence), "all", None, or
         one list of places per item (indices into that item's tokens).
-        Returns float32 logits [wanted, vocab] in the order of the items and,
-        within an item, of its places; None if nothing is wanted.
+        Returns float32 logits [wanted, vocab] on the device, in the order of the items and,
+        within an item, of its places; None if nothing is wanted.  With ``copy=False`` the
+        result is the engine's own buffer, valid until the next step.
         """
+        K.raise_seen_device_errors(self.device)
+        if self.cuda_graphs and isinstance(want, str) and want == "last":
+            logits = self._try_decode(items)
+            if logits is not None:
+                return logits.clone() if copy else logits
         try:
             items = [(int(s), np.asarray(toks, dtype=np.int64).ravel()) for s, toks in items]
         except (TypeError, ValueError):
-            raise StepError("token ids must be integers") from None
+            raise StepError("a step is a list of (slot, token ids) with integer token ids") from None
         V = self.model.vocab_size
-        prepared, self._prepared = self._prepared, None
-        if (prepared is not None and want == "last" and len(items) == len(prepared["slots"])
-                and all(s == ps and len(t) == 1 for (s, t), ps in zip(items, prepared["slots"]))
-                and self._graphs.get(prepared["key"]) is not None):
-            tokens = [int(t[0]) for _, t in items]
-            for (slot, _), t in zip(items, tokens):
-                if not 0 <= t < V:
-                    raise StepError(f"slot {slot}: token id {t} is outside the vocabulary of {V}")
-            logits = self._execute(prepared, tokens)
-            return logits.clone() if copy else logits
         seen = set()
         for slot, toks in items:
             if slot in seen:
@@ -117,12 +151,18 @@ class Engine:
                                 f"{self.max_positions}")
         if want is None:
             places: List[List[int]] = [[] for _ in items]
-        elif want == "last":
-            places = [[len(t) - 1] for _, t in items]
-        elif want == "all":
-            places = [list(range(len(t))) for _, t in items]
+        elif isinstance(want, str):
+            if want == "last":
+                places = [[len(t) - 1] for _, t in items]
+            elif want == "all":
+                places = [list(range(len(t))) for _, t in items]
+            else:
+                raise StepError(f'want={want!r}: known are "last", "all", None or one list of places per item')
         else:
-            places = [[int(i) for i in w] for w in want]
+            try:
+                places = [[int(i) for i in w] for w in want]
+            except (TypeError, ValueError):
+                raise StepError('want must be "last", "all", None or one list of integer places per item') from None
             if len(places) != len(items):
                 raise StepError(f"{len(places)} lists of wanted places for {len(items)} items")
             for (slot, toks), w in zip(items, places):
@@ -181,11 +221,13 @@ class Engine:
         return out
 
     def _run(self, items, places) -> Optional[torch.Tensor]:
-        return self._execute(self._plan(items, places))
-
-    def _plan(self, items, places) -> dict:
-        """Everything of a step that the host can work out before the token ids matter: room in the
-        cache, positions, page tables, and for a decode-shaped step the arrays laid out for its graph."""
+        """One step of at most ``max_step_tokens`` tokens, already checked."""
+        if self.cuda_graphs and all(len(t) == 1 for _, t in items) and all(w == [0] for w in places):
+            slots = np.fromiter((s for s, _ in items), dtype=np.int64, count=len(items))
+            toks = np.fromiter((int(t[0]) for _, t in items), dtype=np.int64, count=len(items))
+            logits = self._decode(slots, toks, None)
+            if logits is not None:
+                return logits
         slots = [s for s, _ in items]
         starts = [self.cache.length(s) for s in slots]
         for s, toks in items:
@@ -195,74 +237,127 @@ class Engine:
         for (_, toks), w in zip(items, places):
             out_rows.extend(row + i for i in w)
             row += len(toks)
-        decode = self.cuda_graphs and all(len(t) == 1 for _, t in items) and \
-            out_rows == list(range(len(items)))
-        # page tables of a decode step are padded to 8 pages so that one graph serves 512 tokens of growth
-        widths = {g: -(-max(len(self.cache._get(s).pages[g]) for s in slots) // 8) * 8 if decode else None
-                  for g in self.cache.kv_groups}
-        page_rows = {g: self.cache.page_rows(g, slots, widths[g]) for g in self.cache.kv_groups}
-        plan = dict(slots=slots, starts=starts, lists=[t for _, t in items], out_rows=out_rows,
-                    page_rows=page_rows, decode=decode, key=None, ctx=None)
-        if decode:
-            plan["key"] = (len(items), tuple(sorted(widths.items())))
-            entry = self._graphs.get(plan["key"])
-            if entry is not None:
-                plan["ctx"] = StepContext(slots=slots, starts=starts, token_lists=plan["lists"], out_rows=out_rows,
-                                          page_rows=page_rows, dtype=self.dtype, ws=entry[1], upload=False)
-        return plan
-
-    def _execute(self, plan: dict, tokens: Optional[List[int]] = None,
-                 device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-        """Run a planned step.  ``tokens`` replaces the token ids of a decode-shaped plan;
-        ``device_tokens`` (int32 [B], on the device) does the same without the host ever seeing them:
-        they are copied into the step's token array on the stream, after the other arrays went up."""
-        slots, starts, lists = plan["slots"], plan["starts"], plan["lists"]
-        if tokens is not None:
-            lists = [[t] for t in tokens]
-
-        def context(ws, reuse=None):
-            ctx = reuse
-            if ctx is None or ctx.ws is not ws:
-                ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=plan["out_rows"],
-                                  page_rows=plan["page_rows"], dtype=self.dtype, ws=ws, upload=False)
-            ctx.upload(np.concatenate([np.asarray(t).ravel() for t in lists]) if ctx is reuse else None)
-            if device_tokens is not None:
-                ctx.tokens.copy_(device_tokens, non_blocking=True)
-            return ctx
-
-        if not plan["decode"]:
-            ctx = context(self.ws)
-            logits = self.model.forward(ctx, self.cache)
-        else:
-            from ..ops import kernels as K
-            entry = self._graphs.get(plan["key"])
-            if entry is None:
-                # first time: run the step for real on a workspace of its own (which sizes every
-                # buffer), then record the same launches for the steps to come
-                # (the real run also notes which weights the products read, in order; recorded, each
-                # product of few rows then asks the L2 cache for its successor's weights)
-                from ..ops import linear as L
-                gws = Workspace(self.device)
-                ctx = context(gws)
-                with L.recording() as order:
-                    logits = self.model.forward(ctx, self.cache)
-                n0 = K.launch_count()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph), L.looking_ahead(order, self.model.weight_extents()):
-                    captured = self.model.forward(ctx, self.cache)
-                n_kernels = K.launch_count() - n0
-                K.add_launches(-n_kernels)                # recorded, not run
-                assert captured.data_ptr() == logits.data_ptr()
-                self._graphs[plan["key"]] = (graph, gws, logits, n_kernels)
-            else:
-                graph, gws, logits, n_kernels = entry
-                ctx = context(gws, plan["ctx"])
-                graph.replay()
-                K.add_launches(n_kernels)
-                self.graph_replays += 1
+        page_rows = {g: self.cache.page_rows(g, slots) for g in self.cache.kv_groups}
+        lists = [t for _, t in items]
+        ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
+                          page_rows=page_rows, dtype=self.dtype, ws=self.ws)
+        logits = self.model.forward(ctx, self.cache)
+        K.note_device_errors(self.device)
         for s, toks in zip(slots, lists):
             self.cache.advance(s, len(toks))
         self.steps_run += 1
+        self.h2d_bytes += ctx.h2d_bytes
+        return logits
+
+    # ---- decode steps: one token for each sequence, every row's logits ------------------------------
+    def _try_decode(self, items) -> Optional[torch.Tensor]:
+        """``items`` as a decode step if they are one: None sends the caller down the general path,
+        which also words the errors."""
+        B = len(items)
+        try:
+            if B == 0 or any(len(t) != 1 for _, t in items):
+                return None
+            slots = np.fromiter((s for s, _ in items), dtype=np.int64, count=B)
+            toks = np.fromiter((t[0] for _, t in items), dtype=np.int64, count=B)
+        except (TypeError, ValueError, IndexError):
+            return None
+        if int(toks.min()) < 0 or int(toks.max()) >= self.model.vocab_size:
+            return None
+        return self._decode(slots, toks, None)
+
+    def _decode(self, slots: np.ndarray, toks: Optional[np.ndarray],
+                device_tokens: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """One more token for each of ``slots`` (an array that names each slot once is checked here),
+        the token ids from the host (``toks``) or from the device (``device_tokens``, int32).  Works on
+        arrays over the sequences; the only per-sequence work is a new page when one crosses a page's
+        end.  Returns None, with nothing touched, if the step cannot run as it stands."""
+        cache = self.cache
+        B = int(slots.size)
+        if not cache.are_assigned(slots) or (B > 1 and np.unique(slots).size != B):
+            return None
+        lengths = cache.lengths_of(slots)
+        if self.max_positions is not None and int(lengths.max()) + 1 > self.max_positions:
+            return None
+        widths: tuple = ()
+        if cache.kv_groups:
+            blocks = lengths // self.page_size + 1
+            short = blocks > cache.blocks_of(slots)
+            if short.any():
+                need = int(short.sum())
+                if any(cache.pages[g].free_count < need for g in cache.kv_groups):
+                    return None
+                for s in slots[short].tolist():
+                    cache.reserve(s, 1)
+            width = _width_for(int(blocks.max()))
+            widths = tuple((g, width) for g in cache.kv_groups)
+        key = (B, widths)
+        rec = self._graphs.get(key)
+        if rec is not None and rec.generation != self._gws.generation:
+            del self._graphs[key]                         # recorded over buffers that have moved since
+            rec = None
+        if rec is None:
+            logits = self._record(key, slots, lengths, toks, device_tokens)
+        else:
+            self._graphs.move_to_end(key)
+            flat, spans = rec.flat, rec.spans
+            if toks is not None:
+                o = spans["tokens"][0]
+                flat[o:o + B] = toks
+            for name, values in (("positions", lengths), ("starts", lengths), ("slots", slots)):
+                o = spans[name][0]
+                flat[o:o + B] = values
+            for g, w in widths:
+                o, n = spans[f"pages{g}"]
+                flat[o:o + n] = cache.table_rows(g, slots, w).reshape(-1)
+            arena = self._gws.stage("step_meta", flat)
+            if device_tokens is not None:
+                o = spans["tokens"][0]
+                arena[o:o + B].copy_(device_tokens, non_blocking=True)
+            rec.graph.replay()
+            K.add_launches(rec.n_kernels)
+            self.graph_replays += 1
+            self.h2d_bytes += flat.size * 4
+            logits = rec.logits
+        cache.advance_each_by_one(slots)
+        self.steps_run += 1
+        return logits
+
+    def _record(self, key, slots: np.ndarray, lengths: np.ndarray, toks: Optional[np.ndarray],
+                device_tokens: Optional[torch.Tensor]) -> torch.Tensor:
+        """The first decode step of a shape: run it for real in the decode workspace (which sizes every
+        buffer and notes which weights the products read, in order), then record the same launches for
+        the steps to come; recorded, each product of few rows asks the L2 cache for its successor's
+        weights."""
+        from ..ops import linear as L
+        gws = self._gws
+        B = int(slots.size)
+        before = gws.generation
+        lists = [[int(t)] for t in toks] if toks is not None else [[0]] * B
+        page_rows = {g: self.cache.table_rows(g, slots, w).tolist() for g, w in key[1]}
+        ctx = StepContext(slots=slots.tolist(), starts=lengths.tolist(), token_lists=lists, out_rows=list(range(B)),
+                          page_rows=page_rows, dtype=self.dtype, ws=gws)
+        if device_tokens is not None:
+            ctx.tokens.copy_(device_tokens, non_blocking=True)
+        with L.recording() as order:
+            logits = self.model.forward(ctx, self.cache)
+        if gws.generation != before:
+            self._graphs.clear()                          # a buffer moved: older recordings name its old place
+        settled = gws.generation
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        n0 = K.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool), L.looking_ahead(order, self.model.weight_extents()):
+            captured = self.model.forward(ctx, self.cache)
+            K.note_device_errors(self.device)
+        n_kernels = K.launch_count() - n0
+        K.add_launches(-n_kernels)                        # recorded, not run
+        if captured.data_ptr() != logits.data_ptr() or gws.generation != settled:
+            raise RuntimeError("a decode step allocated while it was recorded; its recording cannot be replayed")
+        self._graphs[key] = _Recorded(graph, logits, n_kernels, ctx._flat, ctx.spans, settled)
+        self.graphs_recorded += 1
+        while len(self._graphs) > self.max_graphs:
+            self._graphs.popitem(last=False)
         self.h2d_bytes += ctx.h2d_bytes
         return logits
 
@@ -271,43 +366,14 @@ class Engine:
         on the device, e.g. what the sampling kernel just wrote): the step is enqueued without the host
         waiting for them.  Returns the logits of all, or None if the step cannot run now (no room in the
         cache, the context is full): the caller then waits for the tokens and calls ``step``."""
-        self._prepared = None
-        slots = [int(s) for s in slots]
-        if not slots or len(set(slots)) != len(slots) or device_tokens.numel() != len(slots) \
+        if not self.cuda_graphs or len(slots) == 0 or device_tokens.numel() != len(slots) \
                 or device_tokens.dtype != torch.int32 or not device_tokens.is_cuda:
             return None
         try:
-            if self.max_positions is not None and any(self.cache.length(s) + 1 > self.max_positions for s in slots):
-                return None
-            for g in self.cache.kv_groups:
-                need = sum(max(0, -(-(self.cache.length(s) + 1) // self.page_size)
-                               - len(self.cache._get(s).pages[g])) for s in slots)
-                if need > self.cache.pages[g].free_count:
-                    return None
-            plan = self._plan([(s, [0]) for s in slots], [[0]] * len(slots))
-        except CacheError:
+            arr = np.asarray(slots, dtype=np.int64)
+        except (TypeError, ValueError):
             return None
-        return self._execute(plan, device_tokens=device_tokens)
-
-    def prepare_decode(self, slots: Sequence[int]) -> None:
-        """Lay out the next step - one more token for each of ``slots``, logits of all - while the GPU
-        is still busy with the current one.  ``step`` uses the layout if it is then called with
-        exactly these slots and one token each; otherwise the layout is dropped."""
-        self._prepared = None
-        if not self.cuda_graphs:
-            return
-        try:
-            slots = [int(s) for s in slots]
-            if self.max_positions is not None and any(self.cache.length(s) + 1 > self.max_positions for s in slots):
-                return
-            for g in self.cache.kv_groups:
-                need = sum(max(0, -(-(self.cache.length(s) + 1) // self.page_size)
-                               - len(self.cache._get(s).pages[g])) for s in slots)
-                if need > self.cache.pages[g].free_count:
-                    return
-            self._prepared = self._plan([(s, [0]) for s in slots], [[0]] * len(slots))
-        except CacheError:
-            self._prepared = None
+        return self._decode(arr, None, device_tokens)
 
     # ---- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 256,
@@ -346,39 +412,43 @@ class _EngineBackend:
         The step AFTER this one is enqueued before the host waits for this one's tokens (the recent
         tokens that penalties look at are kept on the device by the sampling kernel itself): the
         sampling kernel's output is fed to the next step on the device, for every request that can
-        go on (it has tokens left to generate).  If a request then turns out to have stopped, its row of the early step is simply
-        not used; the other rows do not depend on it.  The next call finds its work already running."""
+        go on (it has tokens left to generate).  If a request then turns out to have stopped, its row
+        of the early step is simply not used; the other rows do not depend on it.  The next call finds
+        its work already running.  The sampler has two sets of buffers; a step and the one enqueued
+        early after it always use different ones."""
         sampler, eng = self.sampler, self.engine
         handles = [r.handle for r in requests]
-        early = self._early
-        self._early = None
+        early, self._early = self._early, None
         if (early is not None and set(handles) <= set(early["handles"])
                 and all(len(t) == 1 and self._last.get(h) == t[0] for h, t in zip(handles, token_lists))):
             rows = [early["handles"].index(h) for h in handles]
-            out_dev, host, event = early["out"], early["host"], early["event"]
+            out_dev, host, event, cur = early["out"], early["host"], early["event"], early["set"]
         else:
+            if early is not None and set(handles) & set(early["handles"]):
+                # the early step has already advanced these sequences by the tokens it sampled itself
+                raise RuntimeError("the generation loop fed other tokens than the ones sampled for its sequences")
+            cur = 1 - early["set"] if early is not None else 0
             logits = eng.step([(r.handle, t) for r, t in zip(requests, token_lists)], "last", copy=False)
             out_dev = sampler.launch(logits, [r.index for r in requests], [len(r.output) for r in requests],
-                                     [r.output for r in requests], states=handles)
-            host, event = sampler.read_async(out_dev)
+                                     [r.output for r in requests], slot=cur, states=handles)
+            host, event = sampler.read_async(out_dev, slot=cur)
             rows = list(range(len(requests)))
         # the step after this one, for the requests that will still have tokens to generate
         if eng.cuda_graphs:
             goers = [(i, r) for i, r in zip(rows, requests) if len(r.output) + 2 <= r.max_new_tokens]
-            if goers and len(goers) == len([r for r in requests if len(r.output) + 1 < r.max_new_tokens]):
-                src = out_dev if [i for i, _ in goers] == list(range(out_dev.numel())) else \
-                    out_dev[torch.tensor([i for i, _ in goers], device=out_dev.device)]
+            if goers:
+                picks = [i for i, _ in goers]
+                src = out_dev if picks == list(range(out_dev.numel())) else \
+                    out_dev[torch.tensor(picks, device=out_dev.device)]
                 nxt = eng.decode_from_device([r.handle for _, r in goers], src)
                 if nxt is not None:
                     out2 = sampler.launch(nxt, [r.index for _, r in goers], [len(r.output) + 1 for _, r in goers],
-                                          [[] for _ in goers], slot=1 - early["slot"] if early else 1,
-                                          states=[r.handle for _, r in goers])
-                    host2, event2 = sampler.read_async(out2, slot=1 - early["slot"] if early else 1)
+                                          [[] for _ in goers], slot=1 - cur, states=[r.handle for _, r in goers])
+                    host2, event2 = sampler.read_async(out2, slot=1 - cur)
                     self._early = dict(handles=[r.handle for _, r in goers], out=out2, host=host2, event=event2,
-                                       slot=1 - early["slot"] if early else 1)
-        else:
-            eng.prepare_decode(handles)
+                                       set=1 - cur)
         event.synchronize()
+        eng.check_errors()                       # exact here: the flag's copy was enqueued before the tokens'
         tokens = host.tolist()
         result = [tokens[i] for i in rows]
         self._last = dict(zip(handles, result))

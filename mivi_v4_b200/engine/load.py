@@ -36,7 +36,8 @@ def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", devi
 
 
 def random_model(config_dict: dict, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16",
-                 device: str = "cuda:0", model_dir: Optional[str] = None, on_device: bool = False) -> Model:
+                 device: str = "cuda:0", model_dir: Optional[str] = None, on_device: bool = False,
+                 init: str = "baseline") -> Model:
     """A model with random weights: written as a model folder (a temporary one
     unless ``model_dir`` is given) and loaded back, so it takes the same path
     as a checkpoint.  ``on_device`` draws the same distributions directly on
@@ -45,7 +46,7 @@ def random_model(config_dict: dict, seed: int = 0, dtype: Union[str, torch.dtype
     dtype = parse_dtype(dtype)
     if on_device:
         from ..weights.loader import run_dtype
-        from ..weights.random_init import _STD
+        from ..weights.random_init import init_std
         config, spec = describe_config(config_dict)
         model = Model(spec, config)
         gen = torch.Generator(device=device)
@@ -57,13 +58,13 @@ def random_model(config_dict: dict, seed: int = 0, dtype: Union[str, torch.dtype
             if ps.role == "table" or ps.init == "zeros":
                 named[name] = torch.zeros(ps.shape, dtype=rd, device=device)
                 continue
-            mean, std = _STD[ps.init]
+            mean, std = init_std(ps, init)
             t = torch.empty(ps.shape, dtype=torch.float32, device=device).normal_(mean, std, generator=gen)
             named[name] = t.to(torch.bfloat16).to(rd) if dtype == torch.bfloat16 else t
         model.load_params(named, dtype, device)
         return model
     store = "bfloat16" if dtype == torch.bfloat16 else "float32"
     if model_dir is not None:
-        return load_model(write_random_model(model_dir, config_dict, seed, store), dtype, device)
+        return load_model(write_random_model(model_dir, config_dict, seed, store, init), dtype, device)
     with tempfile.TemporaryDirectory(prefix="mivi_model_") as tmp:
-        return load_model(write_random_model(tmp, config_dict, seed, store), dtype, device)
+        return load_model(write_random_model(tmp, config_dict, seed, store, init), dtype, device)

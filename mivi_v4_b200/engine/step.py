@@ -23,6 +23,9 @@ class Workspace:
     def __init__(self, device):
         self.device = torch.device(device)
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        # counts the allocations: launches recorded while it had one value name addresses that are
+        # still the buffers' addresses for as long as it keeps that value
+        self.generation = 0
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -33,6 +36,7 @@ class Workspace:
         if buf is None or buf.numel() < n:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
     def bytes(self) -> int:
@@ -49,6 +53,7 @@ class Workspace:
         if buf is None or buf.numel() < n:
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
     def stage(self, name: str, values) -> torch.Tensor:
@@ -156,6 +161,7 @@ class StepContext:
         # filled by upload(), which may come later (a step can be laid out before its tokens are known)
         arena = ws.get("step_meta", (len(flat),), torch.int32)
         self._flat = flat
+        self.spans = spans                                   # name -> (first element, elements) in the arena
         self.h2d_bytes = len(flat) * 4
 
         def view(name: str) -> torch.Tensor:

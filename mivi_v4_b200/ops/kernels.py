@@ -35,6 +35,7 @@ _SIGNATURES = {
         "mv_embed_link_partials": [_I],
         "mv_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "mv_swiglu": [_P, _P, _I, _I, _I, _I, _P],
+        "mv_copy_to_host": [_P, _P, _Q, _P],
         "mv_gemm_simt": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_shortconv_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -365,25 +366,67 @@ def _link_args(x, M: int, N: int, K: int, mode: int, scale: Optional[NormLink], 
 
 
 _error_flags = {}
+_error_mirrors = {}
+_ERROR_ROLES = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "a guarded index"}
 
 
 def _error_flag(device) -> torch.Tensor:
-    """One int per device that a kernel sets when one of its bounded waits ran out."""
+    """One int per device that a kernel sets when one of its bounded waits ran out (or, in a build
+    with index checks, when an index lay outside its bounds)."""
     key = torch.device(device).index or 0
     if key not in _error_flags:
         _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _error_flags[key]
 
 
+def _error_text(key: int, code: int) -> str:
+    role = _ERROR_ROLES.get(code, f"code {code}")
+    if code == 4:
+        return (f"a kernel on cuda:{key} was handed an index outside its bounds (a page or a slot); it skipped "
+                f"the access and its output is not valid")
+    return (f"a tensor-core kernel on cuda:{key} gave up waiting on a barrier in {role}; "
+            f"its output is not valid")
+
+
+def note_device_errors(device) -> None:
+    """Enqueue a copy of the device's error flag into pinned host memory, on the current stream
+    (may be recorded into a CUDA graph).  ``raise_seen_device_errors`` looks at that copy."""
+    key = torch.device(device).index or 0
+    mirror = _error_mirrors.get(key)
+    if mirror is None:
+        mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _error_mirrors[key] = mirror
+    code = _fn("core", "mv_copy_to_host")(mirror.data_ptr(), _error_flag(device).data_ptr(), 4, _stream())
+    if code != 0:
+        raise KernelError(f"copying the error flag to the host failed with CUDA error {code}")
+
+
+def raise_seen_device_errors(device) -> None:
+    """Raise if a copy of the error flag that has arrived on the host is set; does not wait for the
+    device.  Exact where the host has just waited for work enqueued after ``note_device_errors``."""
+    key = torch.device(device).index or 0
+    mirror = _error_mirrors.get(key)
+    if mirror is None:
+        return
+    code = int(mirror[0])
+    if code:
+        torch.cuda.synchronize(device)
+        _error_flags[key].zero_()
+        torch.cuda.synchronize(device)
+        mirror.zero_()
+        raise KernelError(_error_text(key, code))
+
+
 def check_device_errors() -> None:
-    """Raise if a kernel reported that a wait ran out (synchronises the device)."""
+    """Raise if a kernel reported a fault (synchronises the device)."""
     for key, flag in _error_flags.items():
         code = int(flag.item())
         if code:
             flag.zero_()
-            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"code {code}")
-            raise KernelError(f"a tensor-core kernel on cuda:{key} gave up waiting on a barrier in {role}; "
-                              f"its output is not valid")
+            if key in _error_mirrors:
+                torch.cuda.synchronize(flag.device)
+                _error_mirrors[key].zero_()
+            raise KernelError(_error_text(key, code))
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,

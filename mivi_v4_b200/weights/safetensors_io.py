@@ -42,8 +42,12 @@ class TensorEntry:
 
 
 def read_header(path: str) -> Dict[str, TensorEntry]:
-    size = os.path.getsize(path)
-    with open(path, "rb") as f:
+    try:
+        size = os.path.getsize(path)
+        f = open(path, "rb")
+    except OSError as e:
+        raise SafetensorsError(f"{path}: cannot be read ({e.strerror or e})") from None
+    with f:
         head = f.read(8)
         if len(head) < 8:
             raise SafetensorsError(f"{path}: {size} bytes is too short for a safetensors file")
@@ -109,8 +113,13 @@ def read_model_headers(model_dir: str) -> Dict[str, TensorEntry]:
             except (json.JSONDecodeError, KeyError, TypeError):
                 raise SafetensorsError(f"{index}: no weight_map") from None
         out: Dict[str, TensorEntry] = {}
+        if not isinstance(weight_map, dict) or not all(isinstance(v, str) for v in weight_map.values()):
+            raise SafetensorsError(f"{index}: weight_map must map tensor names to file names")
         for shard in sorted(set(weight_map.values())):
-            out.update(read_header(os.path.join(model_dir, shard)))
+            path = os.path.join(model_dir, shard)
+            if not os.path.isfile(path):
+                raise SafetensorsError(f"{index} names the shard {shard!r}, which is not in the folder")
+            out.update(read_header(path))
         return out
     raise SafetensorsError(f"{model_dir}: neither model.safetensors nor model.safetensors.index.json")
 

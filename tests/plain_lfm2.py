@@ -105,8 +105,25 @@ def plain_rope(v: torch.Tensor, positions: torch.Tensor, theta: float,
     return out
 
 
+def _same(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def round_to(storage: torch.dtype):
+    """A function that rounds a tensor to ``storage`` and widens it again.  Passed as ``rnd`` to the
+    functions below, it is applied where a run in that storage dtype keeps an activation between two
+    kernels: the inputs of the matrix products after the norms, the gated convolution's result, the
+    queries, the cached keys and values, the softmax weights, the attention's result and the
+    SwiGLU product.  Sums, norms, the softmax and the residual stream stay in the working dtype.
+    The difference to a run without ``rnd`` is the rounding noise that such a run may show."""
+    def rnd(t: torch.Tensor) -> torch.Tensor:
+        return t.to(storage).to(t.dtype)
+    return rnd
+
+
 def plain_short_conv(u: torch.Tensor, w_in: torch.Tensor, w_conv: torch.Tensor,
-                     w_out: torch.Tensor, b_in=None, b_conv=None, b_out=None) -> torch.Tensor:
+                     w_out: torch.Tensor, b_in=None, b_conv=None, b_out=None, rnd=_same,
+                     return_state: bool = False) -> torch.Tensor:
     """Gated short convolution over a whole sequence u [T, H] (already normed).
 
     p = u W_in^T; B, C, X = thirds of p in that order; bx = B*X;
@@ -134,16 +151,24 @@ def plain_short_conv(u: torch.Tensor, w_in: torch.Tensor, w_conv: torch.Tensor,
                 y[t] += w_conv[:, j] * bx[src]
     if b_conv is not None:
         y = y + b_conv
-    z = Cg * y
+    z = rnd(Cg * y)
     out = z @ w_out.T
     if b_out is not None:
         out = out + b_out
+    if return_state:
+        # what a cache keeps of this layer after the sequence: the last k-1 values of B*x, oldest first
+        # (zeros where the sequence is shorter), crates/mivi-model/src/ssm.rs:87-108
+        state = torch.zeros(k - 1, H, dtype=u.dtype)
+        n = min(k - 1, T)
+        if n:
+            state[k - 1 - n:] = bx[T - n:]
+        return out, state
     return out
 
 
 def plain_attention(u: torch.Tensor, wq, wk, wv, wo, q_norm_w, k_norm_w, *, nh: int,
                     nkv: int, hd: int, eps: float, theta: float, style: str,
-                    window: int = 0, kv=None, return_kv: bool = False):
+                    window: int = 0, kv=None, return_kv: bool = False, rnd=_same):
     """Grouped-query attention over a whole sequence u [T, H] (already normed).
 
     q, k, v projections without bias; per-head RMSNorm of q and k with one
@@ -165,13 +190,13 @@ def plain_attention(u: torch.Tensor, wq, wk, wv, wo, q_norm_w, k_norm_w, *, nh: 
     q = (u @ wq.T).reshape(T, nh, hd)
     if q_norm_w is not None:
         q = plain_rms_norm(q, q_norm_w, eps)
-    q = plain_rope(q, pos, theta, style)
+    q = rnd(plain_rope(q, pos, theta, style))
     if kv is None:
         k = (u @ wk.T).reshape(T, nkv, hd)
         v = (u @ wv.T).reshape(T, nkv, hd)
         if k_norm_w is not None:
             k = plain_rms_norm(k, k_norm_w, eps)
-        k = plain_rope(k, pos, theta, style)
+        k, v = rnd(plain_rope(k, pos, theta, style)), rnd(v)
     else:
         k, v = kv
     group = nh // nkv
@@ -187,12 +212,12 @@ def plain_attention(u: torch.Tensor, wq, wk, wv, wo, q_norm_w, k_norm_w, *, nh: 
             mask = mask & (j > i - window)
         s = s.masked_fill(~mask, float("-inf"))
         p = torch.softmax(s, dim=-1)
-        out[:, h, :] = p @ v[:, g, :]
-    res = out.reshape(T, nh * hd) @ wo.T
+        out[:, h, :] = rnd(p) @ v[:, g, :]
+    res = rnd(out.reshape(T, nh * hd)) @ wo.T
     return (res, (k, v)) if return_kv else res
 
 
-def plain_swiglu(g: torch.Tensor, w1, w3, w2) -> torch.Tensor:
+def plain_swiglu(g: torch.Tensor, w1, w3, w2, rnd=_same) -> torch.Tensor:
     """(silu(g W1^T) * (g W3^T)) W2^T with silu(a) = a / (1 + e^-a).
 
     crates/mivi-model/src/ffn.rs:67-103, crates/mivi-core/src/math.rs:76-98,
@@ -200,7 +225,7 @@ def plain_swiglu(g: torch.Tensor, w1, w3, w2) -> torch.Tensor:
     """
     a = g @ w1.T
     b = g @ w3.T
-    return ((a / (1.0 + torch.exp(-a))) * b) @ w2.T
+    return rnd((a / (1.0 + torch.exp(-a))) * b) @ w2.T
 
 
 # --------------------------------------------------------------------------
@@ -218,25 +243,31 @@ def _opt(weights: dict, name: str, dtype):
 
 
 def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64,
-                  return_hidden: bool = False) -> torch.Tensor:
+                  return_hidden: bool = False, rnd=_same, return_residuals: bool = False,
+                  return_cache: bool = False) -> torch.Tensor:
     """Logits [T, V] of one whole sequence of token ids, no cache.
 
     Embedding row gather (crates/mivi-model/src/model.rs:355-366); per layer
     operator norm -> mixer -> residual, ffn norm -> SwiGLU -> residual
     (ssm.rs:65,155-166; transformer.rs:317,338; ffn.rs:64,106); final norm and
     the head, which is the embedding itself when tied (model.rs:437-473).
+    ``rnd``: see :func:`round_to`.  ``return_residuals``: the residual stream after
+    every layer, [layers, T, H], instead of the logits.  ``return_cache``: what a cache holds after
+    the sequence, instead of the logits: {"kv": [attention layers, 2, T, kv heads, head_dim] (keys after
+    norm and rotation, values), "state": [conv layers, k-1, H] (the last k-1 values of B*x)}.
     """
     d = plain_dims(cfg)
     H, eps = d["H"], d["eps"]
     tok = torch.as_tensor(tokens, dtype=torch.long)
     E = _w(weights, "model.embed_tokens.weight", dtype)
     x = E[tok]
+    residuals, kept_kv, kept_state = [], [], []
     for i, kind in enumerate(d["layer_types"]):
         pre = f"model.layers.{i}."
-        u = plain_rms_norm(x, _w(weights, pre + "operator_norm.weight", dtype), eps)
+        u = rnd(plain_rms_norm(x, _w(weights, pre + "operator_norm.weight", dtype), eps))
         if kind == "conv":
             b = d["bias"]
-            x = x + plain_short_conv(
+            y, state = plain_short_conv(
                 u,
                 _w(weights, pre + "conv.in_proj.weight", dtype),
                 _w(weights, pre + "conv.conv.weight", dtype),
@@ -244,9 +275,12 @@ def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64,
                 _w(weights, pre + "conv.in_proj.bias", dtype) if b else None,
                 _w(weights, pre + "conv.conv.bias", dtype) if b else None,
                 _w(weights, pre + "conv.out_proj.bias", dtype) if b else None,
+                rnd=rnd, return_state=True,
             )
+            x = x + y
+            kept_state.append(state)
         elif kind == "full_attention":
-            x = x + plain_attention(
+            y, (k_, v_) = plain_attention(
                 u,
                 _w(weights, pre + "self_attn.q_proj.weight", dtype),
                 _w(weights, pre + "self_attn.k_proj.weight", dtype),
@@ -255,18 +289,27 @@ def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64,
                 _opt(weights, pre + "self_attn.q_layernorm.weight", dtype),
                 _opt(weights, pre + "self_attn.k_layernorm.weight", dtype),
                 nh=d["nh"], nkv=d["nkv"], hd=d["hd"], eps=eps, theta=d["theta"],
-                style=d["rope_style"],
+                style=d["rope_style"], rnd=rnd, return_kv=True,
             )
+            x = x + y
+            kept_kv.append(torch.stack([k_, v_]))
         else:
             raise ValueError(kind)
-        g = plain_rms_norm(x, _w(weights, pre + "ffn_norm.weight", dtype), eps)
+        g = rnd(plain_rms_norm(x, _w(weights, pre + "ffn_norm.weight", dtype), eps))
         x = x + plain_swiglu(
             g,
             _w(weights, pre + "feed_forward.w1.weight", dtype),
             _w(weights, pre + "feed_forward.w3.weight", dtype),
             _w(weights, pre + "feed_forward.w2.weight", dtype),
+            rnd=rnd,
         )
-    f = plain_rms_norm(x, _w(weights, "model.embedding_norm.weight", dtype), eps)
+        residuals.append(x)
+    if return_residuals:
+        return torch.stack(residuals)
+    if return_cache:
+        return {"kv": torch.stack(kept_kv) if kept_kv else None,
+                "state": torch.stack(kept_state) if kept_state else None}
+    f = rnd(plain_rms_norm(x, _w(weights, "model.embedding_norm.weight", dtype), eps))
     if return_hidden:
         return f
     W = E if d["tied"] else _w(weights, "lm_head.weight", dtype)

@@ -191,6 +191,36 @@ def test_sharded_folder(tmp_path):
     assert torch.equal(m.embedding.weight, t["model.embed_tokens.weight"].float())
 
 
+def test_missing_shard_is_a_weights_error(tmp_path):
+    d = write_random_model(str(tmp_path / "m"), TINY_A, seed=0)
+    os.rename(os.path.join(d, "model.safetensors"), os.path.join(d, "model-00001-of-00002.safetensors"))
+    names = list(read_header(os.path.join(d, "model-00001-of-00002.safetensors")))
+    wm = {n: "model-00001-of-00002.safetensors" for n in names[:-1]}
+    wm[names[-1]] = "model-00002-of-00002.safetensors"
+    json.dump({"weight_map": wm}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
+    with pytest.raises(WeightsError, match="model-00002-of-00002.safetensors"):
+        load_model(d, "float32", "cpu")
+
+
+def test_loud_init_and_storage_overrides(tmp_path):
+    """``init="loud"``: matrices with standard deviation 1/sqrt(columns); ``store_overrides`` keeps single
+    tensors in another dtype, which the loader then leaves in 32-bit in a bfloat16 run."""
+    over = {"model.layers.0.feed_forward.w2.weight": "float32"}
+    d = write_random_model(str(tmp_path / "m"), TINY_A, seed=3, init="loud", store_overrides=over)
+    entries = read_model_headers(d)
+    assert entries["model.layers.0.feed_forward.w2.weight"].dtype == "F32"
+    assert entries["model.layers.0.feed_forward.w1.weight"].dtype == "BF16"
+    m = load_model(d, "bfloat16", "cpu")
+    ffn = m.blocks[0].ffn
+    assert ffn.w2.dtype == torch.float32 and ffn.w13.dtype == torch.bfloat16
+    w = m.blocks[0].mixer.w_in.float()
+    assert abs(w.std().item() * TINY_A["hidden_size"] ** 0.5 - 1.0) < 0.1
+    with pytest.raises(ValueError, match="does not have"):
+        write_random_model(str(tmp_path / "n"), TINY_A, seed=3, store_overrides={"nope": "float32"})
+    with pytest.raises(ValueError, match="init"):
+        write_random_model(str(tmp_path / "n"), TINY_A, seed=3, init="quiet")
+
+
 def test_weight_order_hints_follow_the_recorded_order():
     """The order of a step's products is noted once; replayed in that order each product learns its
     successor's weights (the last one the first's), capped in size; any other order ends the hints."""

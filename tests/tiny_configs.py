@@ -49,6 +49,23 @@ TINY_F = dict(
 CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4),
            "F": (TINY_F, 5)}
 
+# The same configurations with every part loud (``init="loud"``: matrices with standard deviation
+# 1/sqrt(columns)): with N(0, 0.02) matrices at these widths a gated convolution moves the logits by less
+# than a bfloat16 run's rounding, so a fault in one would pass unseen.
+LOUD_CONFIGS = {"AL": (TINY_A, 0), "BL": (TINY_B, 1), "FL": (TINY_F, 5)}
+
+
+def all_folders(root):
+    """Model folders for every configuration above: name -> folder."""
+    from helpers import write_model
+    out = {k: write_model(root, cfg, seed) for k, (cfg, seed) in CONFIGS.items()}
+    out.update({k: write_model(root, cfg, seed, init="loud") for k, (cfg, seed) in LOUD_CONFIGS.items()})
+    return out
+
+
+def config_of(name: str) -> dict:
+    return (CONFIGS.get(name) or LOUD_CONFIGS[name])[0]
+
 
 def prompts(vocab: int, lengths, seed: int = 0):
     g = torch.Generator().manual_seed(seed)
