@@ -5,14 +5,19 @@ weights on one B200, in the manner of the reference's ``bench`` command
 prefill, then generation timed without its first token).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16]
-    python bench.py --workload unequal32 | long32k      (the two further workloads, one JSON line each)
+    python bench.py --workload unequal32 | long32k      (the two further workloads, the same line for each)
+    python bench.py --stages decode|prefill [--batch B] (where a step's time goes, by stage and kernel)
+    python bench.py --kernel NAME [--m .. --n .. --k ..] (one kernel alone, for timing and for profilers)
 
 One "step" is one decode step of the whole batch.  Prints ONE JSON line:
 ``value`` is decoded tokens per second timed on the device over exactly K
 steps; ``e2e`` is the same through ``Engine.generate`` with host token lists in
-and out; ``prefill`` is one 2,048-token prompt; ``roofline`` compares the bytes
-a decode step must read (every weight once, the cache of the live sequences)
-with the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
+and out; ``prefill`` is one 2,048-token prompt (the workloads: their own unequal
+prompts in one step); ``roofline`` compares the bytes a decode step must read
+(every weight once, the cache of the live sequences) with the measured copy
+bandwidth; ``points`` holds decode at batch 1 and 64 with their own fractions.
+The timing itself is the library's (``mivi_v4_b200/measure.py``); this file adds
+the benchmark's configurations, the clocks and the line.
 """
 import argparse
 import json
@@ -171,166 +176,108 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "source": source}
 
 
-def model_numbers(model, cfg):
-    """Bytes and flops of the benchmark's steps, from the model itself."""
-    c = model.config
-    H, F, V, hd, nh, nkv = c.hidden_size, c.ff_dim, c.vocab_size, c.head_dim, c.num_attention_heads, c.num_key_value_heads
-    n_attn, n_conv = len(c.attn_layer_ids), len(c.conv_layer_ids)
-    per_tok_matrix = (n_conv * (3 * H * H + H * H) + n_attn * ((nh + 2 * nkv) * hd * H + nh * hd * H)
-                      + c.num_hidden_layers * 3 * H * F)
-    kv_bytes_per_token = n_attn * 2 * nkv * hd * 2
-    return dict(weight_bytes=model.weight_bytes(), kv_bytes_per_token=kv_bytes_per_token,
-                conv_state_bytes=n_conv * (c.conv_L_cache - 1) * H * 4,
-                gemm_flops_per_token=2 * per_tok_matrix, head_flops_per_row=2 * V * H,
-                attn_flops=lambda T: n_attn * 4 * nh * hd * T * (T + 1) // 2)
+WORKLOADS = {
+    # LFM2-700M shape: 32 prompts of 64..2,048 tokens in one unequal prefill step, 256 decode steps
+    "unequal32": dict(sizes=dict(hidden_size=1536, num_attention_heads=24, num_key_value_heads=8, block_ff_dim=10240),
+                      model="LFM2-700M shape", new=256),
+    # LFM2-350M shape: 8 prompts of 32,768 tokens, 128 decode steps (keys and values only for the six
+    # attention layers, convolution state for the ten others)
+    "long32k": dict(sizes=dict(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, block_ff_dim=6656),
+                    model="LFM2-350M shape", new=128),
+}
 
 
-def time_decode(model, batch, steps, warmup, seed=0):
-    """Device time of exactly ``steps`` decode steps of ``batch`` sequences that
-    each hold a PROMPT-token prompt; greedy sampling on the device included."""
+def workload_lengths(which: str):
     import torch
-    from mivi_v4_b200 import Engine
-    from mivi_v4_b200.ops import kernels as K
-    eng = Engine(model, max_tokens=batch * CONTEXT, max_batch=batch)
-    g = torch.Generator().manual_seed(seed)
-    V = model.vocab_size
-    prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(batch)]
-    feed = torch.randint(0, V, (warmup + steps, batch), generator=g).tolist()
-    slots = [eng.open() for _ in range(batch)]
-    eng.step(list(zip(slots, prompts)), None)
-    work = torch.empty((batch, V), dtype=torch.float32, device=model.device)
-    out = torch.empty((batch,), dtype=torch.int32, device=model.device)
-
-    def one(i):
-        logits = eng.step([(s, [feed[i][b]]) for b, s in enumerate(slots)], "last", copy=False)
-        K.sample(logits, work, out, temperature=0.0)
-
-    for i in range(warmup):
-        one(i)
-    torch.cuda.synchronize()
-    launches0 = K.launch_count()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(warmup, warmup + steps):
-        one(i)
-    t1.record()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / steps
-    launches = K.launch_count() - launches0
-    ctx_mean = PROMPT + warmup + (steps - 1) / 2.0
-    for s in slots:
-        eng.close(s)
-    del eng
-    torch.cuda.empty_cache()
-    return ms, launches, ctx_mean
-
-
-def time_e2e(model, batch, steps, warmup, seed=1):
-    """The same through the public entry point: host token lists in, host token
-    lists out, one host->device copy of the step's inputs and one device->host
-    read of the sampled tokens every step.  Timed from the first emitted token
-    to the return, as the reference times decoding without its first token."""
-    import torch
-    from mivi_v4_b200 import Engine, SamplingParams
-    eng = Engine(model, max_tokens=batch * CONTEXT, max_batch=batch)
-    g = torch.Generator().manual_seed(seed)
-    prompts = [torch.randint(0, model.vocab_size, (PROMPT,), generator=g).tolist() for _ in range(batch)]
-    eng.generate(prompts, warmup + 1, SamplingParams.greedy(), stop_token_ids=[])
-    first = {}
-    h2d0 = None
-
-    def on_token(i, tok):
-        nonlocal h2d0
-        if "t" not in first:
-            first["t"] = time.perf_counter()
-            h2d0 = eng.h2d_bytes
-    torch.cuda.synchronize()
-    out = eng.generate(prompts, steps + 1, SamplingParams.greedy(), stop_token_ids=[], on_token=on_token)
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - first["t"]
-    assert all(len(o) == steps + 1 for o in out)
-    h2d = (eng.h2d_bytes - h2d0) / steps + 2 * batch * 4
-    del eng
-    torch.cuda.empty_cache()
-    return batch * steps / dt, h2d, batch * 4
-
-
-def time_prefill(model, reps, warmup, seed=2):
-    import torch
-    from mivi_v4_b200 import Engine
-    eng = Engine(model, max_tokens=2 * PREFILL_TOKENS, max_batch=2, max_step_tokens=PREFILL_TOKENS)
-    g = torch.Generator().manual_seed(seed)
-    times = []
-    for i in range(warmup + reps):
-        toks = torch.randint(0, model.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
-        s = eng.open()
-        torch.cuda.synchronize()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        eng.step([(s, toks)], "last", copy=False)
-        t1.record()
-        torch.cuda.synchronize()
-        if i >= warmup:
-            times.append(t0.elapsed_time(t1))
-        eng.close(s)
-    del eng
-    torch.cuda.empty_cache()
-    return statistics.median(times)
-
-
-def further_workload(which: str) -> int:
-    """The two further workloads of the benchmark set, through ``Engine.generate``:
-    ``unequal32``: LFM2-700M shape, 32 prompts of 64..2,048 tokens in one unequal prefill step, 256 new tokens;
-    ``long32k``: LFM2-350M shape, 8 prompts of 32,768 tokens, 128 new tokens (keys and values only for the six
-    attention layers, convolution state for the ten others).  Prefill is timed to the first token, decoding
-    from the first token to the end."""
-    import torch
-    from mivi_v4_b200 import Engine, SamplingParams, random_model
-    cfg = dict(BENCH_CONFIG)
     if which == "long32k":
-        cfg.update(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, block_ff_dim=6656)
-        lens, new = [32768] * 8, 128
-    else:
-        cfg.update(hidden_size=1536, num_attention_heads=24, num_key_value_heads=8, block_ff_dim=10240)
-        g = torch.Generator().manual_seed(0)
-        lens, new = torch.randint(64, 2049, (32,), generator=g).tolist(), 256
-    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
-    eng = Engine(model, max_tokens=sum(-(-(n + new) // 64) * 64 for n in lens), max_batch=len(lens))
-    g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, model.vocab_size, (n,), generator=g).tolist() for n in lens]
-    eng.generate([p[:64] for p in prompts[:2]], 4, SamplingParams.greedy(), stop_token_ids=[])       # warm-up
-    first = {}
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    out = eng.generate(prompts, new, SamplingParams.greedy(), stop_token_ids=[],
-                       on_token=lambda i, t: first.setdefault("t", time.perf_counter()))
-    torch.cuda.synchronize()
-    t1 = time.perf_counter()
-    assert all(len(o) == new for o in out)
+        return [32768] * 8
+    g = torch.Generator().manual_seed(0)
+    return torch.randint(64, 2049, (32,), generator=g).tolist()
+
+
+def flat_config(model, name, layers, layers_full, batch, prompt_note, context, pk_src, weight_bytes):
+    """Every size of the run, flat (at most 20 keys)."""
     c = model.config
+    return {
+        "model": name, "layers": layers, "layers_full": layers_full, "attention_layers": len(c.attn_layer_ids),
+        "hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
+        "head_dim": c.head_dim, "ff": c.ff_dim, "vocab": c.vocab_size, "conv_width": c.conv_L_cache,
+        "tied": c.tie_embedding, "global_batch": batch, "seq_len": context, "prompt_len": prompt_note,
+        "parallelism": "single GPU",
+        "l2": "inputs larger than L2 (a step reads %.2f GB of weights)" % (weight_bytes / 1e9), "peaks": pk_src,
+    }
+
+
+def decode_point(nums, res, batch, pk):
+    """tokens/s, bytes a step, GB/s and the fraction of the copy bandwidth of a timed decode run."""
+    step_bytes = nums["weight_bytes"] + batch * (res["cached_tokens_mean"] * nums["kv_bytes_per_token"]
+                                                 + nums["state_bytes_per_seq"])
+    gbs = step_bytes / (res["ms_per_step"] * 1e-3) / 1e9
+    return dict(value=batch * 1000.0 / res["ms_per_step"], ms_per_step=res["ms_per_step"], bytes_per_step=step_bytes,
+                gb_per_s=gbs, frac=gbs / pk["hbm_gbs"])
+
+
+def run_workload(which: str, steps_arg, warmup: int) -> int:
+    """One of the two further workloads, reported like the default run: decode steps timed on the device
+    (``value``, ``ms_per_step``, ``roofline``), the unequal prefill step of all prompts (``prefill``), the
+    same through ``Engine.generate`` (``e2e``), the clocks, every size."""
+    import torch
+    from mivi_v4_b200 import measure, random_model
+    w = WORKLOADS[which]
+    cfg = dict(BENCH_CONFIG)
+    cfg.update(w["sizes"])
+    lens = workload_lengths(which)
+    B, new = len(lens), w["new"]
+    steps = new - warmup if steps_arg is None else steps_arg
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+    nums = measure.model_numbers(model)
+    pk, pk_src = peaks()
+    with ClockSampler() as clk:
+        res = measure.decode_run(model, lens, steps, warmup)
+        e = measure.generate_run(model, lens, new)
+    clocks = clk.summary()
+    point = decode_point(nums, res, B, pk)
+    T = sum(lens)
+    pre_flops = T * nums["gemm_flops_per_token"] + sum(nums["attn_flops"](n) for n in lens)    # no logits wanted
+    pre_tflops = pre_flops / (res["prefill_ms"] * 1e-3) / 1e12
     print(json.dumps({
-        "workload": which, "impl": "ours", "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)",
-        "prompt_tokens": sum(lens), "prefill_tokens_per_s": sum(lens) / (first["t"] - t0),
-        "decode_tokens_per_s": len(lens) * (new - 1) / (t1 - first["t"]), "new_tokens_each": new,
-        "peak_memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30, "cache_gib": eng.cache.bytes() / 2 ** 30,
-        "config": {"hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
-                   "ff": c.ff_dim, "layers": c.num_hidden_layers, "vocab": c.vocab_size, "batch": len(lens),
-                   "longest_prompt": max(lens), "shortest_prompt": min(lens)}}))
+        "metric": f"decode tokens/s, {w['model']}, bf16, random weights ({which})", "workload": which,
+        "value": point["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)", "impl": "ours",
+        "config": flat_config(model, w["model"], FULL_LAYERS, FULL_LAYERS, B,
+                              f"{min(lens)}..{max(lens)} (sum {T})", max(lens) + new, pk_src, nums["weight_bytes"]),
+        "clocks": clocks, "gpu_launches": res["launches"],
+        "prefill": {"value": T / (res["prefill_ms"] * 1e-3), "tokens": T, "ms": res["prefill_ms"], "tflops": pre_tflops,
+                    "frac": pre_tflops / pk["bf16_tflops"]},
+        "roofline": {"bound": "hbm", "bytes_per_step": point["bytes_per_step"], "achieved": point["gb_per_s"],
+                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": point["frac"]},
+        "e2e": {"value": e["decode_tokens_per_s"], "unit": "tokens/s", "prefill_tokens_per_s": e["prefill_tokens_per_s"],
+                "h2d_bytes_per_step": e["h2d_bytes_per_step"], "d2h_bytes_per_step": e["d2h_bytes_per_step"]},
+        "peak_memory_gib": e["peak_memory_bytes"] / 2 ** 30, "cache_gib": e["cache_bytes"] / 2 ** 30}))
     return 0
 
 
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=None, help="timed decode steps (default 64; a workload: all of its own)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help="run the first LAYERS layers of the 16 (sizes unchanged); both numbers go into config")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the end-to-end run")
-    ap.add_argument("--workload", default=None, choices=["unequal32", "long32k"],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the two further workloads instead of the default benchmark")
+    ap.add_argument("--stages", default=None, choices=["decode", "prefill"],
+                    help="print where the time of a decode step (of --batch sequences) or of the prefill goes")
+    ap.add_argument("--kernel", default=None, help="time one kernel alone (see --m/--n/--k, --context, --tokens)")
+    for name, default in (("m", 8), ("n", 16384), ("k", 2048), ("context", 520), ("tokens", PREFILL_TOKENS),
+                          ("heads", 32), ("kv-heads", 8), ("head-dim", 64), ("vocab", 65536), ("reps", 20)):
+        ap.add_argument("--" + name, type=int, default=default)
+    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--accumulate", action="store_true")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -343,65 +290,77 @@ def main() -> int:
                           "n_gpus": args.gpus}))
         return 2
     warmup = max(3, args.warmup)
-    if args.workload:
-        return further_workload(args.workload)
 
     import torch
-    from mivi_v4_b200 import random_model
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
+    from mivi_v4_b200 import measure, random_model
+    if args.kernel:
+        if args.kernel not in measure.KERNELS:
+            print(json.dumps({"error": f"unknown kernel {args.kernel!r}", "known": list(measure.KERNELS)}))
+            return 2
+        print(json.dumps(measure.kernel_run(
+            args.kernel, m=args.m, n=args.n, k=args.k, swiglu=args.swiglu, accumulate=args.accumulate, batch=args.batch,
+            context=args.context, tokens=args.tokens, heads=args.heads, kv_heads=args.kv_heads, head_dim=args.head_dim,
+            vocab=args.vocab, reps=args.reps)))
+        return 0
+    if args.workload:
+        return run_workload(args.workload, args.steps, warmup)
+
+    steps = 64 if args.steps is None else args.steps
     cfg = dict(BENCH_CONFIG)
     if args.layers != FULL_LAYERS:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]
         cfg["num_hidden_layers"] = args.layers
     model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
-    nums = model_numbers(model, cfg)
+    nums = measure.model_numbers(model)
     pk, pk_src = peaks()
+    if args.stages:
+        lens = [PREFILL_TOKENS] if args.stages == "prefill" else [PROMPT] * args.batch
+        rep = measure.stage_report(model, lens, prefill=args.stages == "prefill")
+        measure.print_stage_report(rep, f"{args.stages} step, {len(lens)} sequence(s) of {lens[0]} tokens, LFM2.5-1.2B shape", pk)
+        return 0
 
     # the clocks are sampled over all the timed regions of this run (the K decode steps alone are
     # shorter than one sampling period)
     with ClockSampler() as clk:
-        ms, launches, ctx_mean = time_decode(model, args.batch, args.steps, warmup)
-        value = args.batch * 1000.0 / ms
-        step_bytes = nums["weight_bytes"] + args.batch * (ctx_mean * nums["kv_bytes_per_token"] + nums["conv_state_bytes"])
-        achieved = step_bytes / (ms * 1e-3) / 1e9
+        res = measure.decode_run(model, [PROMPT] * args.batch, steps, warmup, room_each=CONTEXT)
+        main_point = decode_point(nums, res, args.batch, pk)
 
-        pre_ms = time_prefill(model, reps=5, warmup=3)
+        pre_ms = measure.prefill_run(model, PREFILL_TOKENS, reps=5, warmup=3)
         pre_flops = (PREFILL_TOKENS * nums["gemm_flops_per_token"] + nums["head_flops_per_row"]
                      + nums["attn_flops"](PREFILL_TOKENS))
+        pre_tflops = pre_flops / (pre_ms * 1e-3) / 1e12
         prefill = {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
-                   "frac": pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+                   "tflops": pre_tflops, "frac": pre_tflops / pk["bf16_tflops"]}
 
         points, e2e = {}, None
         if not args.no_points:
             for b in (1, 64):
-                pms, _, _ = time_decode(model, b, max(8, args.steps // 2), warmup)
-                points[f"decode_b{b}"] = b * 1000.0 / pms
-            e, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup)
-            e2e = {"value": e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+                # enough steps that the first one's enqueue (the GPU idles meanwhile) does not weigh
+                r = measure.decode_run(model, [PROMPT] * b, max(32, steps), warmup, room_each=CONTEXT)
+                pt = decode_point(nums, r, b, pk)
+                points[f"decode_b{b}"] = pt["value"]
+                points[f"decode_b{b}_ms"] = pt["ms_per_step"]
+                points[f"decode_b{b}_frac"] = pt["frac"]
+            e = measure.generate_run(model, [PROMPT] * args.batch, steps + 1, warmup_tokens=warmup + 1)
+            e2e = {"value": e["decode_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
+                   "d2h_bytes_per_step": e["d2h_bytes_per_step"]}
     clocks = clk.summary()
 
-    c = model.config
     line = {
-        "metric": "decode tokens/s, LFM2.5-1.2B shape, bf16, random weights", "value": value, "unit": "tokens/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)",
-        "impl": "ours",
-        "config": {
-            "model": "LFM2.5-1.2B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
-            "attention_layers": len(c.attn_layer_ids), "hidden": c.hidden_size, "heads": c.num_attention_heads,
-            "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim, "ff": c.ff_dim, "vocab": c.vocab_size,
-            "conv_width": c.conv_L_cache, "tied": c.tie_embedding, "global_batch": args.batch,
-            "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
-            "l2": "inputs larger than L2 (a step reads %.2f GB of weights)" % (nums["weight_bytes"] / 1e9),
-            "peaks": pk_src,
-        },
+        "metric": "decode tokens/s, LFM2.5-1.2B shape, bf16, random weights", "value": main_point["value"],
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": res["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (uniform random token ids, random weights)", "impl": "ours",
+        "config": flat_config(model, "LFM2.5-1.2B shape", args.layers, FULL_LAYERS, args.batch, PROMPT, CONTEXT, pk_src,
+                              nums["weight_bytes"]),
         "clocks": clocks,
-        "gpu_launches": launches,
+        "gpu_launches": res["launches"],
         "prefill": prefill,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"]},
+        "roofline": {"bound": "hbm", "bytes_per_step": main_point["bytes_per_step"], "achieved": main_point["gb_per_s"],
+                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": main_point["frac"]},
         "points": points,
     }
     if e2e is not None:

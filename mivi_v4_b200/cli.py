@@ -15,7 +15,7 @@ writes a model folder from a configuration and a seed.
     python -m mivi_v4_b200 info -m DIR
     python -m mivi_v4_b200 random --config cfg.json --seed 0 --out DIR
     python -m mivi_v4_b200 doctor
-    python -m mivi_v4_b200 bench [-m DIR] [--bench-prompt-tokens 2048]
+    python -m mivi_v4_b200 bench -m DIR | --config cfg.json [--bench-prompt-tokens 2048] [--batch 8] [--profile]
     python -m mivi_v4_b200 replay --model DIR --dtype bfloat16 --out DIR --max-tokens N < steps.jsonl
 """
 from __future__ import annotations
@@ -78,8 +78,13 @@ def build_parser() -> argparse.ArgumentParser:
     rp.add_argument("--max-tokens", type=int, required=True)
 
     b = sub.add_parser("bench", help="prefill and decode throughput of a model folder")
-    b.add_argument("-m", "--model", default=None, help="model folder (default: the LFM2.5-1.2B shape with random weights)")
-    b.add_argument("--bench-prompt-tokens", type=int, default=2048)
+    b.add_argument("-m", "--model", default=None, help="model folder")
+    b.add_argument("--config", default=None, help="config.json: measure a model of these sizes with random weights")
+    b.add_argument("--bench-prompt-tokens", type=int, default=2048, help="tokens of the timed prefill")
+    b.add_argument("--prompt-tokens", type=int, default=512, help="cached tokens of each decoding sequence")
+    b.add_argument("--batch", type=int, default=8, help="sequences that decode together")
+    b.add_argument("--steps", type=int, default=64, help="timed decode steps")
+    b.add_argument("--profile", action="store_true", help="also print where a step's time goes, by stage and kernel")
     b.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     return ap
 
@@ -171,38 +176,36 @@ def cmd_doctor(a) -> int:
 
 
 def cmd_bench(a) -> int:
-    import statistics
-    import torch
-    from . import Engine, SamplingParams, load_model
-    if a.model is None:
-        import os
-        import runpy
-        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-        sys.argv = [os.path.join(root, "bench.py")]
-        runpy.run_path(sys.argv[0], run_name="__main__")
-        return 0
-    model = load_model(a.model, a.dtype, "cuda:0")
-    T = a.bench_prompt_tokens
-    eng = Engine(model, max_tokens=2 * (T + 64), max_batch=2, max_step_tokens=max(T, 64))
-    g = torch.Generator().manual_seed(0)
-    prompt = torch.randint(0, model.vocab_size, (T,), generator=g).tolist()
-    times = []
-    for i in range(4):
-        s = eng.open()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        eng.step([(s, prompt)], "last", copy=False)
-        torch.cuda.synchronize()
-        times.append(time.perf_counter() - t0)
-        eng.close(s)
-    pre = statistics.median(times[1:])
-    first = {}
-    t0 = time.perf_counter()
-    out = eng.generate([prompt], 25, SamplingParams.greedy(), stop_token_ids=[],
-                       on_token=lambda i, t: first.setdefault("t", time.perf_counter()))
-    dt = time.perf_counter() - first["t"]
-    print(json.dumps({"prompt_tokens": T, "prefill_tok_s": T / pre, "ttft_ms": (first["t"] - t0) * 1e3,
-                      "decode_tok_s": (len(out[0]) - 1) / dt, "generated": len(out[0])}))
+    """Prefill and decode throughput of a model folder (or of random weights for a config.json), and with
+    ``--profile`` where the time of a decode step and of the prefill goes, stage by stage, as the
+    reference's bench prints its forward profile (crates/mivi-cli/src/runners/bench.rs:178-238)."""
+    from . import load_model, measure, random_model
+    if a.model is not None:
+        model = load_model(a.model, a.dtype, "cuda:0")
+    elif a.config is not None:
+        with open(a.config) as f:
+            model = random_model(json.load(f), seed=0, dtype=a.dtype, device="cuda:0", on_device=True)
+    else:
+        print("bench: give a model folder (-m) or a config.json for random weights (--config)", file=sys.stderr)
+        return 2
+    T, B = a.bench_prompt_tokens, a.batch
+    nums = measure.model_numbers(model)
+    pre_ms = measure.prefill_run(model, T, reps=3, warmup=2)
+    dec = measure.decode_run(model, [a.prompt_tokens] * B, a.steps, warmup=4)
+    gen = measure.generate_run(model, [a.prompt_tokens] * B, a.steps + 1)
+    step_bytes = nums["weight_bytes"] + B * (dec["cached_tokens_mean"] * nums["kv_bytes_per_token"]
+                                             + nums["state_bytes_per_seq"])
+    pre_flops = T * nums["gemm_flops_per_token"] + nums["head_flops_per_row"] + nums["attn_flops"](T)
+    print(json.dumps({
+        "prompt_tokens": T, "prefill_tok_s": T / (pre_ms * 1e-3), "prefill_ms": pre_ms,
+        "prefill_tflops": pre_flops / (pre_ms * 1e-3) / 1e12, "batch": B, "decode_tok_s": B * 1e3 / dec["ms_per_step"],
+        "decode_ms_per_step": dec["ms_per_step"], "decode_bytes_per_step": step_bytes,
+        "decode_gb_per_s": step_bytes / (dec["ms_per_step"] * 1e-3) / 1e9,
+        "generate_tok_s": gen["decode_tokens_per_s"], "kernels_per_step": dec["launches"] / a.steps}))
+    if a.profile:
+        measure.print_stage_report(measure.stage_report(model, [a.prompt_tokens] * B),
+                                   f"decode step, {B} sequence(s) of {a.prompt_tokens} cached tokens")
+        measure.print_stage_report(measure.stage_report(model, [T], prefill=True), f"prefill of {T} tokens")
     return 0
 
 

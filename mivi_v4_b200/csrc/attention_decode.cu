@@ -309,15 +309,26 @@ MV_API int mv_attention_decode_static(const void* q, const void* pool, long long
                                       char* errbuf, int errbuf_len) {
     if (errbuf && errbuf_len > 0) errbuf[0] = 0;
     if (N <= 0) return 0;
-    if (nkv <= 0 || nh % nkv) return fail(errbuf, errbuf_len, 1, "%lld heads are not a multiple of %lld kv heads", nh, nkv);
+    // everything the kernel assumes is checked before the GPU is touched
+    if (nkv <= 0 || nh <= 0 || nh % nkv)
+        return fail(errbuf, errbuf_len, 1, "%lld heads are not a multiple of %lld kv heads", nh, nkv);
     if (splits < 1) return fail(errbuf, errbuf_len, 1, "splits must be at least 1, got %lld", splits);
+    if (hd <= 0 || hd % 8 || hd > 256)
+        return fail(errbuf, errbuf_len, 1, "head size %lld must be a multiple of 8 between 8 and 256", hd);
+    if (page_size <= 0 || (page_size & (page_size - 1)))
+        return fail(errbuf, errbuf_len, 1, "page size %lld is not a power of two", page_size);
+    if (dtype != MV_DT_F32 && dtype != MV_DT_BF16)
+        return fail(errbuf, errbuf_len, 1, "dtype %lld is neither 0 (float32) nor 1 (bfloat16)", dtype);
+    if (!q || !pool || !page_table || !positions || !seq_of || !o)
+        return fail(errbuf, errbuf_len, 1, "an input or output pointer is null");
     const int G = nh / nkv;
     const int gt = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
     const int head_tiles = (G + gt - 1) / gt;
     const size_t tickets = (size_t)N * nkv * head_tiles;
     const size_t ml_floats = (size_t)N * nh * splits * 2;
     const size_t o_floats = (size_t)N * nh * splits * hd;
-    if (tickets > STATIC_TICKETS)
+    // the counters are used only when the keys are split
+    if (splits > 1 && tickets > STATIC_TICKETS)
         return fail(errbuf, errbuf_len, 2,
                     "the built-in scratch holds %lld (token, kv head) counters, this call needs %lld; "
                     "use mv_attention_decode with scratch of your own", (long long)STATIC_TICKETS, (long long)tickets);
@@ -347,8 +358,10 @@ MV_API int mv_attention_decode_static(const void* q, const void* pool, long long
     float* d_ml = reinterpret_cast<float*>(base + STATIC_TICKETS * sizeof(int));
     float* d_o = d_ml + ml_floats;
     // The counters must start at zero; the array still holds whatever the last call left.
-    e = cudaMemsetAsync(d_tickets, 0, tickets * sizeof(int), stream);
-    if (e != cudaSuccess) return fail(errbuf, errbuf_len, 3, "cudaMemsetAsync failed with error %lld", (long long)e);
+    if (splits > 1) {
+        e = cudaMemsetAsync(d_tickets, 0, tickets * sizeof(int), stream);
+        if (e != cudaSuccess) return fail(errbuf, errbuf_len, 3, "cudaMemsetAsync failed with error %lld", (long long)e);
+    }
     const int rc = mv_attention_decode(q, pool, page_stride, page_table, table_stride, page_size, positions, seq_of,
                                        o, dtype, d_o, d_ml, d_tickets, N, nh, nkv, hd, scale, window, splits, gt,
                                        head_tiles, stream);

@@ -17,8 +17,9 @@
 //   MV_STATIC_ATTN_MAX_TICKETS ints + MV_STATIC_ATTN_MAX_FLOATS floats  (about 4.1 MiB)
 // on EVERY GPU that loads the library, from load until the process exits.
 //
-// Limits.  A call needs  N * nkv * ceil((nh/nkv) / gt)  counters and, when
-// splits > 1,  N * nh * splits * (hd + 2)  floats (gt = 1, 2, 4 or 8: the
+// Limits.  With splits > 1 a call needs  N * nkv * ceil((nh/nkv) / gt)  counters
+// and  N * nh * splits * (hd + 2)  floats; with splits == 1 it needs no scratch
+// at all and any N is taken (gt = 1, 2, 4 or 8: the
 // smallest of these that is >= nh/nkv, at most 8).  A call that needs more than
 // the array holds is refused: the function returns 2 and writes the two numbers
 // into errbuf.  It never falls back to allocating.
@@ -26,7 +27,9 @@
 // Rules of use.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress) and remembers it.  Make that first call with the
-//     device current and before you begin any stream capture on that device.
+//     device current, before you begin any stream capture on that device, and
+//     from one thread: the remembered address is written without a lock (two
+//     threads that race there both write the same value).
 //   * Every call uses the same array.  The function clears the counters on the
 //     given stream before the kernel runs, so leftovers of an earlier call do no
 //     harm; but two calls that overlap on the GPU (different streams, or the

@@ -52,7 +52,7 @@ def _width_for(blocks: int) -> int:
 class Engine:
     def __init__(self, model: Model, *, max_tokens: int, max_batch: Optional[int] = None,
                  page_size: int = 64, max_step_tokens: int = 8192, cuda_graphs: bool = True,
-                 max_graphs: int = 64):
+                 max_graphs: int = 64, profile: bool = False):
         if model.dtype is None:
             raise ValueError("the model has no weights yet; use load_model()")
         if model.device.type != "cuda":
@@ -78,7 +78,10 @@ class Engine:
         # one graph memory pool, so a recording costs its launch records only; the least recently used
         # go when there are more than ``max_graphs``.  When the workspace has to move a buffer (a
         # larger batch than any before), the recordings made before name stale addresses and are dropped.
-        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
+        # ``profile``: every launch of every step is timed by stage and kernel (``profile_report``); steps
+        # then run launch by launch, never from a recording
+        self.profile = K.KernelProfile() if profile else None
+        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe and not profile
         self.max_graphs = max(1, int(max_graphs))
         self._graphs: "OrderedDict[tuple, _Recorded]" = OrderedDict()
         self._gws = Workspace(self.device)
@@ -110,6 +113,14 @@ class Engine:
         (a bounded wait that ran out).  Costs nothing; call it where the host has just read a step's
         results.  ``generate`` does so with every step's tokens."""
         K.raise_seen_device_errors(self.device)
+
+    def profile_report(self, reset: bool = True) -> dict:
+        """Where the time of the steps since the last report went (an engine made with ``profile=True``):
+        per stage of the model and per kernel its launches, device time, share, and where the wrapper
+        knows them the bytes it had to move per second and its floating-point operations per second."""
+        if self.profile is None:
+            raise RuntimeError("this engine was not made with profile=True")
+        return self.profile.report(reset)
 
     # ---- the step function -----------------------------------------------------
     def step(self, items: Sequence[Tuple[int, Sequence[int]]], want: Want = "last",
@@ -241,7 +252,10 @@ class Engine:
         lists = [t for _, t in items]
         ctx = StepContext(slots=slots, starts=starts, token_lists=lists, out_rows=out_rows,
                           page_rows=page_rows, dtype=self.dtype, ws=self.ws)
-        logits = self.model.forward(ctx, self.cache)
+        with K.profiling(self.profile):
+            logits = self.model.forward(ctx, self.cache)
+        if self.profile is not None:
+            self.profile.steps += 1
         K.note_device_errors(self.device)
         for s, toks in zip(slots, lists):
             self.cache.advance(s, len(toks))
@@ -429,8 +443,9 @@ class _EngineBackend:
                 raise RuntimeError("the generation loop fed other tokens than the ones sampled for its sequences")
             cur = 1 - early["set"] if early is not None else 0
             logits = eng.step([(r.handle, t) for r, t in zip(requests, token_lists)], "last", copy=False)
-            out_dev = sampler.launch(logits, [r.index for r in requests], [len(r.output) for r in requests],
-                                     [r.output for r in requests], slot=cur, states=handles)
+            with K.profiling(eng.profile), K.profile_stage("sampling"):
+                out_dev = sampler.launch(logits, [r.index for r in requests], [len(r.output) for r in requests],
+                                         [r.output for r in requests], slot=cur, states=handles)
             host, event = sampler.read_async(out_dev, slot=cur)
             rows = list(range(len(requests)))
         # the step after this one, for the requests that will still have tokens to generate

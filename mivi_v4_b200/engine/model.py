@@ -11,6 +11,7 @@ import torch
 from .. import architectures  # noqa: F401  (registers the architectures that ship with the package)
 from ..cache import CachePlan, plan_cache
 from ..config import architecture_for
+from ..ops import kernels as K
 from ..ops.linear import end_norms_carried
 from ..parts import ModelSpec, ParamSpec, build
 
@@ -106,11 +107,12 @@ class Model:
         first = self.blocks[self.schedule[0].block] if self.schedule else None
         link = first.entry_link(step) if (hasattr(first, "entry_link") and getattr(self.embedding, "emits_norm", False)
                                           and end_norms_carried(step.n_tokens)) else None
-        if link is not None:
-            x = self.embedding.forward(step, emit=link)
-            step.leave_link(link)
-        else:
-            x = self.embedding.forward(step)
+        with K.profile_stage("embedding"):
+            if link is not None:
+                x = self.embedding.forward(step, emit=link)
+                step.leave_link(link)
+            else:
+                x = self.embedding.forward(step)
         for pos, entry in enumerate(self.schedule):
             block = self.blocks[entry.block]
             view = cache.view(pos, step.page_tables)
@@ -123,12 +125,13 @@ class Model:
                 block.forward(x, step, view)
         if step.n_out == 0:
             return None
-        link = step.take_link(self.final_norm)
-        if link is not None:
-            return self.head.forward(link.xg, step, self.embedding, scale=link)
-        f = step.ws.get("final", (step.n_out, self.hidden_size), step.dtype)
-        self.final_norm.forward(x, f, rows=step.out_rows)
-        return self.head.forward(f, step, self.embedding)
+        with K.profile_stage("logits"):
+            link = step.take_link(self.final_norm)
+            if link is not None:
+                return self.head.forward(link.xg, step, self.embedding, scale=link)
+            f = step.ws.get("final", (step.n_out, self.hidden_size), step.dtype)
+            self.final_norm.forward(x, f, rows=step.out_rows)
+            return self.head.forward(f, step, self.embedding)
 
 
 def describe_config(config_dict: dict):

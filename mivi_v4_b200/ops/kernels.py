@@ -61,6 +61,123 @@ _SIGNATURES = {
 _fns = {}
 
 
+class KernelProfile:
+    """Device time of every launch made while it is active, by stage of the model and by entry point,
+    with the bytes and floating-point operations that the launch's wrapper accounts for it.
+
+    The reference times the stages of its forward pass behind a switch (embedding, attention and its
+    stages, the convolution layers and their stages, logits: crates/mivi-model/src/model.rs:57-74,
+    273-293) and prints them from its ``bench`` command.  Here every launch is bracketed by two CUDA
+    events on the launching stream; that keeps consecutive kernels from overlapping, so the sum is a
+    little more than what the same step takes when it is replayed from a recording."""
+
+    def __init__(self):
+        self.records = []            # [stage, entry point, start event, end event, bytes, flops]
+        self.stage = "-"
+        self.steps = 0
+
+    def wrap(self, name: str, f):
+        def timed(*args):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            code = f(*args)
+            e1.record()
+            self.records.append([self.stage, name, e0, e1, 0, 0])
+            return code
+        return timed
+
+    def account(self, nbytes: int, flops: int) -> None:
+        if self.records:
+            self.records[-1][4] += int(nbytes)
+            self.records[-1][5] += int(flops)
+
+    def report(self, reset: bool = True) -> dict:
+        """{"rows": [{stage, kernel, calls, us, share, gb_per_s, tflops}], "stages": {stage: us}, "total_us",
+        "steps"}: rows sorted by time.  Waits for the device."""
+        torch.cuda.synchronize()
+        agg = {}
+        for stage, name, e0, e1, nbytes, flops in self.records:
+            row = agg.setdefault((stage, name), [0, 0.0, 0, 0])
+            row[0] += 1
+            row[1] += e0.elapsed_time(e1) * 1e3
+            row[2] += nbytes
+            row[3] += flops
+        total = sum(r[1] for r in agg.values()) or 1.0
+        rows = [dict(stage=k[0], kernel=k[1], calls=r[0], us=r[1], share=r[1] / total,
+                     gb_per_s=(r[2] / r[1] / 1e3) if r[2] else None, tflops=(r[3] / r[1] / 1e6) if r[3] else None)
+                for k, r in sorted(agg.items(), key=lambda kv: -kv[1][1])]
+        stages = {}
+        for row in rows:
+            stages[row["stage"]] = stages.get(row["stage"], 0.0) + row["us"]
+        out = dict(rows=rows, stages=stages, total_us=total, steps=self.steps)
+        if reset:
+            self.records, self.steps = [], 0
+        return out
+
+
+_profile: Optional[KernelProfile] = None
+
+
+class _NoStage:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_STAGE = _NoStage()
+
+
+class _Stage:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        self.prev, _profile.stage = _profile.stage, self.name
+
+    def __exit__(self, *exc):
+        if _profile is not None:
+            _profile.stage = self.prev
+        return False
+
+
+def profile_stage(name: str):
+    """``with profile_stage("mixer gqa"):`` names the stage of the launches inside, when a profile is active."""
+    return _Stage(name) if _profile is not None else _NO_STAGE
+
+
+class profiling:
+    """``with profiling(p):`` every launch inside is timed into ``p`` (a KernelProfile, or None: nothing)."""
+
+    def __init__(self, p: Optional[KernelProfile]):
+        self.p = p
+
+    def __enter__(self):
+        global _profile
+        self.prev, _profile = _profile, self.p
+        return self.p
+
+    def __exit__(self, *exc):
+        global _profile
+        _profile = self.prev
+        return False
+
+
+def profiling_on() -> bool:
+    return _profile is not None
+
+
+def account(nbytes: int = 0, flops: int = 0) -> None:
+    """Bytes that the last launch has to move and operations it has to do, for the active profile."""
+    if _profile is not None:
+        _profile.account(nbytes, flops)
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
 def _fn(lib: str, name: str):
     key = (lib, name)
     f = _fns.get(key)
@@ -69,6 +186,8 @@ def _fn(lib: str, name: str):
         f.argtypes = _SIGNATURES[lib][name]
         f.restype = ctypes.c_int
         _fns[key] = f
+    if _profile is not None and name.startswith("mv_") and not name.endswith(("_partials", "_tile_rows", "_to_host")):
+        return _profile.wrap(name, f)
     return f
 
 
@@ -144,10 +263,12 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor,
             _need(emit.xg, "normed rows", torch.bfloat16, (N, H)), emit.partials.data_ptr(), emit.partials.shape[1],
             _stream()), "mv_embed_link")
         emit.n_partials = n_part
+        account(N * H * (table.element_size() + 4 + 2))
         return out
     _check(_fn("core", "mv_embed")(
         _need(table, "embedding table"), _dt(table), _need(tokens, "tokens", torch.int32),
         _need(out, "embedding out", torch.float32, (N, H)), N, H, _stream()), "mv_embed")
+    account(N * H * (table.element_size() + 4))
     return out
 
 
@@ -160,6 +281,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
         _need(x, "rmsnorm x", torch.float32), _need(w, "rmsnorm weight", torch.float32, (H,)),
         _need(out, "rmsnorm out", None, (n, H)), _dt(out),
         _need(rows, "rmsnorm rows", torch.int32, optional=True), n, H, float(eps), _stream()), "mv_rmsnorm")
+    account(n * H * (4 + out.element_size()))
     return out
 
 
@@ -176,10 +298,17 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.Tensor:
     _check(_fn("core", "mv_swiglu")(
         _need(gu, "swiglu in", torch.float32), _need(out, "swiglu out", None, (N, F)), _dt(out), N, F, int(group),
         _stream()), "mv_swiglu")
+    account(_nbytes(gu, out))
     return out
 
 
 STORE, ACCUMULATE = "store", "accumulate"
+
+
+def _account_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:
+    if _profile is not None:
+        account(_nbytes(x, w) + (2 if accumulate else 1) * out.numel() * out.element_size(),
+                2 * x.shape[0] * w.shape[0] * w.shape[1])
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
@@ -202,6 +331,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Opti
     _check(_fn("core", "mv_gemm_simt")(
         _need(x, "gemm x"), _need(w, "gemm w"), _dt(x), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, N, _stream()), "mv_gemm_simt")
+    _account_gemm(x, w, out, accumulate)
     return out
 
 
@@ -262,6 +392,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
     _check(_fn("bf16", "mv_gemm_small_m")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, ldo, *link, *(ahead or (None, 0)), _stream()), "mv_gemm_small_m")
+    _account_gemm(x, w, out, accumulate)
     return out
 
 
@@ -299,6 +430,7 @@ def gemm_small_m_shortconv(x: torch.Tensor, w_in: torch.Tensor, b_in: Optional[t
         _need(taps, "shortconv taps", torch.float32), _need(b_conv, "shortconv bias", torch.float32, (H,), True),
         state.data_ptr(), _need(slots, "slots", torch.int32), _need(out, "shortconv out", torch.bfloat16, (M, H)),
         M, H, K, k, sp, n_sp, s_stride, dim, eps, *(ahead or (None, 0)), _stream()), "mv_gemm_small_m_shortconv")
+    _account_gemm(x, w_in, out, False)
     return out
 
 
@@ -336,6 +468,7 @@ def gemm_small_m_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq: Optional[torch.
         page_table.data_ptr(), page_table.shape[1], page_size, _need(pool, "cache pool"), pool.stride(0),
         _need(q_out, "q out", torch.bfloat16, (M, nh * hd)), M, nh, nkv, K, sp, n_sp, s_stride, dim, eps_norm,
         *(ahead or (None, 0)), _stream()), "mv_gemm_small_m_heads")
+    _account_gemm(x, w_qkv, q_out, False)
     return q_out
 
 
@@ -457,6 +590,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
     _check(_fn("bf16", "mv_gemm_tc")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc")
+    _account_gemm(x, w, out, accumulate)
     return out
 
 
@@ -491,6 +625,7 @@ def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
     _check(_fn("bf16", "mv_gemm_tc_swap")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, ldo, *link, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_swap")
+    _account_gemm(x, w, out, accumulate)
     return out
 
 
@@ -515,6 +650,7 @@ def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], st
             _need(bias, "shortconv bias", torch.float32, (H,), True), state.data_ptr(),
             _need(slots, "slots", torch.int32), _need(out, "shortconv out", None, (N, H)), _dt(out), N, H, k,
             _stream()), "mv_shortconv_decode")
+        account(_nbytes(p, out) + 2 * N * (k - 1) * H * 4)
         return out
     _check(_fn("core", "mv_shortconv")(
         _need(p, "shortconv p", torch.float32), _need(w, "shortconv taps", torch.float32),
@@ -523,6 +659,7 @@ def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], st
         _need(cu, "cu", torch.int32), _need(slots, "slots", torch.int32),
         _need(starts, "starts", torch.int32), _need(lens, "lens", torch.int32),
         _need(out, "shortconv out", None, (N, H)), _dt(out), N, n_seqs, H, k, _stream()), "mv_shortconv")
+    account(_nbytes(p, out) + 2 * n_seqs * (k - 1) * H * 4)
     return out
 
 
@@ -557,6 +694,7 @@ def qk_prepare(qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch
         page_table.data_ptr(), page_table.shape[1], page_size, _need(pool, "cache pool"),
         pool.stride(0), int(append), _need(q_out, "q out", None, (N, nh * hd)), _dt(q_out), N, nh, nkv, hd,
         _stream()), "mv_qk_prepare")
+    account(_nbytes(qkv, q_out) + N * 2 * nkv * hd * pool.element_size())
     return q_out
 
 
@@ -794,4 +932,5 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
         _need(ring, "recent ring", torch.int32, (None, RECENT_RING), True),
         _need(ring_rows, "ring rows", torch.int32, (B,), ring is None),
         _need(out, "sample out", torch.int32, (B,)), _stream()), "mv_sample")
+    account(B * V * 4)
     return out

@@ -1,6 +1,7 @@
 """Arrangements of a layer's parts."""
 from __future__ import annotations
 
+from ..ops.kernels import profile_stage
 from .base import Part
 from .registry import register
 
@@ -45,17 +46,21 @@ class PreNormBlock(Part):
             u, kw["scale"] = entry.xg, entry
         else:
             u = step.ws.get("normed", (N, H), step.dtype)
-            self.mixer_norm.forward(resid, u)
+            with profile_stage("norm"):
+                self.mixer_norm.forward(resid, u)
         if mid is not None:
             kw["emit"] = mid
-        self.mixer.forward(u, resid, step, view, **kw)
+        with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
+            self.mixer.forward(u, resid, step, view, **kw)
         kw = {}
         if mid is not None:
             g, kw["scale"] = mid.xg, mid
         else:
             g = step.ws.get("normed", (N, H), step.dtype)
-            self.ffn_norm.forward(resid, g)
+            with profile_stage("norm"):
+                self.ffn_norm.forward(resid, g)
         if leave is not None:
             kw["emit"] = leave
-        self.ffn.forward(g, resid, step, **kw)
+        with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
+            self.ffn.forward(g, resid, step, **kw)
         step.leave_link(leave)

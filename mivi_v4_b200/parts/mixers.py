@@ -167,4 +167,11 @@ class GroupedQueryAttention(Part):
         else:
             K.attention_generic(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                 self.scale, self.window)
+        if K.profiling_on():
+            # keys that the step's queries read (each query its own context), for the attention launch
+            pairs = sum(n * s + n * (n + 1) // 2 for s, n in zip(step.host_starts, step.host_lens))
+            rows = sum(s + n for s, n in zip(step.host_starts, step.host_lens)) if N > K.DECODE_ATTENTION_MAX_TOKENS \
+                else pairs
+            K.account(2 * nkv * hd * view.pool.element_size() * rows + 2 * N * nh * hd * q.element_size(),
+                      4 * nh * hd * pairs)
         linear(o, self.w_o, resid, accumulate=True, emit=emit)

@@ -175,8 +175,8 @@ def test_decoding_from_500_to_1100_cached_tokens(folder, models, dtype):
     eng.close(sa)
     check(torch.cat(rows_a), folder, a, dtype, "decoding 500..1100", rows=slice(500, 1100))
     check(torch.cat(rows_b), folder, b, dtype, "the short companion", rows=slice(40, 140))
-    widths = {key[1] for key in eng.graph_keys()}
-    assert len(widths) >= 3, widths                     # 512, 1,024 and 1,536 tokens of page table
+    # two sequences under a page table of 512 and of 1,024 tokens, then one under 1,024 and 2,048
+    assert eng.graphs_recorded >= 4 and any(key[1][0][1] == 32 for key in eng.graph_keys()), eng.graph_keys()
     assert eng.graph_replays >= 590
     if dtype == torch.bfloat16:
         assert K.attention_decode_tc_plan(1, WIDE["num_key_value_heads"], 1152) > 1

@@ -96,7 +96,7 @@ def test_decoding_across_the_page_table_growth(folders, dtype):
             rows_b.append(lg[1:2])
     check(torch.cat(rows_a), folders[name], a, dtype, "decoding 500..1100", rows=slice(500, 1100))
     check(torch.cat(rows_b), folders[name], b, dtype, "its companion 3..600", rows=slice(3, 600))
-    assert len({key[1] for key in eng.graph_keys()}) >= 3
+    assert eng.graphs_recorded >= 3 and any(key[1][0][1] == 32 for key in eng.graph_keys()), eng.graph_keys()
     assert eng.graph_replays >= 590
 
 
@@ -151,3 +151,38 @@ def test_temperature_generation_bfloat16_draws_from_the_plain_distribution(folde
             kth = torch.topk(row, 8).values[-1]
             assert row[tok] >= kth - 32 * noise, (i, tok)
     assert len({t for out in got for t in out}) > 8          # not one token over and over
+
+
+def test_many_decode_shapes_share_one_workspace(folders):
+    """Sequences that end one by one and grow past page-table widths make many decode shapes.  Their
+    recordings work in one workspace and one graph memory pool: the device memory that the engine holds
+    does not grow with their number, the least recently used are dropped beyond ``max_graphs``, and the
+    logits stay those of the plain implementation throughout."""
+    name = "FL"
+    Vn = config_of(name)["vocab_size"]
+    n = 12
+    full = prompts(Vn, [530 + 9 * i for i in range(n)], seed=18)
+    eng = engine(folders[name], torch.bfloat16, max_tokens=n * 640, max_batch=n, max_graphs=6)
+    slots = [eng.open() for _ in full]
+    start = 500
+    eng.step([(s, t[:start]) for s, t in zip(slots, full)], None)
+    got = [[] for _ in full]
+    live = list(range(n))
+    pos = start
+    mem = []
+    while live:
+        lg = eng.step([(slots[i], [full[i][pos]]) for i in live], "last")
+        for j, i in enumerate(live):
+            got[i].append(lg[j:j + 1].cpu())
+        pos += 1
+        for i in [i for i in live if pos == len(full[i])]:
+            eng.close(slots[i])
+        live = [i for i in live if pos < len(full[i])]
+        mem.append(torch.cuda.memory_allocated())
+        assert len(eng.graph_keys()) <= 6
+    for i in range(n):
+        check(torch.cat(got[i]), folders[name], full[i], torch.bfloat16, f"request {i}", rows=slice(start, len(full[i])))
+    assert eng.graphs_recorded >= n + 1                      # every batch size, and the wider page table
+    # after the first step (which sized the workspace) nothing more is held, whatever the number of shapes
+    assert max(mem) - mem[0] <= (1 << 20), (mem[0], max(mem))
+    eng.cache.check()

@@ -78,3 +78,45 @@ def test_static_scratch_entry_refuses_what_does_not_fit():
     assert rc == 2 and b"built-in scratch" in err.value
     rc = fn(d, d, 0, d, 1, 64, d, d, d, 1, 4, 5, 2, 64, 0.125, 0, 1, None, err, len(err))
     assert rc == 1 and b"multiple" in err.value
+    # bad arguments are named as such (1), before anything is enqueued: a head size, a page size, a pointer
+    rc = fn(d, d, 0, d, 1, 64, d, d, d, 1, 4, 8, 2, 60, 0.125, 0, 2, None, err, len(err))
+    assert rc == 1 and b"head size 60" in err.value
+    rc = fn(d, d, 0, d, 1, 48, d, d, d, 1, 4, 8, 2, 64, 0.125, 0, 2, None, err, len(err))
+    assert rc == 1 and b"page size 48" in err.value
+    rc = fn(d, d, 0, d, 1, 64, d, d, None, 1, 4, 8, 2, 64, 0.125, 0, 2, None, err, len(err))
+    assert rc == 1 and b"null" in err.value
+
+
+def test_static_scratch_entry_leaves_device_memory_alone():
+    """It allocates nothing: the device's free memory is the same before and after calls, and an
+    unsplit call of many tokens needs none of the built-in scratch."""
+    from mivi_v4_b200.ops import kernels as K
+    from mivi_v4_b200.engine.step import Workspace
+    fn = static_entry()
+    nh, nkv, hd, page = 4, 2, 32, 16
+    scale = 1.0 / math.sqrt(hd)
+    lengths = [37] * 20
+    pool, table, dense = build_cache(lengths, nkv, hd, page, torch.float32, seed=5)
+    N = 20000                                   # beyond the counters of the built-in array: fine when unsplit
+    g = torch.Generator().manual_seed(5)
+    qd = torch.randn(N, nh * hd, generator=g).to(DEV)
+    seq_of = ints([i % 20 for i in range(N)])
+    positions = ints([36] * N)
+    want = torch.empty_like(qd)
+    K.attention_decode(qd, pool, table, positions, seq_of, want, nh, nkv, hd, scale, 0, Workspace(DEV), splits=1)
+    got = torch.full_like(qd, float("nan"))
+    err = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    free0 = None
+    for call in range(3):
+        if call == 1:                           # the first call may load the library's device code
+            torch.cuda.synchronize()
+            free0, _ = torch.cuda.mem_get_info()
+        rc = fn(qd.data_ptr(), pool.data_ptr(), pool.stride(0), table.data_ptr(), table.shape[1], page,
+                positions.data_ptr(), seq_of.data_ptr(), got.data_ptr(), 0, N, nh, nkv, hd, scale, 0, 1, stream,
+                err, len(err))
+        assert rc == 0, err.value.decode()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert torch.allclose(got, want, rtol=2e-5, atol=2e-5)
