@@ -6,8 +6,8 @@ Layers with the same need form a group with storage of its own:
   * a KV group: pool[layer, page, 2 (K, V), kv head, row, head_dim] in the
     model's dtype, pages of ``page_size`` tokens handed out on demand; a group
     with a window gives pages back as they fall out of it;
-  * a state group: state[layer, slot, ...] in float32, zeroed when the slot is
-    assigned.
+  * a state group: state[layer, slot, ...] in the need's dtype (float32 unless it
+    says otherwise), zeroed when the slot is assigned.
 The reference allocates keys and values only for its attention layers through
 a layer map (crates/mivi-kv/src/cache.rs:109-141) and keeps the convolution
 state per layer in its run state (crates/mivi-core/src/arena.rs:56,82,105);
@@ -43,41 +43,48 @@ class GroupPlan:
 class CachePlan:
     """Which group and which layer of it each position of the schedule uses."""
     groups: List[GroupPlan]
-    binding: List[Optional[Tuple[int, int]]]      # schedule position -> (group, layer in group) or None
+    binding: List[Optional[Tuple[int, int]]]      # schedule position -> (group, layer in group) of its first need, or None
     owner: List[bool]                             # False: the position reads another position's cache
+    bindings: List[List[Tuple[int, int]]]         # schedule position -> (group, layer in group) of each of its needs
+    several: List[bool]                           # the position gave a list of needs and gets a list of views
 
 
-def plan_cache(needs: Sequence[Need], cache_of: Sequence[Optional[int]]) -> CachePlan:
+def plan_cache(needs: Sequence[Union[Need, Sequence[Need]]], cache_of: Sequence[Optional[int]]) -> CachePlan:
+    """Layers with equal needs share a group.  A position's need is one need, None, or a list of needs."""
     groups: List[GroupPlan] = []
     index: Dict[Need, int] = {}
-    binding: List[Optional[Tuple[int, int]]] = []
+    bindings: List[List[Tuple[int, int]]] = []
     owner: List[bool] = []
+    several: List[bool] = []
     for pos, (need, src) in enumerate(zip(needs, cache_of)):
+        is_list = isinstance(need, (list, tuple))
+        wanted = [n for n in need if n is not None] if is_list else ([] if need is None else [need])
+        several.append(is_list)
         if src is not None:
             if not (0 <= src < pos):
                 raise CacheError(f"schedule position {pos} reads the cache of position {src}, "
                                  f"which is not an earlier position")
-            if binding[src] is None or not owner[src]:
+            if not bindings[src] or not owner[src]:
                 raise CacheError(f"schedule position {pos} reads the cache of position {src}, "
                                  f"which keeps none of its own")
-            if groups[binding[src][0]].need != need:
+            kept = [groups[g].need for g, _ in bindings[src]]
+            if kept != wanted:
                 raise CacheError(f"schedule position {pos} needs {need} but position {src} keeps "
-                                 f"{groups[binding[src][0]].need}")
-            binding.append(binding[src])
+                                 f"{kept[0] if len(kept) == 1 else kept}")
+            bindings.append(list(bindings[src]))
             owner.append(False)
             continue
-        if need is None:
-            binding.append(None)
-            owner.append(True)
-            continue
-        if need not in index:
-            index[need] = len(groups)
-            groups.append(GroupPlan(need))
-        g = index[need]
-        binding.append((g, groups[g].n_layers))
-        groups[g].n_layers += 1
+        mine = []
+        for n in wanted:
+            if n not in index:
+                index[n] = len(groups)
+                groups.append(GroupPlan(n))
+            g = index[n]
+            mine.append((g, groups[g].n_layers))
+            groups[g].n_layers += 1
+        bindings.append(mine)
         owner.append(True)
-    return CachePlan(groups, binding, owner)
+    return CachePlan(groups, [b[0] if b else None for b in bindings], owner, bindings, several)
 
 
 @dataclass
@@ -137,7 +144,7 @@ class SequenceCache:
                 self.storage[gi] = torch.zeros(shape, dtype=dtype, device=self.device)
             else:
                 shape = (g.n_layers, max(n_slots, 1)) + tuple(g.need.shape)
-                self.storage[gi] = torch.zeros(shape, dtype=torch.float32, device=self.device)
+                self.storage[gi] = torch.zeros(shape, dtype=g.need.dtype, device=self.device)
 
     # ---- sizes ------------------------------------------------------------
     @property
@@ -291,16 +298,19 @@ class SequenceCache:
 
     # ---- views ------------------------------------------------------------------
     def view(self, position: int, page_tables: Dict[int, torch.Tensor]):
-        """The cache as schedule position ``position`` sees it in this step."""
-        bind = self.plan.binding[position]
-        if bind is None:
-            return None
-        gi, layer = bind
-        need = self.plan.groups[gi].need
+        """The cache as schedule position ``position`` sees it in this step: one view, None, or (for a
+        position that gave a list of needs) a list of views in the order of its needs."""
         writable = self.plan.owner[position]
-        if isinstance(need, KVNeed):
-            return KVView(self.storage[gi][layer], page_tables[gi], self.page_size, writable, need)
-        return StateView(self.storage[gi][layer], writable, need)
+        views = []
+        for gi, layer in self.plan.bindings[position]:
+            need = self.plan.groups[gi].need
+            if isinstance(need, KVNeed):
+                views.append(KVView(self.storage[gi][layer], page_tables[gi], self.page_size, writable, need))
+            else:
+                views.append(StateView(self.storage[gi][layer], writable, need))
+        if self.plan.several[position]:
+            return views
+        return views[0] if views else None
 
     # ---- inspection ---------------------------------------------------------------
     def dump_slot(self, slot: int) -> Dict[int, torch.Tensor]:

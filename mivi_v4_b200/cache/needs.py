@@ -1,8 +1,12 @@
-"""What a mixer asks of the cache.  A mixer that keeps nothing returns None."""
+"""What a mixer asks of the cache.  A mixer that keeps nothing returns None; one that keeps
+several things (keys and values AND a state, two states of different shape or dtype) returns a
+list of needs and gets a list of views, one for each, in the same order."""
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Tuple
+
+import torch
 
 
 @dataclass(frozen=True)
@@ -17,6 +21,7 @@ class KVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """State of a fixed size per sequence, float32, zero when a sequence starts
-    (the short convolution's last k-1 inputs; any recurrent state)."""
+    """State of a fixed size per sequence, zero when a sequence starts (the short
+    convolution's last k-1 inputs; any recurrent state).  ``dtype``: what it is stored in."""
     shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32

@@ -231,3 +231,23 @@ MV_API int mv_copy_to_host(void* dst, const void* src, long long bytes, cudaStre
     if (bytes <= 0) return 0;
     return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost, stream);
 }
+
+// ------------------------------------------------------------------- delay
+// Keeps the stream busy for ``us`` microseconds (at most 50 ms): a profile of a step of
+// many short kernels enqueues it first, so that the step's launches queue up behind it and
+// run back to back instead of each waiting for the host.
+__global__ void delay_kernel(unsigned long long ns) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    do {
+        __nanosleep(2000);
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    } while (t - t0 < ns);
+}
+
+MV_API int mv_delay(long long us, cudaStream_t stream) {
+    if (us <= 0) return 0;
+    if (us > 50000) us = 50000;
+    delay_kernel<<<1, 1, 0, stream>>>((unsigned long long)us * 1000ull);
+    return mv_launch_status();
+}

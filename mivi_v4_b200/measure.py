@@ -29,7 +29,8 @@ def model_numbers(model) -> dict:
     plan = model.cache_plan()
     kv_per_token = sum(g.n_layers * 2 * g.need.n_kv_heads * g.need.head_dim * elt
                        for g in plan.groups if isinstance(g.need, KVNeed))
-    state_per_seq = sum(g.n_layers * 4 * math.prod(g.need.shape) for g in plan.groups if not isinstance(g.need, KVNeed))
+    state_per_seq = sum(g.n_layers * torch.empty(0, dtype=g.need.dtype).element_size() * math.prod(g.need.shape)
+                        for g in plan.groups if not isinstance(g.need, KVNeed))
 
     def matrices(part) -> int:
         n = sum(math.prod(spec.shape) for spec in part.param_specs().values() if spec.role == "matrix")
@@ -136,7 +137,8 @@ def generate_run(model, prompt_lens: Sequence[int], new_tokens: int, warmup_toke
     from .sampling import SamplingParams
     eng = _engine(model, prompt_lens, max(new_tokens, warmup_tokens) + 1)
     prompts = random_prompts(model.vocab_size, prompt_lens, seed)
-    eng.generate([p[:64] for p in prompts], warmup_tokens, SamplingParams.greedy(), stop_token_ids=[])
+    # the same lengths as the timed run: its decode steps then find their shapes recorded
+    eng.generate(prompts, warmup_tokens, SamplingParams.greedy(), stop_token_ids=[])
     first: Dict[str, float] = {}
     h2d0 = [0]
 

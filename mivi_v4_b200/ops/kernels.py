@@ -36,6 +36,7 @@ _SIGNATURES = {
         "mv_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "mv_swiglu": [_P, _P, _I, _I, _I, _I, _P],
         "mv_copy_to_host": [_P, _P, _Q, _P],
+        "mv_delay": [_Q, _P],
         "mv_gemm_simt": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_shortconv_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -164,6 +165,13 @@ class profiling:
         return False
 
 
+def delay(us: int) -> None:
+    """Keep the current stream busy for ``us`` microseconds (at most 50,000)."""
+    code = _fn("core", "mv_delay")(int(us), _stream())
+    if code != 0:
+        raise KernelError(f"mv_delay: launch failed with CUDA error {code}")
+
+
 def profiling_on() -> bool:
     return _profile is not None
 
@@ -186,7 +194,7 @@ def _fn(lib: str, name: str):
         f.argtypes = _SIGNATURES[lib][name]
         f.restype = ctypes.c_int
         _fns[key] = f
-    if _profile is not None and name.startswith("mv_") and not name.endswith(("_partials", "_tile_rows", "_to_host")):
+    if _profile is not None and not name.endswith(("_partials", "_tile_rows", "_to_host", "_delay")):
         return _profile.wrap(name, f)
     return f
 
@@ -735,7 +743,19 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table, positions
     return out
 
 
-N_SMS = 148
+_n_sms = {}
+
+
+def n_sms(device=None) -> int:
+    """Multiprocessors of the device (asked once); 148 where no device can be asked (planning on a CPU)."""
+    if not torch.cuda.is_available():
+        return 148
+    key = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if key not in _n_sms:
+        _n_sms[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _n_sms[key]
+
+
 DECODE_ATTENTION_MAX_TOKENS = 128      # steps with more query tokens split the work over the queries
 
 
@@ -749,7 +769,7 @@ def attention_decode_plan(N: int, nh: int, nkv: int, context_cap: int = 0):
     G = nh // nkv
     gt = 1 if G <= 1 else (2 if G <= 2 else (4 if G <= 4 else 8))
     head_tiles = -(-G // gt)
-    splits = -(-2 * N_SMS // max(1, N * nkv * head_tiles))
+    splits = -(-2 * n_sms() // max(1, N * nkv * head_tiles))
     splits = max(splits, -(-context_cap // (32 * 4 * 8)))
     return gt, head_tiles, max(1, min(32, splits))
 
@@ -790,7 +810,7 @@ def attention_decode_tc_plan(N: int, nkv: int, context_cap: int) -> int:
     blocks of 128 a split.  Like ``attention_decode_plan`` it depends on the page table's
     reach, not on the lengths."""
     blocks = max(1, -(-context_cap // 128))
-    want = (2 * N_SMS) // max(1, N * nkv)
+    want = (2 * n_sms()) // max(1, N * nkv)
     if blocks <= 8:
         return 1          # up to 1,024 cached tokens a split saves less than its merge kernel costs
     return max(1, min(64, want, blocks // 2))

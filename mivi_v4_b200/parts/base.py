@@ -36,6 +36,12 @@ class Part:
         A mixer or feed-forward that answers (False, False), the default, is never passed either."""
         return False, False
 
+    def scratch(self, step, name: str, shape, dtype):
+        """A buffer from the step's workspace under a name of this part's kind: parts of different kinds
+        never share one, so a part may hold its buffers across a call into another part.  (Layers of the
+        same kind do share them: a layer is done with its buffers when the next one starts.)"""
+        return step.ws.get(f"{getattr(self, 'kind', type(self).__name__)}.{name}", shape, dtype)
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         """Local tensor name (appended to ``prefix``) -> how the checkpoint stores it."""
         return {}

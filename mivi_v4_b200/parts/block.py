@@ -45,7 +45,7 @@ class PreNormBlock(Part):
         if entry is not None:
             u, kw["scale"] = entry.xg, entry
         else:
-            u = step.ws.get("normed", (N, H), step.dtype)
+            u = self.scratch(step, "normed", (N, H), step.dtype)
             with profile_stage("norm"):
                 self.mixer_norm.forward(resid, u)
         if mid is not None:
@@ -56,7 +56,7 @@ class PreNormBlock(Part):
         if mid is not None:
             g, kw["scale"] = mid.xg, mid
         else:
-            g = step.ws.get("normed", (N, H), step.dtype)
+            g = self.scratch(step, "normed", (N, H), step.dtype)
             with profile_stage("norm"):
                 self.ffn_norm.forward(resid, g)
         if leave is not None:

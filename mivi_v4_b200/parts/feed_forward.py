@@ -47,11 +47,11 @@ class SwiGLU(Part):
 
     def forward(self, g, resid, step, scale=None, emit=None) -> None:
         N = g.shape[0]
-        h = step.ws.get("ffh", (N, self.ff), step.dtype)
+        h = self.scratch(step, "ffh", (N, self.ff), step.dtype)
         if self.group and tensor_core_ok(g, self.w13):
             linear_swiglu(g, self.w13, h, scale=scale)
         else:
-            gu = step.ws.get("proj", (N, 2 * self.ff), torch.float32)
+            gu = self.scratch(step, "proj", (N, 2 * self.ff), torch.float32)
             linear(g, self.w13, gu, scale=scale)
             K.swiglu(gu, h, self.group)
         linear(h, self.w2, resid, accumulate=True, emit=emit)

@@ -53,14 +53,14 @@ class ShortConv(Part):
 
     def forward(self, u, resid, step, view, scale=None, emit=None) -> None:
         N, H = u.shape
-        z = step.ws.get("mix", (N, H), step.dtype)
+        z = self.scratch(step, "mix", (N, H), step.dtype)
         if step.is_decode and N == step.n_seqs and shortconv_decode_fused_ok(N, u, self.w_in):
             # a few sequences, one token each: the convolution is the projection's epilogue
             linear_shortconv_decode(u, self.w_in, self.b_in, self.taps, self.b_conv, view.state, step.slots, z,
                                     scale=scale)
             linear(z, self.w_out, resid, bias=self.b_out, accumulate=True, emit=emit)
             return
-        p = step.ws.get("proj", (N, 3 * H), torch.float32)
+        p = self.scratch(step, "proj", (N, 3 * H), torch.float32)
         linear(u, self.w_in, p, bias=self.b_in, scale=scale)
         K.shortconv(p, self.taps, self.b_conv, view.state, step.positions, step.seq_of, step.cu,
                     step.slots, step.starts, step.lens, z, step.n_seqs, decode=step.is_decode)
@@ -132,7 +132,7 @@ class GroupedQueryAttention(Part):
         if view.writable == self.shared_kv:
             raise RuntimeError("a shared_kv attention layer must read another layer's cache, and only it may")
         width = (nh + (0 if self.shared_kv else 2 * nkv)) * hd
-        q = step.ws.get("q", (N, nh * hd), step.dtype)
+        q = self.scratch(step, "q", (N, nh * hd), step.dtype)
         rot = self.position.rotary(u.device)
         inv_freq, half_split = rot if rot is not None else (None, False)
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
@@ -141,14 +141,14 @@ class GroupedQueryAttention(Part):
             linear_heads(u, self.w_qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
                          step.seq_of, view.page_table, view.pool, q, nh, nkv, scale=scale)
         else:
-            qkv = step.ws.get("proj", (N, width), torch.float32)
+            qkv = self.scratch(step, "proj", (N, width), torch.float32)
             linear(u, self.w_qkv, qkv, scale=scale)
             if self.shared_kv:
                 K.qk_prepare_q_only(qkv, self.q_norm, eps, inv_freq, half_split, step.positions, q, nh, hd)
             else:
                 K.qk_prepare(qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
                              step.seq_of, view.page_table, view.pool, q, nh, nkv, hd)
-        o = step.ws.get("mix", (N, nh * hd), step.dtype)
+        o = self.scratch(step, "mix", (N, nh * hd), step.dtype)
         if N <= K.DECODE_ATTENTION_MAX_TOKENS and K.attention_decode_tc_supported(step.dtype, hd, view.pool,
                                                                                  self.window, nh, nkv):
             # few query tokens, head size 64: flash decoding with both products on tcgen05

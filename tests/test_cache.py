@@ -5,7 +5,7 @@ import random
 import pytest
 import torch
 
-from mivi_v4_b200.cache import CacheError, IndexPool, KVNeed, SequenceCache, StateNeed, plan_cache
+from mivi_v4_b200.cache import CacheError, IndexPool, KVNeed, KVView, SequenceCache, StateNeed, StateView, plan_cache
 
 
 def make(n_slots=4, n_pages=8, page=4, needs=None, cache_of=None):
@@ -160,3 +160,22 @@ def test_dump_slot_reads_pages_in_order():
     d = c.dump_slot(s)[1]
     assert d.shape == (2, 2, 6, 2, 8)
     assert d[0, 0, :, 0, 0].tolist() == [0, 1, 2, 3, 10, 11]
+
+
+def test_a_position_with_several_needs_gets_several_views():
+    """A layer may keep more than one thing: its needs come as a list, each joins the group of its kind
+    (shape and dtype included), and the layer gets one view for each, in order."""
+    both = [KVNeed(2, 8), StateNeed((3,), torch.bfloat16)]
+    plan = plan_cache([StateNeed((3,)), both, None, both, [StateNeed((3,))]], [None, None, None, 1, None])
+    assert [g.need for g in plan.groups] == [StateNeed((3,)), KVNeed(2, 8), StateNeed((3,), torch.bfloat16)]
+    assert plan.bindings == [[(0, 0)], [(1, 0), (2, 0)], [], [(1, 0), (2, 0)], [(0, 1)]]
+    assert plan.several == [False, True, False, True, True] and plan.owner[3] is False
+    c = SequenceCache(plan, n_slots=2, n_pages=4, page_size=16, dtype=torch.float32, device="cpu")
+    assert c.storage[2].dtype == torch.bfloat16 and c.storage[0].dtype == torch.float32
+    tables = {g: torch.zeros(1, 1, dtype=torch.int32) for g in c.kv_groups}
+    assert isinstance(c.view(0, tables), StateView) and c.view(2, tables) is None
+    kv, st = c.view(1, tables)
+    assert isinstance(kv, KVView) and isinstance(st, StateView) and st.state.dtype == torch.bfloat16
+    assert [type(v) for v in c.view(4, tables)] == [StateView]
+    with pytest.raises(CacheError, match="keeps"):
+        plan_cache([both, [KVNeed(2, 8)]], [None, 0])

@@ -168,6 +168,42 @@ def register_toy_parts():
                 row += n
             linear(s_all.to(step.dtype), self.w, resid, accumulate=True)
 
+    @register("mixer", "toy_sum_and_count", replace=True)
+    class SumAndCount(Part):
+        """A mixer with TWO states of different shape and dtype: the running sum above (float32 [hidden]) and
+        the number of tokens seen so far, kept with its negative in bfloat16 [1, 2].  out = s_t W^T * (1 +
+        count_t / 100).  It asks the cache for a list of needs and gets a list of views."""
+        graph_safe = False
+
+        def __init__(self, hidden: int, decay: float):
+            self.hidden, self.decay = hidden, decay
+
+        def param_specs(self):
+            return {"mix.weight": ParamSpec((self.hidden, self.hidden))}
+
+        def load(self, t):
+            self.w = t["mix.weight"]
+
+        def cache_need(self):
+            return [StateNeed((self.hidden,)), StateNeed((1, 2), torch.bfloat16)]
+
+        def forward(self, u, resid, step, views):
+            sums, counts = views
+            assert counts.state.dtype == torch.bfloat16 and tuple(counts.state.shape[1:]) == (1, 2)
+            s_all = torch.empty(u.shape, dtype=torch.float32, device=u.device)
+            row = 0
+            for slot, n in zip(step.host_slots, step.host_lens):
+                s, c = sums.state[slot], counts.state[slot].float()
+                for i in range(n):
+                    s = self.decay * s + u[row + i].float()
+                    c = c + torch.tensor([[1.0, -1.0]], device=u.device)
+                    s_all[row + i] = s * (1.0 + c[0, 0] / 100.0)
+                sums.state[slot] = s
+                counts.state[slot] = c.to(torch.bfloat16)
+                assert float(c[0, 0]) == -float(c[0, 1])
+                row += n
+            linear(s_all.to(step.dtype), self.w, resid, accumulate=True)
+
     @register("feed_forward", "toy_top1_experts", replace=True)
     class Top1Experts(Part):
         """A feed-forward with routing: every token goes to the one expert whose router logit is
@@ -249,6 +285,8 @@ def register_toy_parts():
                 ffn = PartSpec("toy_top1_experts", dict(hidden=H, ff=c.ff, experts=c.experts), prefix=pre + "moe.")
             if kind == "sum":
                 mixer = PartSpec("toy_running_sum", dict(hidden=H, decay=c.decay), prefix=pre + "sum.")
+            elif kind == "sum2":
+                mixer = PartSpec("toy_sum_and_count", dict(hidden=H, decay=c.decay), prefix=pre + "sum.")
             elif kind == "attn_stretched":
                 mixer = PartSpec("gqa", dict(hidden=H, n_heads=c.heads, n_kv_heads=c.kv_heads, head_dim=hd,
                                              qk_norm_eps=None, window=0, shared_kv=False), prefix=pre + "attn.",
@@ -319,11 +357,11 @@ def toy_plain(cfg, w, tokens, margins=None):
                                               f(pre + "attn.v_proj.weight"), f(pre + "attn.out_proj.weight"),
                                               cfg.get("heads", 2), cfg.get("kv_heads", 1), hd, 1e4,
                                               cfg.get("stretch", 4.0))
-        elif kind == "sum":
+        elif kind in ("sum", "sum2"):
             s, rows = torch.zeros(H, dtype=torch.float64), []
             for t in range(len(tokens)):
                 s = cfg["decay"] * s + u[t]
-                rows.append(s)
+                rows.append(s * (1.0 + (t + 1) / 100.0) if kind == "sum2" else s)
             x = x + torch.stack(rows) @ f(pre + "sum.mix.weight").T
         elif kind in ("attn", "attn_shared"):
             kw = dict(nh=cfg.get("heads", 2), nkv=cfg.get("kv_heads", 1), hd=hd, eps=1e-5, theta=1e4,
@@ -361,6 +399,8 @@ def toy_plain(cfg, w, tokens, margins=None):
 TOYS = {
     # a mixer with state of its own between two kinds the package ships
     "state": dict(layer_types=["sum", "conv", "sum"], schedule=[[0, None], [1, None], [2, None]]),
+    # a mixer with two states of different shape and dtype (a list of cache needs), run twice
+    "two_states": dict(layer_types=["sum2", "attn"], schedule=[[0, None], [1, None], [0, None]]),
     # the layer order is data: block 0 runs twice (same weights, a cache of its own each time)
     "twice": dict(layer_types=["conv", "attn", "sum"], schedule=[[0, None], [1, None], [0, None], [2, None], [1, None]]),
     # the last attention layer has no keys and values of its own and reads the first one's cache
@@ -418,6 +458,9 @@ def test_toy_architecture_registered_from_the_test(toy, dtype, tmp_path):
         for i in range(len(seqs)):
             if sure[i][cut[i] + j]:
                 close(lg[i], want[i][cut[i] + j], f"decode {j}")
+    if toy == "two_states":
+        kinds = sorted((str(eng.cache.storage[g].dtype), tuple(eng.cache.storage[g].shape)) for g in eng.cache.state_groups)
+        assert kinds == [("torch.bfloat16", (2, eng.cache.n_slots, 1, 2)), ("torch.float32", (2, eng.cache.n_slots, 48))]
     if toy == "window":
         kvg = eng.cache.kv_groups[0]
         assert eng.cache._get(slots[0]).pages[kvg][0] is None     # pages before the window went back
