@@ -276,6 +276,8 @@ def main() -> int:
     for name, default in (("m", 8), ("n", 16384), ("k", 2048), ("context", 520), ("tokens", PREFILL_TOKENS),
                           ("heads", 32), ("kv-heads", 8), ("head-dim", 64), ("vocab", 65536), ("reps", 20)):
         ap.add_argument("--" + name, type=int, default=default)
+    ap.add_argument("--pair", default=None, choices=["0", "1"],
+                    help="--kernel gemm_tc: 1 the kernel of two multiprocessors a tile, 0 the one-multiprocessor kernels")
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--accumulate", action="store_true")
     args = ap.parse_args()
@@ -303,7 +305,7 @@ def main() -> int:
         print(json.dumps(measure.kernel_run(
             args.kernel, m=args.m, n=args.n, k=args.k, swiglu=args.swiglu, accumulate=args.accumulate, batch=args.batch,
             context=args.context, tokens=args.tokens, heads=args.heads, kv_heads=args.kv_heads, head_dim=args.head_dim,
-            vocab=args.vocab, reps=args.reps)))
+            vocab=args.vocab, reps=args.reps, pair=None if args.pair is None else args.pair == "1")))
         return 0
     if args.workload:
         return run_workload(args.workload, args.steps, warmup)

@@ -66,7 +66,7 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
     T* kv_row = nullptr;
     if (append && hs0 + SLOTS > nh) {
         const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
-        kv_row = pool + (size_t)page * page_stride + (size_t)(pos & (page_size - 1)) * hd;
+        if (mv_page_ok(page)) kv_row = pool + (size_t)page * page_stride + (size_t)(pos & (page_size - 1)) * hd;
     }
 #pragma unroll
     for (int s = 0; s < SLOTS; ++s) {
@@ -77,7 +77,7 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
         if (is_q) {
             dst = q_out + ((size_t)n * nh + hs) * hd;
         } else {
-            if (!append) continue;
+            if (!append || kv_row == nullptr) continue;
             const int g = is_k ? hs - nh : hs - nh - nkv;
             dst = kv_row + ((size_t)(is_k ? 0 : 1) * nkv + g) * page_size * hd;
         }
@@ -134,6 +134,8 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
         }
     }
 }
+
+MV_GUARD_SETTER(attention)
 
 MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, float eps,
                          const float* inv_freq, int half_split, const int* positions,
@@ -207,7 +209,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ pool, lo
         const T* krow = nullptr;
         float s = -INFINITY;
         if (valid) {
-            const int page = table[t >> page_shift];
+            const int page = mv_read_page(table[t >> page_shift]);
             krow = pool + (size_t)page * page_stride + ((size_t)g * page_size + (t & (page_size - 1))) * hd;
             float dot = 0.f;
             for (int d = 0; d < hd; d += 8) {

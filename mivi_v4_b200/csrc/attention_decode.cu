@@ -79,7 +79,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pool, lon
         const int cnt = min(32, pos - (lo + (run << 5)) + 1);
         // the row of this lane's key; lanes past the last key point at the run's first row
         const int tt = valid ? t : lo + (run << 5);
-        const T* krow = pool + (size_t)table[tt >> page_shift] * page_stride +
+        const T* krow = pool + (size_t)mv_read_page(table[tt >> page_shift]) * page_stride +
                         ((size_t)g * page_size + (tt & (page_size - 1))) * hd;
         const unsigned long long kaddr = (unsigned long long)krow;
         float s[GT];
@@ -248,6 +248,8 @@ int dispatch(int gt, int r, const void* q, const void* pool, long long page_stri
 }
 
 }  // namespace
+
+MV_GUARD_SETTER(attention_decode)
 
 // Scratch: part_o [N * nh * splits * hd] floats, part_ml [N * nh * splits * 2]
 // floats, tickets [N * nkv * head_tiles] ints that are zero before the first

@@ -113,7 +113,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         for (int idx = threadIdx.x; idx < KB * CHUNKS; idx += NWARPS * 32) {
             const int r = idx / CHUNKS, c = idx - r * CHUNKS;
             const int t = min(kb * KB + r, last_pos);                    // rows past the end repeat the last key
-            const int page = table[t >> page_shift];
+            const int page = mv_read_page(table[t >> page_shift]);
             const __nv_bfloat16* src = pool + (size_t)page * page_stride +
                                        ((size_t)g * page_size + (t & (page_size - 1))) * HD + c * 8;
             cp_async16(ks + ((size_t)buf * KB + r) * LDS + c * 8, src);
@@ -252,6 +252,8 @@ int launch(const void* q, const void* pool, long long page_stride, const int* pa
 
 // bfloat16 only; head sizes that are multiples of 16 up to 128.  Other sizes and
 // float32 use the generic kernel.
+MV_GUARD_SETTER(attention_prefill)
+
 MV_API int mv_attention_prefill(const void* q, const void* pool, long long page_stride, const int* page_table,
                                 int table_stride, int page_size, const int* cu, const int* starts, void* o,
                                 int N, int B, int nh, int nkv, int hd, float scale, int window,

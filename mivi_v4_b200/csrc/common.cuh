@@ -157,6 +157,44 @@ __device__ __forceinline__ void mv_unpack16(const uint4& r, float* out, const __
     }
 }
 
+// ---- index checks of a debug build -------------------------------------------------
+// Built with -DMIVI_DEBUG_CHECKS (MIVI_DEBUG_CHECKS=1 in the environment of the process that
+// loads the library), the kernels that turn a page-table entry or a slot number into an
+// address compare it first with the bound that the launch wrapper declared for this file
+// (mv_set_guard_<file>): an index outside it is never used for an access - a read takes
+// page or slot 0 instead, a write is skipped - and the device's error flag is set to 4,
+// which the host reports like a wait that ran out.  Nothing traps.  In an ordinary build
+// the checks compile to nothing.
+#ifdef MIVI_DEBUG_CHECKS
+struct MvGuard {
+    int n_pages, n_slots;
+    int* err;
+};
+static __device__ MvGuard mv_guard = {0x7fffffff, 0x7fffffff, nullptr};
+__device__ __forceinline__ bool mv_page_ok(int page) {
+    if ((unsigned)page < (unsigned)mv_guard.n_pages) return true;
+    if (mv_guard.err) atomicExch(mv_guard.err, 4);
+    return false;
+}
+__device__ __forceinline__ bool mv_slot_ok(int slot) {
+    if ((unsigned)slot < (unsigned)mv_guard.n_slots) return true;
+    if (mv_guard.err) atomicExch(mv_guard.err, 4);
+    return false;
+}
+#define MV_GUARD_SETTER(file)                                                                         \
+    MV_API int mv_set_guard_##file(int n_pages, int n_slots, int* err, cudaStream_t stream) {            \
+        const MvGuard g = {n_pages, n_slots, err};                                                    \
+        return (int)cudaMemcpyToSymbolAsync(mv_guard, &g, sizeof(g), 0, cudaMemcpyHostToDevice, stream); \
+    }
+#else
+__device__ __forceinline__ bool mv_page_ok(int) { return true; }
+__device__ __forceinline__ bool mv_slot_ok(int) { return true; }
+#define MV_GUARD_SETTER(file)
+#endif
+// an index for a read: itself, or 0 (always valid) where the debug build finds it out of bounds
+__device__ __forceinline__ int mv_read_page(int page) { return mv_page_ok(page) ? page : 0; }
+__device__ __forceinline__ int mv_read_slot(int slot) { return mv_slot_ok(slot) ? slot : 0; }
+
 static inline int mv_launch_status() {
     return (int)cudaGetLastError();
 }

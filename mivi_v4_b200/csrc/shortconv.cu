@@ -26,7 +26,7 @@ __global__ void shortconv_fwd_kernel(const float* __restrict__ p, const float* _
     const int n = (int)(i / H), d = (int)(i - (long long)n * H);
     const int b = seq_of[n];
     const int pos = positions[n], start = starts[b];
-    const float* st = state + (size_t)slots[b] * (k - 1) * H;
+    const float* st = state + (size_t)mv_read_slot(slots[b]) * (k - 1) * H;
     float y = bias ? bias[d] : 0.f;
     for (int j = 0; j < k; ++j) {
         const int src = pos - (k - 1) + j;
@@ -56,7 +56,7 @@ __global__ void shortconv_fwd_vec4_kernel(const float* __restrict__ p, const flo
     const int n = (int)(i / H4), d = (int)(i - (long long)n * H4) * 4;
     const int b = seq_of[n];
     const int pos = positions[n], start = starts[b];
-    const float* st = state + (size_t)slots[b] * (k - 1) * H;
+    const float* st = state + (size_t)mv_read_slot(slots[b]) * (k - 1) * H;
     float4 y = bias ? *reinterpret_cast<const float4*>(bias + d) : make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < k; ++j) {
         const int src = pos - (k - 1) + j;
@@ -111,7 +111,7 @@ __global__ void shortconv_fwd_tile_kernel(const float* __restrict__ p, const flo
         if (b != prev_b) {
             // the KW-1 values before this token: from this step's rows or from the carried state
             const int pos = positions[n], start = starts[b];
-            const float* st = state + (size_t)slots[b] * (KW - 1) * H;
+            const float* st = state + (size_t)mv_read_slot(slots[b]) * (KW - 1) * H;
 #pragma unroll
             for (int j = 0; j < KW - 1; ++j) {
                 const int src = pos - (KW - 1) + j;
@@ -161,7 +161,7 @@ __global__ void shortconv_state_kernel(const float* __restrict__ p, float* __res
     if (i >= (long long)B * H) return;
     const int b = (int)(i / H), d = (int)(i - (long long)b * H);
     const int len = lens[b];
-    if (len <= 0) return;
+    if (len <= 0 || !mv_slot_ok(slots[b])) return;
     float* st = state + (size_t)slots[b] * (k - 1) * H;
     const int first_row = cu[b];
     for (int j = 0; j < k - 1; ++j) {
@@ -188,6 +188,7 @@ __global__ void shortconv_decode_kernel(const float* __restrict__ p, const float
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)B * H) return;
     const int b = (int)(i / H), d = (int)(i - (long long)b * H);
+    if (!mv_slot_ok(slots[b])) return;
     float* st = state + (size_t)slots[b] * (k - 1) * H;
     const float* row = p + (size_t)b * 3 * H;
     const float bx = row[d] * row[2 * H + d];
@@ -204,6 +205,8 @@ __global__ void shortconv_decode_kernel(const float* __restrict__ p, const float
     y = fmaf(w[d * k + (k - 1)], bx, y);
     z[i] = mv_from_f32<TO>(row[H + d] * y);
 }
+
+MV_GUARD_SETTER(shortconv)
 
 MV_API int mv_shortconv_decode(const float* p, const float* w, const float* bias, float* state,
                                const int* slots, void* z, int z_dtype, int B, int H, int k,

@@ -81,7 +81,8 @@ class Engine:
         # ``profile``: every launch of every step is timed by stage and kernel (``profile_report``); steps
         # then run launch by launch, never from a recording
         self.profile = K.KernelProfile() if profile else None
-        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe and not profile
+        # (a build with index checks declares its bounds by host copies that cannot be recorded)
+        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe and not profile and not K.DEBUG_CHECKS
         self.max_graphs = max(1, int(max_graphs))
         self._graphs: "OrderedDict[tuple, _Recorded]" = OrderedDict()
         self._gws = Workspace(self.device)

@@ -230,7 +230,8 @@ def _replayed_us(calls, reps: int) -> float:
 
 def kernel_run(kernel: str, *, m: int = 8, n: int = 16384, k: int = 2048, swiglu: bool = False, accumulate: bool = False,
                batch: int = 8, context: int = 520, tokens: int = 2048, heads: int = 32, kv_heads: int = 8,
-               head_dim: int = 64, vocab: int = 65536, reps: int = 20, mark: bool = True) -> dict:
+               head_dim: int = 64, vocab: int = 65536, reps: int = 20, mark: bool = True,
+               pair: Optional[bool] = None) -> dict:
     """One kernel alone at given sizes.  Weights are rotated through enough copies that every launch
     reads them from HBM, not from L2.  After the timing, one more plain launch runs between
     cudaProfilerStart and cudaProfilerStop (``mark``), for a profiler that captures from there."""
@@ -249,6 +250,8 @@ def kernel_run(kernel: str, *, m: int = 8, n: int = 16384, k: int = 2048, swiglu
             out, kw = torch.zeros(m, n, device=dev), dict(accumulate=True)
         else:
             out, kw = torch.empty(m, n, device=dev), {}
+        if kernel == "gemm_tc":
+            kw["pair"] = pair
         fn(x, ws[0], out, **kw)                                        # first call: attributes, tensor maps
         us = _replayed_us([lambda w=w: fn(x, w, out, **kw) for w in ws], reps)
         res.update(m=m, n=n, k=k, us=us, weights_gb_per_s=n * k * 2 / us / 1e3, tflops=2.0 * m * n * k / us / 1e6)

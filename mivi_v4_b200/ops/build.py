@@ -28,12 +28,22 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "gemm_simt.cu", "shortconv.cu", "attention.cu", "attention_decode.cu",
              "sampling.cu"],
-    "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_swap.cu", "attention_prefill.cu",
+    "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_pair.cu", "gemm_tc_swap.cu", "attention_prefill.cu",
              "attention_prefill_tc.cu", "attention_decode_tc.cu"],
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+# MIVI_DEBUG_CHECKS=1: a build of its own whose kernels check page and slot indices against declared bounds
+# (see common.cuh); it lives beside the ordinary build under another name.
+DEBUG_CHECKS = os.environ.get("MIVI_DEBUG_CHECKS", "0") == "1"
+
+
+def nvcc_flags(debug_checks: bool = None) -> List[str]:
+    debug_checks = DEBUG_CHECKS if debug_checks is None else debug_checks
+    return NVCC_FLAGS + (["-DMIVI_DEBUG_CHECKS"] if debug_checks else [])
+
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -82,9 +92,9 @@ def build_dir() -> str:
     raise BuildError(f"no writable folder for compiled kernels (tried {in_tree} and {fallback})")
 
 
-def _digest(name: str) -> str:
+def _digest(name: str, debug_checks: bool = None) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(nvcc_flags(debug_checks)).encode())
     files = sorted(set(LIBRARIES[name]) | {f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))})
     for f in files:
         h.update(f.encode())
@@ -93,8 +103,13 @@ def _digest(name: str) -> str:
     return h.hexdigest()[:16]
 
 
-def library_path(name: str) -> str:
-    return os.path.join(build_dir(), f"libmivi_{name}_{_digest(name)}.so")
+def _stem(name: str, debug_checks: bool = None) -> str:
+    debug_checks = DEBUG_CHECKS if debug_checks is None else debug_checks
+    return f"libmivi_{name}{'dbg' if debug_checks else ''}_"
+
+
+def library_path(name: str, debug_checks: bool = None) -> str:
+    return os.path.join(build_dir(), f"{_stem(name, debug_checks)}{_digest(name, debug_checks)}.so")
 
 
 def _run(cmd: List[str], what: str) -> None:
@@ -103,15 +118,17 @@ def _run(cmd: List[str], what: str) -> None:
         raise BuildError(f"nvcc failed on {what}:\n{' '.join(cmd)}\n{proc.stdout}")
 
 
-def compile_library(name: str, verbose: bool = True) -> str:
+def compile_library(name: str, verbose: bool = True, debug_checks: bool = None) -> str:
     """Build ``name`` if its file is not there yet; returns the path of the .so."""
     if name not in LIBRARIES:
         raise BuildError(f"unknown kernel library {name!r}; known: {', '.join(sorted(LIBRARIES))}")
-    out = library_path(name)
+    out = library_path(name, debug_checks)
+    flags = nvcc_flags(debug_checks)
+    stem = _stem(name, debug_checks)
     if os.path.isfile(out):
         return out
     bdir = os.path.dirname(out)
-    with open(os.path.join(bdir, f".lock_{name}"), "w") as lock:
+    with open(os.path.join(bdir, f".lock_{stem}"), "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)        # another process may be building the same file
         try:
             if os.path.isfile(out):
@@ -120,7 +137,8 @@ def compile_library(name: str, verbose: bool = True) -> str:
             srcs = LIBRARIES[name]
             t0 = time.time()
             if verbose:
-                _say(f"compiling the {name} kernels for sm_100a ({len(srcs)} files, first call only) ...")
+                _say(f"compiling the {name} kernels for sm_100a ({len(srcs)} files, first call only"
+                     f"{', with index checks' if '-DMIVI_DEBUG_CHECKS' in flags else ''}) ...")
             stop = threading.Event()
 
             def ticker():
@@ -135,7 +153,7 @@ def compile_library(name: str, verbose: bool = True) -> str:
 
                 def one(src: str) -> str:
                     obj = os.path.join(tmp, src.replace(".cu", ".o"))
-                    _run([nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj], src)
+                    _run([nvcc, *flags, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj], src)
                     return obj
                 with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
                     objs = list(pool.map(one, srcs))
@@ -145,7 +163,7 @@ def compile_library(name: str, verbose: bool = True) -> str:
                 os.replace(part, out)
                 shutil.rmtree(tmp, ignore_errors=True)
                 for old in os.listdir(bdir):              # builds of older sources
-                    if old.startswith(f"libmivi_{name}_") and old.endswith(".so") and \
+                    if old.startswith(stem) and old.endswith(".so") and \
                             os.path.join(bdir, old) != out:
                         try:
                             os.remove(os.path.join(bdir, old))
@@ -167,5 +185,5 @@ def load_library(name: str) -> ctypes.CDLL:
         return _loaded[name]
 
 
-def build_all(verbose: bool = True) -> Dict[str, str]:
-    return {name: compile_library(name, verbose) for name in LIBRARIES}
+def build_all(verbose: bool = True, debug_checks: bool = None) -> Dict[str, str]:
+    return {name: compile_library(name, verbose, debug_checks) for name in LIBRARIES}

@@ -9,12 +9,13 @@ is an error, and so is a library that cannot be built.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional
 
 import torch
 
-from .build import load_library
+from .build import DEBUG_CHECKS, load_library
 
 F32, BF16 = 0, 1
 MAX_HEAD_DIM = 256
@@ -53,6 +54,7 @@ _SIGNATURES = {
         "mv_gemm_small_m_heads": [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
                                   _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "mv_gemm_tc_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
@@ -197,6 +199,23 @@ def _fn(lib: str, name: str):
     if _profile is not None and not name.endswith(("_partials", "_tile_rows", "_to_host", "_delay")):
         return _profile.wrap(name, f)
     return f
+
+
+def _guard(lib: str, file: str, device, n_pages: int = 0x7fffffff, n_slots: int = 0x7fffffff) -> None:
+    """In a build with index checks: declare, for the kernels of one source file, how many pages and slots
+    the tensors of the next launch really have.  Nothing in an ordinary build."""
+    if not DEBUG_CHECKS:
+        return
+    name = "mv_set_guard_" + file
+    f = _fns.get((lib, name))
+    if f is None:
+        f = getattr(load_library(lib), name)
+        f.argtypes = [_I, _I, _P, _P]
+        f.restype = ctypes.c_int
+        _fns[(lib, name)] = f
+    code = f(int(min(n_pages, 0x7fffffff)), int(min(n_slots, 0x7fffffff)), _error_flag(device).data_ptr(), _stream())
+    if code != 0:
+        raise KernelError(f"{name}: CUDA error {code}")
 
 
 def _stream() -> int:
@@ -570,10 +589,24 @@ def check_device_errors() -> None:
             raise KernelError(_error_text(key, code))
 
 
+_PREFILL_GEMM = os.environ.get("MIVI_PREFILL_GEMM", "auto")      # pair | single | auto
+
+
+def gemm_tc_pair_takes(M: int, N: int) -> bool:
+    """Shapes for which two multiprocessors share a 256 x 256 tile (``gemm_tc_pair.cu``): more than
+    128 rows, and enough tiles that most pairs of the device get one."""
+    if _PREFILL_GEMM == "single" or M <= 128 or N < 128:
+        return False
+    tiles = -(-M // 256) * -(-N // 256)
+    return _PREFILL_GEMM == "pair" or tiles >= n_sms() // 3
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+            accumulate: bool = False, swiglu: bool = False, pair: Optional[bool] = None) -> torch.Tensor:
     """out = x @ w.T, bfloat16 operands, on the tcgen05 tensor cores (TMA
-    loads, accumulator in tensor memory): the matrix product of prefill."""
+    loads, accumulator in tensor memory): the matrix product of prefill.
+    ``pair``: True: the kernel in which two multiprocessors share a 256 x 256 tile, False: the
+    one-multiprocessor kernels, None: by shape (``gemm_tc_pair_takes``)."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
@@ -595,9 +628,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
         mode = 0 if out.dtype == torch.float32 else 1
         _need(out, "gemm out", None, (M, N))
         _dt(out)
-    _check(_fn("bf16", "mv_gemm_tc")(
+    if pair is None:
+        pair = gemm_tc_pair_takes(M, N)
+    elif pair and (M <= 128 or N < 128):
+        raise KernelError(f"gemm_tc: the pair kernel needs more than 128 rows and at least 128 columns, got {M} x {N}")
+    entry = "mv_gemm_tc_pair" if pair else "mv_gemm_tc"
+    _check(_fn("bf16", entry)(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc")
+        out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), entry)
     _account_gemm(x, w, out, accumulate)
     return out
 
@@ -652,6 +690,7 @@ def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], st
     _need(state, "shortconv state", torch.float32)
     if state.dim() != 3 or state.shape[1] != k - 1 or state.shape[2] != H:
         raise KernelError(f"shortconv: state shape {tuple(state.shape)}, expected [slots, {k - 1}, {H}]")
+    _guard("core", "shortconv", p.device, n_slots=state.shape[0])
     if N == n_seqs and decode:
         _check(_fn("core", "mv_shortconv_decode")(
             _need(p, "shortconv p", torch.float32), _need(w, "shortconv taps", torch.float32),
@@ -693,6 +732,7 @@ def qk_prepare(qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch
     if pool.dtype != q_out.dtype:
         raise KernelError(f"qk_prepare: cache is {pool.dtype} but q is {q_out.dtype}")
     _need(page_table, "page table", torch.int32)
+    _guard("core", "attention", qkv.device, n_pages=pool.shape[0])
     _check(_fn("core", "mv_qk_prepare")(
         _need(qkv, "qkv", torch.float32, (N, (nh + 2 * nkv) * hd)),
         _need(wq, "q norm weight", torch.float32, (hd,), True),
@@ -734,6 +774,7 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, page_table, positions
     _check_kv(pool, nkv, hd, page_size, "attention")
     if q.dtype != pool.dtype or out.dtype != q.dtype:
         raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    _guard("core", "attention", q.device, n_pages=pool.shape[0])
     _check(_fn("core", "mv_attention_generic")(
         _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.stride(0),
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
@@ -793,6 +834,7 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, page_table, positions,
     part_o = ws.get("attn_part_o", (N * nh * splits * hd,), torch.float32)
     part_ml = ws.get("attn_part_ml", (N * nh * splits * 2,), torch.float32)
     tickets = ws.get_zeroed("attn_tickets", (N * nkv * head_tiles,), torch.int32)
+    _guard("core", "attention_decode", q.device, n_pages=pool.shape[0])
     _check(_fn("core", "mv_attention_decode")(
         _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.stride(0),
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
@@ -875,6 +917,7 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, page_table, cu, start
     _check_kv(pool, nkv, hd, page_size, "attention")
     if q.dtype != pool.dtype or out.dtype != q.dtype:
         raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    _guard("bf16", "attention_prefill", q.device, n_pages=pool.shape[0])
     _check(_fn("bf16", "mv_attention_prefill")(
         _need(q, "q", None, (N, nh * hd)), _need(pool, "cache pool"), pool.stride(0),
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
@@ -887,6 +930,8 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, page_table, cu, start
 def attention_prefill_tc_supported(dtype: torch.dtype, hd: int, pool: torch.Tensor, window: int) -> bool:
     """What the tcgen05 prefill attention takes: bfloat16, head size 64, no window, and a
     dense cache pool [pages, 2, kv heads, 64, 64] that a 2-D tensor map can describe."""
+    if DEBUG_CHECKS:
+        return False            # a build with index checks runs the kernels that have them
     if dtype != torch.bfloat16 or hd != 64 or window != 0 or pool.dim() != 5 or pool.shape[3] != 64:
         return False
     rows = pool.shape[0] * 2 * pool.shape[2] * 64

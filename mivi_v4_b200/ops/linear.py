@@ -129,7 +129,7 @@ def shortconv_decode_fused_ok(n_rows: int, x: torch.Tensor, w_in: torch.Tensor) 
     projection (``kernels.gemm_small_m_shortconv``): the steps whose products take the
     register-streaming kernel, bfloat16 operands.  One launch less a layer; MIVI_FUSED_CONV=0
     keeps the two kernels."""
-    return (_FUSED_CONV and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
+    return (_FUSED_CONV and not K.DEBUG_CHECKS and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
             and tensor_core_ok(x, w_in))
 
 
@@ -151,7 +151,7 @@ def heads_fused_ok(n_rows: int, x: torch.Tensor, w_qkv: torch.Tensor, head_dim: 
     """Whether the preparation of q, k and v (per-head norm, rotation, append to the cache) can run
     as the epilogue of their projection (``kernels.gemm_small_m_heads``): steps whose products take
     the register-streaming kernel, heads of 64, bfloat16 cache.  MIVI_FUSED_QK=0 keeps the two kernels."""
-    return (_FUSED_QK and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
+    return (_FUSED_QK and not K.DEBUG_CHECKS and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
             and head_dim == K.HEADS_FUSED_HEAD_DIM and pool.dtype == torch.bfloat16 and tensor_core_ok(x, w_qkv))
 
 

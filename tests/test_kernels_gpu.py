@@ -349,22 +349,26 @@ def test_shortconv_any_cut(out_dtype, H, k, bias):
                                     (1000, 2048, 2048), (2048, 512, 8192), (70, 9600, 96),
                                     # wide enough for the persistent 128 x 256 kernel, ragged in every dimension
                                     (2048, 2048, 512), (1500, 4100, 264), (4096, 6144, 2048), (12300, 300, 72),
-                                    (2048, 2048, 8192)])
-def test_gemm_tc(M, N, Kd):
+                                    (2048, 2048, 8192), (129, 128, 64), (257, 257, 136), (5000, 1100, 392)])
+@pytest.mark.parametrize("pair", [False, True], ids=["one_sm", "pair"])
+def test_gemm_tc(M, N, Kd, pair):
+    """Both tcgen05 products of many rows: one multiprocessor a tile, and two on a 256 x 256 tile."""
+    if pair and (M <= 128 or N < 128):
+        pytest.skip("the pair kernel takes more than 128 rows and at least 128 columns")
     x, w = rnd(M, Kd, dtype=torch.bfloat16), rnd(N, Kd, dtype=torch.bfloat16, seed=1)
     bias = rnd(N, seed=2)
     want = x.double() @ w.double().T
     tol = dict(rtol=1e-4, atol=1e-3 * math.sqrt(Kd / 64))
     out = torch.full((M, N), float("nan"), device=DEV)
-    K().gemm_tc(x, w, out)
+    K().gemm_tc(x, w, out, pair=pair)
     K().check_device_errors()
     assert torch.allclose(out.double(), want, **tol), (out.double() - want).abs().max()
     base = rnd(M, N, seed=3)
     acc = base.clone()
-    K().gemm_tc(x, w, acc, bias=bias, accumulate=True)
+    K().gemm_tc(x, w, acc, bias=bias, accumulate=True, pair=pair)
     assert torch.allclose(acc.double(), want + base.double() + bias.double(), **tol)
     ob = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    K().gemm_tc(x, w, ob)
+    K().gemm_tc(x, w, ob, pair=pair)
     assert torch.allclose(ob.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(Kd / 64))
     K().check_device_errors()
 
@@ -490,11 +494,14 @@ def test_gemm_swiglu_epilogue(M, F, Kd):
     want = a / (1 + torch.exp(-a)) * b
     out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
     scale = max(1.0, want.abs().max().item())
-    for fn in ([K().gemm_small_m, K().gemm_tc_swap] if M <= 64 else [K().gemm_tc]):
+    import functools
+    many = [functools.partial(K().gemm_tc, pair=False)] + \
+        ([functools.partial(K().gemm_tc, pair=True)] if M > 128 and 2 * F >= 128 else [])
+    for fn in ([K().gemm_small_m, K().gemm_tc_swap] if M <= 64 else many):
         out.fill_(float("nan"))
         fn(x, grouped(w1, w3), out, swiglu=True)
         K().check_device_errors()
-        assert (out.double() - want).abs().max().item() <= 1e-2 * scale, fn.__name__
+        assert (out.double() - want).abs().max().item() <= 1e-2 * scale, fn
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
