@@ -135,6 +135,84 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
     }
 }
 
+
+// The same for heads of 64 with the pairs (2i, 2i+1), the shape of every LFM2 model, when a step has
+// many tokens: one warp a token.  A lane holds four consecutive elements (two pairs) of a head, so
+// a half-warp is one head and the warp takes two heads a round, eight heads' loads in flight before
+// any is used.  The rotation of a lane's two pairs at this position is worked out once for all the
+// token's heads, and the per-head sums of squares need four shuffles inside the half-warp.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_prepare_hd64_kernel(const float* __restrict__ qkv, const float* __restrict__ wq, const float* __restrict__ wk,
+                       float eps, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                       const int* __restrict__ seq_of, const int* __restrict__ page_table, int table_stride,
+                       int page_shift, T* __restrict__ pool, long long page_stride, int append,
+                       T* __restrict__ q_out, int N, int nh, int nkv) {
+    mv_pdl_begin();
+    constexpr int HD = 64, U = 4;
+    const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (n >= N) return;
+    const int lane = threadIdx.x & 31, sub = lane & 15, hsel = lane >> 4;
+    const int slots = nh + 2 * nkv;
+    const int pos = positions[n];
+    const int page_size = 1 << page_shift;
+    float sn0 = 0.f, cs0 = 1.f, sn1 = 0.f, cs1 = 1.f;
+    if (inv_freq) {
+        sincosf((float)pos * inv_freq[2 * sub], &sn0, &cs0);
+        sincosf((float)pos * inv_freq[2 * sub + 1], &sn1, &cs1);
+    }
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 wq4 = wq ? *reinterpret_cast<const float4*>(wq + 4 * sub) : one;
+    const float4 wk4 = wk ? *reinterpret_cast<const float4*>(wk + 4 * sub) : one;
+    T* kv_row = nullptr;
+    if (append) {
+        const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
+        if (mv_page_ok(page)) kv_row = pool + (size_t)page * page_stride + (size_t)(pos & (page_size - 1)) * HD;
+    }
+    const float* row = qkv + (size_t)n * slots * HD + 4 * sub;
+    for (int base = 0; base < slots; base += 2 * U) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int hs = base + 2 * u + hsel;
+            v[u] = hs < slots ? *reinterpret_cast<const float4*>(row + (size_t)hs * HD) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int hs = base + 2 * u + hsel;
+            const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
+            float4 x = v[u];
+            // every lane takes part in the shuffles; what a lane beyond the last head computes is not stored
+            float ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (hs >= slots) continue;
+            if (is_q || is_k) {
+                const float* w = is_q ? wq : wk;
+                if (w) {
+                    const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+                    const float4 ww = is_q ? wq4 : wk4;
+                    x.x *= scale * ww.x; x.y *= scale * ww.y; x.z *= scale * ww.z; x.w *= scale * ww.w;
+                }
+                if (inv_freq) {
+                    const float a0 = x.x * cs0 - x.y * sn0, b0 = x.x * sn0 + x.y * cs0;
+                    const float a1 = x.z * cs1 - x.w * sn1, b1 = x.z * sn1 + x.w * cs1;
+                    x = make_float4(a0, b0, a1, b1);
+                }
+            }
+            T* dst;
+            if (is_q) {
+                dst = q_out + ((size_t)n * nh + hs) * HD;
+            } else {
+                if (!append || kv_row == nullptr) continue;
+                const int g = is_k ? hs - nh : hs - nh - nkv;
+                dst = kv_row + ((size_t)(is_k ? 0 : 1) * nkv + g) * page_size * HD;
+            }
+            mv_store4(dst + 4 * sub, x.x, x.y, x.z, x.w);
+        }
+    }
+}
+
 MV_GUARD_SETTER(attention)
 
 MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, float eps,
@@ -146,6 +224,21 @@ MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, flo
     if (hd % 2 || hd > MV_MAX_HEAD_DIM || (page_size & (page_size - 1))) return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
+    if (hd == 64 && !half_split && N >= 256 && nkv > 0 &&
+        ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool | (uintptr_t)wq | (uintptr_t)wk) & 15) == 0) &&
+        (page_stride * (dtype == MV_DT_BF16 ? 2 : 4)) % 16 == 0) {
+        // many tokens with heads of 64: a warp a token
+        const unsigned tblocks = (unsigned)((N + 7) / 8);
+        if (dtype == MV_DT_BF16)
+            mv_launch(qk_prepare_hd64_kernel<__nv_bfloat16>, tblocks, 256, 0, stream, qkv, wq, wk, eps, inv_freq,
+                      positions, seq_of, page_table, table_stride, page_shift, (__nv_bfloat16*)pool, page_stride,
+                      append, (__nv_bfloat16*)q_out, N, nh, nkv);
+        else
+            mv_launch(qk_prepare_hd64_kernel<float>, tblocks, 256, 0, stream, qkv, wq, wk, eps, inv_freq, positions,
+                      seq_of, page_table, table_stride, page_shift, (float*)pool, page_stride, append,
+                      (float*)q_out, N, nh, nkv);
+        return mv_launch_status();
+    }
     // many tokens: four head slots a warp, whose loads overlap; few: one, for more warps
     const int slots = N >= 64 ? 4 : 1;
     const long long warps = (long long)N * ((nh + 2 * nkv + slots - 1) / slots);

@@ -285,6 +285,46 @@ def test_qk_prepare(dtype, style, nh, nkv, hd, eps, theta):
     assert int((pool != 0).sum()) <= written     # nothing was written anywhere else
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("nh,nkv,normed,rotated", [(32, 8, True, True), (3, 1, True, True), (5, 2, False, True),
+                                                   (4, 4, True, False), (7, 3, False, False)])
+def test_qk_prepare_many_tokens_heads_of_64(dtype, nh, nkv, normed, rotated):
+    """Steps of hundreds of tokens with heads of 64 take a kernel of their own (a warp a token, two heads a
+    round): odd head counts, so that the two halves of a warp hold heads of different kinds; two sequences
+    whose tokens lie in shuffled pages; with and without the norm and the rotation."""
+    hd, page, eps, theta = 64, 16, 1e-5, 10000.0
+    lengths = [301, 260]
+    g = torch.Generator().manual_seed(nh * 10 + nkv)
+    blocks = [-(-n // page) for n in lengths]
+    order = torch.randperm(sum(blocks) + 2, generator=g).tolist()
+    table = torch.zeros(2, max(blocks), dtype=torch.int32)
+    for b in range(2):
+        for blk in range(blocks[b]):
+            table[b, blk] = order.pop()
+    pool = torch.zeros(sum(blocks) + 2, 2, nkv, page, hd, dtype=dtype, device=DEV)
+    toks = [(0, p) for p in range(lengths[0])] + [(1, p) for p in range(lengths[1])]
+    qkv = rnd(len(toks), (nh + 2 * nkv) * hd, scale=2.0)
+    wq, wk = (rnd(hd) + 1.0, rnd(hd, seed=1) + 1.0) if normed else (None, None)
+    inv = (1.0 / (torch.tensor(theta, dtype=torch.float64) ** (2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)))
+    q_out = torch.full((len(toks), nh * hd), float("nan"), dtype=dtype, device=DEV)
+    K().qk_prepare(qkv, wq, wk, eps, inv.float().to(DEV) if rotated else None, False, ints([p for _, p in toks]),
+                   ints([b for b, _ in toks]), table.to(DEV), pool, q_out, nh, nkv, hd)
+    pos = torch.tensor([p for _, p in toks])
+    x = qkv.double().cpu()
+    qw, kw = x[:, :nh * hd].reshape(-1, nh, hd), x[:, nh * hd:(nh + nkv) * hd].reshape(-1, nkv, hd)
+    if normed:
+        qw, kw = P.plain_rms_norm(qw, wq.double().cpu(), eps), P.plain_rms_norm(kw, wk.double().cpu(), eps)
+    if rotated:
+        qw, kw = P.plain_rope(qw, pos, theta, "interleaved"), P.plain_rope(kw, pos, theta, "interleaved")
+    vw = x[:, (nh + nkv) * hd:].reshape(-1, nkv, hd)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(q_out.double().cpu().reshape(-1, nh, hd), qw, rtol=tol, atol=tol * 4)
+    got_k = torch.stack([pool[int(table[b, p // page]), 0, :, p % page] for b, p in toks]).double().cpu()
+    got_v = torch.stack([pool[int(table[b, p // page]), 1, :, p % page] for b, p in toks]).double().cpu()
+    assert torch.allclose(got_k, kw, rtol=tol, atol=tol * 4) and torch.allclose(got_v, vw, rtol=tol, atol=tol * 4)
+    assert int((pool != 0).sum()) <= len(toks) * 2 * nkv * hd        # nothing was written anywhere else
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("H,k,bias", [(8, 3, False), (200, 4, True), (64, 2, False), (16, 1, True), (24, 7, False)])
 def test_shortconv_any_cut(out_dtype, H, k, bias):
