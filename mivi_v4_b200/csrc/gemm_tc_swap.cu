@@ -36,23 +36,66 @@ struct NormLink {
     int emit_stride;
 };
 
-template <int BN, int STAGES>
-struct SwapLayout {
-    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int CSUM_BYTES = BM * BN * 4;   // [token][row]: a warp reads consecutive words
-    static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 8;
-    static constexpr int TOTAL = (TILE_BYTES > CSUM_BYTES ? TILE_BYTES : CSUM_BYTES) + BAR_BYTES + 1024;
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+// The gated short convolution of a decode step as the epilogue of its input projection (TAIL 1;
+// crates/mivi-model/src/ssm.rs:81-140): W is [3 H, K] with the rows of B, C and x one after another.
+// A block takes 128 channels, that is the same 128 rows out of each third: three W tiles a K block,
+// three accumulators in tensor memory.  After the slices are added a lane holds B, C and x of four
+// channels of a token and finishes them: B * x, the k taps over the sequence's k-1 kept values, the
+// shift of those, C *.
+struct ConvTail {
+    const float* taps;                 // [H][k]
+    const float* conv_bias;            // [H] or null
+    float* state;                      // [slots][k - 1][H], the last k-1 values of B * x per sequence
+    const int* slots;                  // [M]: the slot of token m's sequence (one token a sequence)
+    int k;
 };
 
-template <int BN, int STAGES>
+// The preparation of q, k and v as the epilogue of their fused projection (TAIL 2, head size 64, the
+// pairs (2i, 2i+1); crates/mivi-model/src/transformer.rs:81-108): W is [(nh + 2 nkv) 64, K], query
+// heads, then key heads, then value heads; a tile of 128 rows is two heads, a half-warp finishes one
+// for a token with four elements a lane: RMSNorm over the head (q and k), rotation by the token's
+// position (q and k), then q goes out in bfloat16 and k and v into the token's row of its cache page.
+struct HeadTail {
+    const float* wq;                   // [64] norm weight of the query heads, or null: no norm
+    const float* wk;                   // the same for the key heads
+    const float* inv_freq;             // [32] or null: no rotation
+    const int* positions;              // [M]
+    const int* seq_of;                 // [M] row of the page table
+    const int* page_table;
+    __nv_bfloat16* pool;               // [page][K, V][kv head][page_size][64]
+    __nv_bfloat16* q_out;              // [M][nh * 64]
+    long long page_stride;
+    float eps;
+    int table_stride, page_shift, nh, nkv;
+};
+
+// What the NEXT product of the step will read (or null): once a block's loads are all issued, the
+// idle lanes of its loading warp ask the L2 cache for their share of these lines.
+struct Ahead {
+    const void* w;
+    long long bytes;
+};
+
+template <int BN, int STAGES, int TAIL>
+struct SwapLayout {
+    static constexpr int NW = TAIL == 1 ? 3 : 1;     // W tiles (and accumulators) a K block
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = NW * A_BYTES + B_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int CSUM_BYTES = NW * BM * BN * 4;   // [accumulator][token][row]: a warp reads consecutive words
+    static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 8;
+    static constexpr int TOTAL = (TILE_BYTES > CSUM_BYTES ? TILE_BYTES : CSUM_BYTES) + BAR_BYTES + 1024;
+    static constexpr int TMEM_COLS = NW * BN <= 32 ? 32 : (NW * BN <= 64 ? 64 : (NW * BN <= 128 ? 128 : 256));
+};
+
+template <int BN, int STAGES, int TAIL>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
-                    const NormLink link, int* __restrict__ err) {
-    using L = SwapLayout<BN, STAGES>;
+                    const NormLink link, const ConvTail tail, const HeadTail heads, const Ahead ahead,
+                    int* __restrict__ err) {
+    using L = SwapLayout<BN, STAGES, TAIL>;
+    constexpr int NW = L::NW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int DATA_BYTES = L::TILE_BYTES > L::CSUM_BYTES ? L::TILE_BYTES : L::CSUM_BYTES;
@@ -98,20 +141,33 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int first = nkb < STAGES ? nkb : STAGES;
             for (int i = 0; i < first; ++i) {
                 mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
-                tma_load_2d(tiles0 + i * L::STAGE_BYTES, &map_w, (kb0 + i) * BK, n0, full0 + 8 * i);
+#pragma unroll
+                for (int t = 0; t < NW; ++t)          // TAIL 1: the same rows of the B, C and x thirds, N rows apart
+                    tma_load_2d(tiles0 + i * L::STAGE_BYTES + t * L::A_BYTES, &map_w, (kb0 + i) * BK, n0 + t * N,
+                                full0 + 8 * i);
             }
             mv_pdl_wait();
             for (int i = 0; i < first; ++i)
-                tma_load_2d(tiles0 + i * L::STAGE_BYTES + L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * i);
+                tma_load_2d(tiles0 + i * L::STAGE_BYTES + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * i);
             for (int i = first; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const unsigned phase = (unsigned)(i / STAGES) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, err, 1)) break;
                 mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
                 const unsigned a_dst = tiles0 + s * L::STAGE_BYTES;
-                tma_load_2d(a_dst, &map_w, (kb0 + i) * BK, n0, full0 + 8 * s);
-                tma_load_2d(a_dst + L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * s);
+#pragma unroll
+                for (int t = 0; t < NW; ++t)
+                    tma_load_2d(a_dst + t * L::A_BYTES, &map_w, (kb0 + i) * BK, n0 + t * N, full0 + 8 * s);
+                tma_load_2d(a_dst + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * s);
             }
+        }
+        __syncwarp();
+        if (ahead.w && ahead.bytes > 0) {
+            // this block's own loads are on their way: ask L2 for the block's share of what comes next
+            const long long lines = ahead.bytes >> 7;
+            const long long nblk = (long long)gridDim.x * gridDim.y, me = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+            for (long long l = me * 32 + lane; l < lines; l += nblk * 32)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)ahead.w + (l << 7)));
         }
     } else if (warp == 1) {
         if (lane == 0 && nkb > 0) {
@@ -122,11 +178,13 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (!mbar_wait(full0 + 8 * s, phase, err, 2)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned a_addr = tiles0 + s * L::STAGE_BYTES;
-                const unsigned b_addr = a_addr + L::A_BYTES;
+                const unsigned b_addr = a_addr + NW * L::A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)
-                    mma_f16(tmem_base, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
-                            (i > 0 || k > 0) ? 1u : 0u);
+                for (int t = 0; t < NW; ++t)
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        mma_f16(tmem_base + (unsigned)(t * BN), smem_desc(a_addr + t * L::A_BYTES + k * 32),
+                                smem_desc(b_addr + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 mma_commit(empty0 + 8 * s);
             }
             mma_commit(acc_bar);
@@ -138,7 +196,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (acc_ok) acc_ok = mbar_wait(acc_bar, 0, err, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = 0; c0 < NW * BN; c0 += (BN < 32 ? BN : 32)) {
             unsigned v[32];
             if (acc_ok) {
                 tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
@@ -148,8 +206,8 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int j = 0; j < 32; ++j) v[j] = 0u;
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (c0 + j < BN) csum[(c0 + j) * BM + r] = __uint_as_float(v[j]);      // [token][row]
+            for (int j = 0; j < (BN < 32 ? BN : 32); ++j)
+                csum[(c0 + j) * BM + r] = __uint_as_float(v[j]);      // [accumulator][token][row], column c0 + j
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -167,12 +225,166 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         __syncthreads();
         share[0] = csum;
     }
+    constexpr int WARPS_ALL = THREADS / 32;
+    if constexpr (TAIL == 1) {
+        // The convolution: an item is 128 channels of one token, four consecutive channels a lane, whose
+        // B, C and x sums lie in the three accumulators' regions of every slice.
+        const int r = 4 * lane, d = n0 + r;                  // N counts channels here
+        const int k = tail.k;
+        const bool fast = k <= 4 && (N & 3) == 0 && (ldo & 3) == 0 &&
+                          ((((uintptr_t)tail.state | (uintptr_t)tail.taps | (uintptr_t)bias | (uintptr_t)tail.conv_bias) & 15) == 0) &&
+                          (((uintptr_t)out & 7) == 0);
+        for (int m = slice + slices * warp; m < M; m += slices * WARPS_ALL) {
+            float ss = 0.f;
+            if (link.scale_part)
+                for (int p = lane; p < link.n_scale_part; p += 32)
+                    ss += link.scale_part[(size_t)m * link.scale_stride + p];
+            float4 part[3][8];
+#pragma unroll
+            for (int t = 0; t < 3; ++t)
+#pragma unroll
+                for (int sl = 0; sl < 8; ++sl)
+                    part[t][sl] = sl < slices ? *reinterpret_cast<const float4*>(share[sl] + (t * BN + m) * BM + r)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            float v[3][4];
+#pragma unroll
+            for (int t = 0; t < 3; ++t) {
+                v[t][0] = v[t][1] = v[t][2] = v[t][3] = 0.f;
+#pragma unroll
+                for (int sl = 0; sl < 8; ++sl) {
+                    v[t][0] += part[t][sl].x; v[t][1] += part[t][sl].y; v[t][2] += part[t][sl].z; v[t][3] += part[t][sl].w;
+                }
+            }
+            float sc = 1.f;
+            if (link.scale_part) sc = 1.0f / sqrtf(mv_warp_sum(ss) * link.inv_dim + link.eps);
+            float* st = tail.state + (size_t)tail.slots[m] * (k - 1) * N;
+            __nv_bfloat16* z = (__nv_bfloat16*)out + (size_t)m * ldo;
+            if (fast && d + 3 < N) {
+                // widths up to 4, everything 16-byte aligned: the kept values, the taps and the biases of the
+                // lane's four channels come in 16-byte loads that are all requested before any is used
+                float4 kept[3], tp[4], bb[3], cb = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 3; ++j)
+                    kept[j] = j < k - 1 ? *reinterpret_cast<const float4*>(st + (size_t)j * N + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)               // the 4 k taps of channels d .. d + 3 lie one after another
+                    tp[j] = j < k ? *reinterpret_cast<const float4*>(tail.taps + (size_t)d * k + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int t = 0; t < 3; ++t)
+                    bb[t] = bias ? *reinterpret_cast<const float4*>(bias + t * N + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (tail.conv_bias) cb = *reinterpret_cast<const float4*>(tail.conv_bias + d);
+                const float* tpf = reinterpret_cast<const float*>(tp);
+                const float* kf[3] = {reinterpret_cast<const float*>(&kept[0]), reinterpret_cast<const float*>(&kept[1]),
+                                      reinterpret_cast<const float*>(&kept[2])};
+                const float* cbf = reinterpret_cast<const float*>(&cb);
+                float bxv[4], zv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float Bv = v[0][e] * sc + reinterpret_cast<const float*>(&bb[0])[e];
+                    const float Cv = v[1][e] * sc + reinterpret_cast<const float*>(&bb[1])[e];
+                    const float Xv = v[2][e] * sc + reinterpret_cast<const float*>(&bb[2])[e];
+                    bxv[e] = Bv * Xv;
+                    float y = cbf[e];
+#pragma unroll
+                    for (int j = 0; j < 3; ++j)
+                        if (j < k - 1) y = fmaf(tpf[e * k + j], kf[j][e], y);
+                    y = fmaf(tpf[e * k + (k - 1)], bxv[e], y);
+                    zv[e] = Cv * y;
+                }
+#pragma unroll
+                for (int j = 1; j < 3; ++j)
+                    if (j < k - 1) *reinterpret_cast<float4*>(st + (size_t)(j - 1) * N + d) = kept[j];   // shift towards the older end
+                if (k > 1) *reinterpret_cast<float4*>(st + (size_t)(k - 2) * N + d) = make_float4(bxv[0], bxv[1], bxv[2], bxv[3]);
+                mv_store4(z + d, zv[0], zv[1], zv[2], zv[3]);
+                continue;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int c = d + e;
+                if (c >= N) break;
+                float Bv = v[0][e] * sc, Cv = v[1][e] * sc, Xv = v[2][e] * sc;
+                if (bias) { Bv += bias[c]; Cv += bias[N + c]; Xv += bias[2 * N + c]; }
+                const float bx = Bv * Xv;
+                float y = tail.conv_bias ? tail.conv_bias[c] : 0.f;
+                for (int j = 0; j < k - 1; ++j) {
+                    const float old = st[(size_t)j * N + c];
+                    y = fmaf(tail.taps[c * k + j], old, y);
+                    if (j > 0) st[(size_t)(j - 1) * N + c] = old;        // shift towards the older end
+                }
+                if (k > 1) st[(size_t)(k - 2) * N + c] = bx;
+                y = fmaf(tail.taps[c * k + (k - 1)], bx, y);
+                z[c] = __float2bfloat16_rn(Cv * y);
+            }
+        }
+    } else if constexpr (TAIL == 2) {
+        // The heads: an item is the tile's two heads of one token; a half-warp holds a head, a lane four
+        // consecutive elements of it, that is the pairs 2 sub and 2 sub + 1.
+        const int sub = lane & 15, r = 4 * lane;
+        const int hs = 2 * (int)blockIdx.y + (lane >> 4);
+        const int n_slots = heads.nh + 2 * heads.nkv;
+        const bool is_q = hs < heads.nh, is_k = !is_q && hs < heads.nh + heads.nkv;
+        const float* w = is_q ? heads.wq : (is_k ? heads.wk : nullptr);
+        float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (w) w4 = *reinterpret_cast<const float4*>(w + 4 * sub);
+        const bool rotate = heads.inv_freq && (is_q || is_k);
+        const float f0 = rotate ? heads.inv_freq[2 * sub] : 0.f, f1 = rotate ? heads.inv_freq[2 * sub + 1] : 0.f;
+        for (int m = slice + slices * warp; m < M; m += slices * WARPS_ALL) {
+            float ss = 0.f;
+            if (link.scale_part)
+                for (int p = lane; p < link.n_scale_part; p += 32)
+                    ss += link.scale_part[(size_t)m * link.scale_stride + p];
+            float4 part[8];
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl)
+                part[sl] = sl < slices ? *reinterpret_cast<const float4*>(share[sl] + m * BM + r)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                v[0] += part[sl].x; v[1] += part[sl].y; v[2] += part[sl].z; v[3] += part[sl].w;
+            }
+            if (link.scale_part) {
+                const float sc = 1.0f / sqrtf(mv_warp_sum(ss) * link.inv_dim + link.eps);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] *= sc;
+            }
+            // the head's sum of squares: over the 16 lanes of the half-warp (every lane takes part)
+            float hq = fmaf(v[0], v[0], fmaf(v[1], v[1], fmaf(v[2], v[2], v[3] * v[3])));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) hq += __shfl_xor_sync(0xffffffffu, hq, o);
+            if (hs >= n_slots) continue;
+            const int pos = heads.positions[m];
+            if (w) {
+                const float scale = 1.0f / sqrtf(hq / 64.0f + heads.eps);
+                v[0] *= scale * w4.x; v[1] *= scale * w4.y; v[2] *= scale * w4.z; v[3] *= scale * w4.w;
+            }
+            if (rotate) {
+                float sn0, cs0, sn1, cs1;
+                sincosf((float)pos * f0, &sn0, &cs0);
+                sincosf((float)pos * f1, &sn1, &cs1);
+                const float a0 = v[0] * cs0 - v[1] * sn0, b0 = v[0] * sn0 + v[1] * cs0;
+                const float a1 = v[2] * cs1 - v[3] * sn1, b1 = v[2] * sn1 + v[3] * cs1;
+                v[0] = a0; v[1] = b0; v[2] = a1; v[3] = b1;
+            }
+            __nv_bfloat16* dst;
+            if (is_q) {
+                dst = heads.q_out + ((size_t)m * heads.nh + hs) * 64;
+            } else {
+                const int page_size = 1 << heads.page_shift;
+                const int page = heads.page_table[(size_t)heads.seq_of[m] * heads.table_stride + (pos >> heads.page_shift)];
+                const int g2 = is_k ? hs - heads.nh : hs - heads.nh - heads.nkv;
+                dst = heads.pool + (size_t)page * heads.page_stride + (size_t)(pos & (page_size - 1)) * 64 +
+                      ((size_t)(is_k ? 0 : 1) * heads.nkv + g2) * page_size * 64;
+            }
+            mv_store4(dst + 4 * sub, v[0], v[1], v[2], v[3]);
+        }
+    } else
     {
         // An item is the tile's 128 rows for one token, four consecutive rows per lane (16-byte reads
         // through distributed shared memory, 16-byte stores).  A warp takes its items two at a time:
         // first every load of both (the slices' sums, and the old values where the product is added
         // to memory), then the arithmetic and the stores - so the round trips overlap.
-        constexpr int CH = 2, WARPS_ALL = THREADS / 32;
+        constexpr int CH = 2;
         const int r = 4 * lane, n = n0 + r;
         const bool vec_ok = n + 3 < N && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0;   // else one by one
         for (int m0 = slice + slices * warp; m0 < M; m0 += CH * slices * WARPS_ALL) {
@@ -281,19 +493,20 @@ int k_slices(int N, int K) {
     return slices < 1 ? 1 : slices;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int TAIL = 0>
 int launch(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-           const NormLink& link, int* err, cudaStream_t stream) {
-    using L = SwapLayout<BN, STAGES>;
+           const NormLink& link, const ConvTail& tail, const HeadTail& heads, const Ahead& ahead, int* err,
+           cudaStream_t stream, int slices) {
+    using L = SwapLayout<BN, STAGES, TAIL>;
     CUtensorMap mw, mx;
-    if (!tensor_map(W, N, K, BM, &mw) || !tensor_map(X, M, K, BN, &mx)) return (int)cudaErrorInvalidValue;
+    // TAIL 1: W has three times N rows (the B, C and x thirds), N counts channels
+    if (!tensor_map(W, TAIL == 1 ? 3 * N : N, K, BM, &mw) || !tensor_map(X, M, K, BN, &mx)) return (int)cudaErrorInvalidValue;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, STAGES, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         attr_set = true;
     }
     const int tiles = (N + BM - 1) / BM;
-    const int slices = k_slices(N, K);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(slices, tiles);
     cfg.blockDim = dim3(THREADS);
@@ -315,7 +528,8 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaLaunchKernelEx(&cfg, gemm_tc_swap_kernel<BN, STAGES>, mw, mx, bias, out, mode, M, N, K, ldo, link, err);
+    cudaLaunchKernelEx(&cfg, gemm_tc_swap_kernel<BN, STAGES, TAIL>, mw, mx, bias, out, mode, M, N, K, ldo, link, tail, heads,
+                       ahead, err);
     return mv_launch_status();
 }
 
@@ -327,7 +541,7 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
 MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
                            int K, int ldo, const float* scale_part, int n_scale_part, int scale_stride, int dim,
                            float eps, const float* emit_g, void* emit_x, float* emit_part, int emit_stride,
-                           int* err, cudaStream_t stream) {
+                           const void* next_w, long long next_bytes, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
@@ -351,9 +565,93 @@ MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void
     // A ring of 8 stages fills a multiprocessor's shared memory with one block.  Clusters of such
     // blocks need 8 free multiprocessors in one GPC each, and only 15 fit the GPU at a time: a
     // product that is cut along K takes 4 stages, so that two blocks share a multiprocessor.
-    const bool deep = k_slices(N, K) == 1;
-#define MV_GO(BN) return deep ? launch<BN, 8>(X, W, bias, out, mode, M, N, K, ldo, link, err, stream) \
-                              : launch<BN, 4>(X, W, bias, out, mode, M, N, K, ldo, link, err, stream)
+    const int slices = k_slices(N, K);
+    const bool deep = slices == 1;
+    const Ahead ahead = {next_w, next_bytes};
+#define MV_GO(BN) return deep ? launch<BN, 8>(X, W, bias, out, mode, M, N, K, ldo, link, ConvTail{}, HeadTail{}, ahead, err, stream, slices) \
+                              : launch<BN, 4>(X, W, bias, out, mode, M, N, K, ldo, link, ConvTail{}, HeadTail{}, ahead, err, stream, slices)
+    if (M <= 16) MV_GO(16);
+    if (M <= 32) MV_GO(32);
+    MV_GO(64);
+#undef MV_GO
+}
+
+namespace {
+NormLink scale_link(const float* scale_part, int n_scale_part, int scale_stride, int dim, float eps) {
+    NormLink link = {};
+    if (scale_part) {
+        link.scale_part = scale_part;
+        link.n_scale_part = n_scale_part;
+        link.scale_stride = scale_stride;
+        link.inv_dim = 1.0f / (float)dim;
+        link.eps = eps;
+    }
+    return link;
+}
+// slices of K for a product of ``tiles`` row tiles whose blocks are alone on a multiprocessor
+int k_slices_single(int tiles, int K) {
+    const int kblocks = (K + BK - 1) / BK;
+    int slices = 148 / (tiles < 1 ? 1 : tiles);
+    slices = slices >= 8 ? 8 : (slices >= 4 ? 4 : (slices >= 2 ? 2 : 1));
+    while (slices > 1 && kblocks / slices < 2) slices >>= 1;
+    return slices < 1 ? 1 : slices;
+}
+}  // namespace
+
+// A decode step's gated short convolution together with its input projection, for 1 <= M <= 64 rows
+// (one a sequence): [B | C | x] = X W^T (+ bias[3 H]) with W [3 H, K]; z[m, c] = C * (conv_bias + sum_j
+// taps[c][j] * value j of the sequence's kept B*x values followed by this token's); ``state``
+// [slots][k-1][H] is shifted and updated for slots[m].  ``z`` is bfloat16 [M, H].  scale_part etc. as
+// in mv_gemm_tc_swap.
+MV_API int mv_gemm_tc_swap_shortconv(const void* X, const void* W, const float* bias, const float* taps,
+                                     const float* conv_bias, float* state, const int* slots, void* z, int M, int H,
+                                     int K, int k, const float* scale_part, int n_scale_part, int scale_stride,
+                                     int dim, float eps, const void* next_w, long long next_bytes, int* err,
+                                     cudaStream_t stream) {
+    if (M <= 0 || H <= 0) return 0;
+    if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || k < 1 || k > 16 || !taps ||
+        (!state && k > 1) || !slots)
+        return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
+    const NormLink link = scale_link(scale_part, n_scale_part, scale_stride, dim, eps);
+    const ConvTail tail = {taps, conv_bias, state, slots, k};
+    const Ahead ahead = {next_w, next_bytes};
+    const int slices = k_slices_single((H + BM - 1) / BM, K);
+#define MV_GO(BN, ST) return launch<BN, ST, 1>(X, W, bias, z, 1, M, H, K, H, link, tail, HeadTail{}, ahead, err, stream, slices)
+    if (M <= 16) MV_GO(16, 4);
+    if (M <= 32) MV_GO(32, 4);
+    MV_GO(64, 3);
+#undef MV_GO
+}
+
+// The fused q/k/v projection of a step of 1 <= M <= 64 tokens together with the preparation of its heads
+// (head size 64, pairs (2i, 2i+1), bfloat16 cache): W [(nh + 2 nkv) 64, K].
+MV_API int mv_gemm_tc_swap_heads(const void* X, const void* W, const float* wq, const float* wk, float head_eps,
+                                 const float* inv_freq, const int* positions, const int* seq_of,
+                                 const int* page_table, int table_stride, int page_size, void* pool,
+                                 long long page_stride, void* q_out, int M, int nh, int nkv, int K,
+                                 const float* scale_part, int n_scale_part, int scale_stride, int dim, float eps,
+                                 const void* next_w, long long next_bytes, int* err, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || nh <= 0 || nkv <= 0 ||
+        (page_size & (page_size - 1)) || !positions || !seq_of || !page_table || !pool || !q_out ||
+        ((uintptr_t)q_out & 7) || ((uintptr_t)pool & 7))
+        return (int)cudaErrorInvalidValue;
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
+    const NormLink link = scale_link(scale_part, n_scale_part, scale_stride, dim, eps);
+    HeadTail heads = {};
+    heads.wq = wq; heads.wk = wk; heads.inv_freq = inv_freq; heads.positions = positions; heads.seq_of = seq_of;
+    heads.page_table = page_table; heads.pool = (__nv_bfloat16*)pool; heads.q_out = (__nv_bfloat16*)q_out;
+    heads.page_stride = page_stride; heads.eps = head_eps; heads.table_stride = table_stride;
+    heads.page_shift = 0;
+    while ((1 << heads.page_shift) < page_size) ++heads.page_shift;
+    heads.nh = nh; heads.nkv = nkv;
+    const int N = (nh + 2 * nkv) * 64;
+    const Ahead ahead = {next_w, next_bytes};
+    const int slices = k_slices(N, K);
+    const bool deep = slices == 1;
+#define MV_GO(BN) return deep ? launch<BN, 8, 2>(X, W, nullptr, q_out, 1, M, N, K, N, link, ConvTail{}, heads, ahead, err, stream, slices) \
+                              : launch<BN, 4, 2>(X, W, nullptr, q_out, 1, M, N, K, N, link, ConvTail{}, heads, ahead, err, stream, slices)
     if (M <= 16) MV_GO(16);
     if (M <= 32) MV_GO(32);
     MV_GO(64);

@@ -55,7 +55,11 @@ _SIGNATURES = {
                                   _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "mv_gemm_tc_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-        "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
+        "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P, _P],
+        "mv_gemm_tc_swap_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q,
+                                      _P, _P],
+        "mv_gemm_tc_swap_heads": [_P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
+                                  _P, _I, _I, _I, _F, _P, _Q, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
@@ -642,7 +646,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
 
 def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
                  accumulate: bool = False, swiglu: bool = False, scale: Optional[NormLink] = None,
-                 emit: Optional[NormLink] = None) -> torch.Tensor:
+                 emit: Optional[NormLink] = None, ahead: Optional[tuple] = None) -> torch.Tensor:
     """out = x @ w.T for at most 64 rows of x on the tcgen05 tensor cores with the
     operands' roles swapped (rows of w on the MMA's M side): a TMA pipeline that
     streams w once.  Same contract as ``gemm_small_m``."""
@@ -670,9 +674,74 @@ def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: O
     link = _link_args(x, M, N, K, mode, scale, emit, -(-N // 128))
     _check(_fn("bf16", "mv_gemm_tc_swap")(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, *link, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_swap")
+        out.data_ptr(), mode, M, N, K, ldo, *link, *(ahead or (None, 0)), _error_flag(x.device).data_ptr(), _stream()),
+        "mv_gemm_tc_swap")
     _account_gemm(x, w, out, accumulate)
     return out
+
+
+def gemm_tc_swap_shortconv(x: torch.Tensor, w_in: torch.Tensor, b_in: Optional[torch.Tensor], taps: torch.Tensor,
+                           b_conv: Optional[torch.Tensor], state: torch.Tensor, slots: torch.Tensor,
+                           out: torch.Tensor, *, scale: Optional[NormLink] = None,
+                           ahead: Optional[tuple] = None) -> torch.Tensor:
+    """``gemm_small_m_shortconv`` for up to 64 rows, on the tcgen05 kernel with swapped operands: a block
+    takes 128 channels and keeps the B, C and x rows of them in three accumulators."""
+    M, K = x.shape
+    H, k = taps.shape
+    if tuple(w_in.shape) != (3 * H, K):
+        raise KernelError(f"shortconv: in_proj weight is {tuple(w_in.shape)}, expected [{3 * H}, {K}]")
+    if x.dtype != torch.bfloat16 or w_in.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tc_swap_shortconv: operands must be bfloat16, got {x.dtype} and {w_in.dtype}")
+    if not 1 <= M <= SMALL_M_MAX or K % 8 or K < 8:
+        raise KernelError(f"gemm_tc_swap_shortconv: needs 1..{SMALL_M_MAX} rows and K a multiple of 8, got M={M}, K={K}")
+    if not 1 <= k <= MAX_CONV_K:
+        raise KernelError(f"shortconv: convolution width {k} is outside 1..{MAX_CONV_K}")
+    _need(state, "shortconv state", torch.float32)
+    if state.dim() != 3 or state.shape[1] != k - 1 or state.shape[2] != H:
+        raise KernelError(f"shortconv: state shape {tuple(state.shape)}, expected [slots, {k - 1}, {H}]")
+    if slots.numel() < M:
+        raise KernelError(f"shortconv: {slots.numel()} slots for {M} rows")
+    sp, n_sp, s_stride, dim, eps = _link_args(x, M, 3 * H, K, 1, scale, None, 0)[:5]
+    _check(_fn("bf16", "mv_gemm_tc_swap_shortconv")(
+        _need(x, "gemm x"), _need(w_in, "gemm w"), _need(b_in, "in_proj bias", torch.float32, (3 * H,), True),
+        _need(taps, "shortconv taps", torch.float32), _need(b_conv, "shortconv bias", torch.float32, (H,), True),
+        state.data_ptr(), _need(slots, "slots", torch.int32), _need(out, "shortconv out", torch.bfloat16, (M, H)),
+        M, H, K, k, sp, n_sp, s_stride, dim, eps, *(ahead or (None, 0)), _error_flag(x.device).data_ptr(), _stream()),
+        "mv_gemm_tc_swap_shortconv")
+    _account_gemm(x, w_in, out, False)
+    return out
+
+
+def gemm_tc_swap_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                       eps: float, inv_freq: Optional[torch.Tensor], positions, seq_of, page_table,
+                       pool: torch.Tensor, q_out: torch.Tensor, nh: int, nkv: int, *,
+                       scale: Optional[NormLink] = None, ahead: Optional[tuple] = None) -> torch.Tensor:
+    """``gemm_small_m_heads`` for up to 64 tokens, on the tcgen05 kernel with swapped operands (heads of 64,
+    the pairs (2i, 2i+1) only): a tile of 128 rows is two heads, a half-warp finishes one for a token."""
+    M, K = x.shape
+    hd = HEADS_FUSED_HEAD_DIM
+    if tuple(w_qkv.shape) != ((nh + 2 * nkv) * hd, K):
+        raise KernelError(f"gemm_tc_swap_heads: weight is {tuple(w_qkv.shape)}, expected "
+                          f"[{(nh + 2 * nkv) * hd}, {K}] ({nh} + 2 x {nkv} heads of {hd})")
+    if x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tc_swap_heads: operands and cache must be bfloat16, got {x.dtype}, "
+                          f"{w_qkv.dtype} and {pool.dtype}")
+    if not 1 <= M <= SMALL_M_MAX or K % 8 or K < 8:
+        raise KernelError(f"gemm_tc_swap_heads: needs 1..{SMALL_M_MAX} rows and K a multiple of 8, got M={M}, K={K}")
+    page_size = pool.shape[3]
+    _check_kv(pool, nkv, hd, page_size, "gemm_tc_swap_heads")
+    _need(page_table, "page table", torch.int32)
+    sp, n_sp, s_stride, dim, eps_norm = _link_args(x, M, (nh + 2 * nkv) * hd, K, 1, scale, None, 0)[:5]
+    _check(_fn("bf16", "mv_gemm_tc_swap_heads")(
+        _need(x, "gemm x"), _need(w_qkv, "gemm w"), _need(wq, "q norm weight", torch.float32, (hd,), True),
+        _need(wk, "k norm weight", torch.float32, (hd,), True), float(eps),
+        _need(inv_freq, "inv_freq", torch.float32, (hd // 2,), True),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        page_table.data_ptr(), page_table.shape[1], page_size, _need(pool, "cache pool"), pool.stride(0),
+        _need(q_out, "q out", torch.bfloat16, (M, nh * hd)), M, nh, nkv, K, sp, n_sp, s_stride, dim, eps_norm,
+        *(ahead or (None, 0)), _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_swap_heads")
+    _account_gemm(x, w_qkv, q_out, False)
+    return q_out
 
 
 def shortconv(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,

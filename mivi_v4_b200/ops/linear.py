@@ -90,7 +90,7 @@ def _ahead(w: torch.Tensor, fn) -> dict:
     if _order is None:
         return {}
     nxt = _order.next_after(w)
-    return {"ahead": nxt} if nxt is not None and fn is K.gemm_small_m else {}
+    return {"ahead": nxt} if nxt is not None and (fn is K.gemm_small_m or fn is K.gemm_tc_swap) else {}
 
 
 def _small_m(m: int):
@@ -122,6 +122,13 @@ def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bflo
 
 
 _FUSED_CONV = os.environ.get("MIVI_FUSED_CONV", "1") != "0"
+# From 9 rows on the fused kernel exists too (``kernels.gemm_tc_swap_shortconv``: three accumulators a block
+# of 128 channels) but measured slower than the two kernels it replaces (decode steps of 64 sequences of
+# the 1.2B-parameter shape: 1.29 ms with it, 1.20 with its K cut in 4 instead of 8, 1.12 without): a block
+# holds 168 KB of shared memory, so one runs per multiprocessor and its phases (load, move the three
+# accumulators to shared memory, add the slices, convolve) do not overlap with another block's.
+# MIVI_FUSED_CONV_TC=1 turns it on.
+_FUSED_CONV_TC = os.environ.get("MIVI_FUSED_CONV_TC", "0") == "1"
 
 
 def shortconv_decode_fused_ok(n_rows: int, x: torch.Tensor, w_in: torch.Tensor) -> bool:
@@ -129,30 +136,37 @@ def shortconv_decode_fused_ok(n_rows: int, x: torch.Tensor, w_in: torch.Tensor) 
     projection (``kernels.gemm_small_m_shortconv``): the steps whose products take the
     register-streaming kernel, bfloat16 operands.  One launch less a layer; MIVI_FUSED_CONV=0
     keeps the two kernels."""
-    return (_FUSED_CONV and not K.DEBUG_CHECKS and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
-            and tensor_core_ok(x, w_in))
+    return (_FUSED_CONV and not K.DEBUG_CHECKS and 1 <= n_rows <= K.SMALL_M_MAX and tensor_core_ok(x, w_in)
+            and (n_rows <= K.SHORTCONV_FUSED_MAX_ROWS if _small_m(n_rows) is K.gemm_small_m else _FUSED_CONV_TC))
 
 
 def linear_shortconv_decode(x: torch.Tensor, w_in: torch.Tensor, b_in, taps, b_conv, state, slots, out, *,
                             scale: Optional[K.NormLink] = None) -> torch.Tensor:
-    """The input projection and the convolution of a decode step in one kernel; needs
-    ``shortconv_decode_fused_ok``."""
+    """The input projection and the convolution of a decode step in one kernel (the register-streaming
+    one up to 8 rows, the tcgen05 one from there to 64); needs ``shortconv_decode_fused_ok``."""
     ahead = {}
     if _order is not None:
         nxt = _order.next_after(w_in)
         ahead = {"ahead": nxt} if nxt is not None else {}
-    return K.gemm_small_m_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
+    fn = K.gemm_tc_swap_shortconv if _small_m(x.shape[0]) is K.gemm_tc_swap else K.gemm_small_m_shortconv
+    return fn(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
 
 
 _FUSED_QK = os.environ.get("MIVI_FUSED_QK", "1") != "0"
 
 
-def heads_fused_ok(n_rows: int, x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int, pool: torch.Tensor) -> bool:
+def heads_fused_ok(n_rows: int, x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int, pool: torch.Tensor,
+                   half_split: bool = False) -> bool:
     """Whether the preparation of q, k and v (per-head norm, rotation, append to the cache) can run
-    as the epilogue of their projection (``kernels.gemm_small_m_heads``): steps whose products take
-    the register-streaming kernel, heads of 64, bfloat16 cache.  MIVI_FUSED_QK=0 keeps the two kernels."""
-    return (_FUSED_QK and not K.DEBUG_CHECKS and _DECODE_GEMM != "tc" and 1 <= n_rows <= min(MMA_MAX_ROWS, K.SHORTCONV_FUSED_MAX_ROWS)
-            and head_dim == K.HEADS_FUSED_HEAD_DIM and pool.dtype == torch.bfloat16 and tensor_core_ok(x, w_qkv))
+    as the epilogue of their projection (``kernels.gemm_small_m_heads`` up to 8 rows,
+    ``kernels.gemm_tc_swap_heads`` from there to 64, which pairs the elements (2i, 2i+1) only): heads of 64,
+    bfloat16 cache.  MIVI_FUSED_QK=0 keeps the two kernels."""
+    if not (_FUSED_QK and not K.DEBUG_CHECKS and 1 <= n_rows <= K.SMALL_M_MAX and head_dim == K.HEADS_FUSED_HEAD_DIM
+            and pool.dtype == torch.bfloat16 and tensor_core_ok(x, w_qkv)):
+        return False
+    if _small_m(n_rows) is K.gemm_tc_swap:
+        return not half_split
+    return n_rows <= K.SHORTCONV_FUSED_MAX_ROWS
 
 
 def linear_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq, wk, eps: float, inv_freq, half_split: bool, positions,
@@ -162,6 +176,9 @@ def linear_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq, wk, eps: float, inv_f
     if _order is not None:
         nxt = _order.next_after(w_qkv)
         ahead = {"ahead": nxt} if nxt is not None else {}
+    if _small_m(x.shape[0]) is K.gemm_tc_swap:
+        return K.gemm_tc_swap_heads(x, w_qkv, wq, wk, eps, inv_freq, positions, seq_of, page_table, pool, q_out, nh,
+                                    nkv, scale=scale, **ahead)
     return K.gemm_small_m_heads(x, w_qkv, wq, wk, eps, inv_freq, half_split, positions, seq_of, page_table, pool,
                                 q_out, nh, nkv, scale=scale, **ahead)
 

@@ -136,7 +136,7 @@ class GroupedQueryAttention(Part):
         rot = self.position.rotary(u.device)
         inv_freq, half_split = rot if rot is not None else (None, False)
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
-        if not self.shared_kv and heads_fused_ok(N, u, self.w_qkv, hd, view.pool):
+        if not self.shared_kv and heads_fused_ok(N, u, self.w_qkv, hd, view.pool, half_split):
             # a few tokens: norm, rotation and the append to the cache are the projection's epilogue
             linear_heads(u, self.w_qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
                          step.seq_of, view.page_table, view.pool, q, nh, nkv, scale=scale)

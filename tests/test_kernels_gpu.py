@@ -589,21 +589,26 @@ def test_shortconv_long_steps(out_dtype, H, k, bias):
             assert torch.allclose(torch.cat(a).double().cpu(), b_, rtol=tol, atol=tol), cuts
 
 
-@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("kernel,M", [("mma", 1), ("mma", 3), ("mma", 8), ("tc", 1), ("tc", 8), ("tc", 9), ("tc", 20),
+                                      ("tc", 33), ("tc", 64)])
 @pytest.mark.parametrize("H,Kd,k,bias,scaled", [(16, 8, 3, False, False), (200, 72, 4, True, True), (40, 2048, 1, True, False),
-                                                (2048, 2048, 3, False, True), (24, 8200, 7, False, False)])
-def test_gemm_small_m_shortconv(M, H, Kd, k, bias, scaled):
-    """The decode step's convolution as the epilogue of its input projection: several steps in a
+                                                (2048, 2048, 3, False, True), (24, 8200, 7, False, False),
+                                                (300, 264, 2, True, True)])
+def test_gemm_small_m_shortconv(kernel, M, H, Kd, k, bias, scaled):
+    """The decode step's convolution as the epilogue of its input projection (the register-streaming
+    kernel up to 8 rows, the tcgen05 kernel with three accumulators up to 64): several steps in a
     row over slots in any order, against a float64 expression and against the two separate kernels
     (same outputs within rounding, same kind of state)."""
     from mivi_v4_b200.ops.kernels import NormLink
+    fused = K().gemm_small_m_shortconv if kernel == "mma" else K().gemm_tc_swap_shortconv
     g = torch.Generator().manual_seed(H + Kd + k + M)
     w_in = (torch.randn(3 * H, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16).to(DEV)
     taps = torch.randn(H, k, generator=g).to(DEV)
     b_in = torch.randn(3 * H, generator=g).to(DEV) if bias else None
     b_conv = torch.randn(H, generator=g).to(DEV) if bias else None
-    slots = ints([5, 0, 7, 2, 1, 6, 3, 4][:M])
-    state = torch.zeros(9, k - 1, H, device=DEV)
+    n_slots = M + 3
+    slots = ints(torch.randperm(n_slots, generator=g).tolist()[:M])
+    state = torch.zeros(n_slots, k - 1, H, device=DEV)
     state_two = torch.zeros_like(state)
     hist = torch.zeros(M, k - 1, H, dtype=torch.float64)           # the plain side's kept values of B * x
     n_part = 3
@@ -631,36 +636,41 @@ def test_gemm_small_m_shortconv(M, H, Kd, k, bias, scaled):
         hist = torch.cat([hist[:, 1:], bx[:, None]], dim=1) if k > 1 else hist
 
         out = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
-        K().gemm_small_m_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=link)
+        fused(x, w_in, b_in, taps, b_conv, state, slots, out, scale=link)
+        K().check_device_errors()
         tol = dict(rtol=2e-2, atol=2e-2 * float(want.abs().max()))
         assert torch.allclose(out.double().cpu(), want, **tol), step
         # the separate kernels
         p32 = torch.empty(M, 3 * H, device=DEV)
-        K().gemm_small_m(x, w_in, p32, bias=b_in, scale=link)
+        (K().gemm_small_m if kernel == "mma" else K().gemm_tc_swap)(x, w_in, p32, bias=b_in, scale=link)
         out_two = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
         K().shortconv(p32, taps, b_conv, state_two, None, None, None, slots, None, None, out_two, M, decode=True)
         assert torch.allclose(out.float(), out_two.float(), rtol=2e-2, atol=2e-2 * float(want.abs().max())), step
         if k > 1:
             assert torch.allclose(state, state_two, rtol=1e-4, atol=1e-4 * float(bx.abs().max())), step
             assert torch.allclose(state[slots.long()].double().cpu(), hist, rtol=1e-3, atol=1e-3 * float(bx.abs().max()))
-    untouched = [s for s in range(9) if s not in slots.tolist()]
+    untouched = [s for s in range(n_slots) if s not in slots.tolist()]
     assert not state[untouched].any()                               # other sequences' state is left alone
 
 
-@pytest.mark.parametrize("style", ["interleaved", "half_split"])
+@pytest.mark.parametrize("kernel,style,M", [("mma", "interleaved", 7), ("mma", "half_split", 7), ("tc", "interleaved", 7),
+                                            ("tc", "interleaved", 9), ("tc", "interleaved", 40), ("tc", "interleaved", 64)])
 @pytest.mark.parametrize("nh,nkv,Kd,eps,theta,normed,scaled", [
     (4, 2, 64, 1e-5, 1e4, True, False), (3, 1, 200, 1e-6, 1e6, True, True), (5, 5, 2048, 1e-5, 5e4, False, False),
     (32, 8, 2048, 1e-5, 1e6, True, True), (2, 2, 8200, 1e-5, 1e6, True, False)])
-def test_gemm_small_m_heads(style, nh, nkv, Kd, eps, theta, normed, scaled):
-    """Norm, rotation and append as the epilogue of the q/k/v projection (heads of 64): against the
-    plain expressions on a float64 product, and against the two separate kernels."""
+def test_gemm_small_m_heads(kernel, style, M, nh, nkv, Kd, eps, theta, normed, scaled):
+    """Norm, rotation and append as the epilogue of the q/k/v projection (heads of 64; the register-streaming
+    kernel up to 8 tokens, the tcgen05 kernel, two heads a tile, up to 64): against the plain expressions on a
+    float64 product, and against the two separate kernels."""
     from mivi_v4_b200.ops.kernels import NormLink
     hd, page = 64, 16
     pool = torch.zeros(8, 2, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
     pool_two = torch.zeros_like(pool)
     table = ints([[3, 5, 1], [6, 0, 0], [2, 7, 4]])
     toks = [(0, p) for p in (0, 15, 16, 39)] + [(1, 6), (2, 47), (2, 31)]
-    M = len(toks)
+    # more tokens: further positions of the three sequences, each (sequence, position) once
+    more = [(b, p) for p in range(48) for b in (0, 2) if (b, p) not in toks] + [(1, p) for p in range(16) if p != 6]
+    toks = (toks + more)[:M]
     x = rnd(M, Kd, dtype=torch.bfloat16)
     w = (rnd((nh + 2 * nkv) * hd, Kd, seed=1) * (2.0 / math.sqrt(Kd))).to(torch.bfloat16)
     wq, wk = (rnd(hd) + 1.0, rnd(hd, seed=1) + 1.0) if normed else (None, None)
@@ -675,8 +685,12 @@ def test_gemm_small_m_heads(style, nh, nkv, Kd, eps, theta, normed, scaled):
         qkv = qkv * (1.0 / torch.sqrt(parts[:, :4].double().sum(1) / Kd + 1e-5))[:, None]
     qkv = qkv.cpu()
     q_out = torch.empty(M, nh * hd, dtype=torch.bfloat16, device=DEV)
-    K().gemm_small_m_heads(x, w, wq, wk, eps, inv_d, style == "half_split", positions, seq_of, table, pool, q_out,
-                           nh, nkv, scale=link)
+    if kernel == "mma":
+        K().gemm_small_m_heads(x, w, wq, wk, eps, inv_d, style == "half_split", positions, seq_of, table, pool, q_out,
+                               nh, nkv, scale=link)
+    else:
+        K().gemm_tc_swap_heads(x, w, wq, wk, eps, inv_d, positions, seq_of, table, pool, q_out, nh, nkv, scale=link)
+    K().check_device_errors()
     pos = torch.tensor([p for _, p in toks])
     qh, kh = qkv[:, :nh * hd].reshape(-1, nh, hd), qkv[:, nh * hd:(nh + nkv) * hd].reshape(-1, nkv, hd)
     if normed:
@@ -693,7 +707,7 @@ def test_gemm_small_m_heads(style, nh, nkv, Kd, eps, theta, normed, scaled):
     assert int((pool != 0).sum()) <= M * 2 * nkv * hd     # nothing was written anywhere else
     # the separate kernels
     p32 = torch.empty(M, (nh + 2 * nkv) * hd, device=DEV)
-    K().gemm_small_m(x, w, p32, scale=link)
+    (K().gemm_small_m if kernel == "mma" else K().gemm_tc_swap)(x, w, p32, scale=link)
     q_two = torch.empty_like(q_out)
     K().qk_prepare(p32, wq, wk, eps, inv_d, style == "half_split", positions, seq_of, table, pool_two, q_two, nh, nkv, hd)
     assert torch.allclose(q_out.float(), q_two.float(), rtol=2e-2, atol=tol["atol"])
