@@ -272,6 +272,11 @@ def main() -> int:
                     help="run one of the two further workloads instead of the default benchmark")
     ap.add_argument("--stages", default=None, choices=["decode", "prefill"],
                     help="print where the time of a decode step (of --batch sequences) or of the prefill goes")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT,
+                    help="with --stages decode: tokens that each sequence holds before the profiled steps")
+    ap.add_argument("--replayed", action="store_true",
+                    help="with --stages: the kernels of the step as replayed from its recording (activity records), "
+                         "instead of launch by launch with stages")
     ap.add_argument("--kernel", default=None, help="time one kernel alone (see --m/--n/--k, --context, --tokens)")
     for name, default in (("m", 8), ("n", 16384), ("k", 2048), ("context", 520), ("tokens", PREFILL_TOKENS),
                           ("heads", 32), ("kv-heads", 8), ("head-dim", 64), ("vocab", 65536), ("reps", 20)):
@@ -319,7 +324,12 @@ def main() -> int:
     nums = measure.model_numbers(model)
     pk, pk_src = peaks()
     if args.stages:
-        lens = [PREFILL_TOKENS] if args.stages == "prefill" else [PROMPT] * args.batch
+        lens = [PREFILL_TOKENS] if args.stages == "prefill" else [args.prompt_len] * args.batch
+        if args.replayed:
+            rep = measure.replayed_kernels(model, lens, prefill=args.stages == "prefill")
+            measure.print_replayed_kernels(rep, f"{args.stages} step as the engine runs it, {len(lens)} sequence(s) of "
+                                                f"{lens[0]} tokens, LFM2.5-1.2B shape")
+            return 0
         rep = measure.stage_report(model, lens, prefill=args.stages == "prefill")
         measure.print_stage_report(rep, f"{args.stages} step, {len(lens)} sequence(s) of {lens[0]} tokens, LFM2.5-1.2B shape", pk)
         return 0

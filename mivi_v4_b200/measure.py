@@ -190,6 +190,61 @@ def stage_report(model, prompt_lens: Sequence[int], steps: int = 8, prefill: boo
     return eng.profile_report()
 
 
+def replayed_kernels(model, prompt_lens: Sequence[int], prefill: bool = False, seed: int = 3) -> dict:
+    """Kernel by kernel, how long one decode step took while it was REPLAYED from its recording (or, with
+    ``prefill``, the prefill step as the engine launches it): from the CUDA activity records of the step
+    (torch.profiler), so the kernels overlap as they do in service and none is serialised by a profiler.
+    {"span_us", "kernels", "rows": [{kernel, calls, us, share}]}."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from .engine import Engine
+    B = len(prompt_lens)
+    room = sum(-(-(n + 24) // 64) * 64 for n in prompt_lens)
+    eng = Engine(model, max_tokens=2 * room, max_batch=B, max_step_tokens=max(8192, max(prompt_lens)))
+    prompts = random_prompts(model.vocab_size, prompt_lens, seed)
+    slots = [eng.open() for _ in range(B)]
+    eng.step(list(zip(slots, prompts)), "last", copy=False)
+    n_steps = 1 if prefill else 3
+    if prefill:
+        for s in slots:
+            eng.close(s)
+        slots = [eng.open() for _ in range(B)]
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            eng.step(list(zip(slots, prompts)), "last", copy=False)
+            torch.cuda.synchronize()
+    else:
+        for i in range(6):
+            eng.step([(s, [i + 3]) for s in slots], "last", copy=False)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(n_steps):
+                eng.step([(s, [i + 30]) for s in slots], "last", copy=False)
+            torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()]
+    ev.sort(key=lambda e: e.time_range.start)
+    n = len(ev) // n_steps
+    last = ev[-n:]
+    agg: Dict[str, list] = {}
+    for e in last:
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+        t = agg.setdefault(name, [0.0, 0])
+        t[0] += e.time_range.end - e.time_range.start
+        t[1] += 1
+    span = last[-1].time_range.end - last[0].time_range.start
+    rows = [dict(kernel=k, calls=c, us=t, share=t / span) for k, (t, c) in sorted(agg.items(), key=lambda kv: -kv[1][0])]
+    return dict(span_us=span, kernels=n, rows=rows)
+
+
+def print_replayed_kernels(rep: dict, title: str, file=None) -> None:
+    print(f"{title}: {rep['kernels']} kernels, {rep['span_us']:.0f} us from the first one's start to the last one's end",
+          file=file)
+    for r in rep["rows"]:
+        print(f"  {r['us']:8.1f} us  {100 * r['share']:5.1f} %  {r['calls']:3d} x {r['us'] / r['calls']:6.1f} us  {r['kernel']}",
+              file=file)
+
+
 def print_stage_report(rep: dict, title: str, peaks: Optional[dict] = None, file=None) -> None:
     steps = max(rep["steps"], 1)
     print(f"{title}: {rep['total_us'] / steps:.0f} us a step over {steps} step(s), launch by launch", file=file)
@@ -239,6 +294,17 @@ def kernel_run(kernel: str, *, m: int = 8, n: int = 16384, k: int = 2048, swiglu
     dev = "cuda:0"
     torch.manual_seed(0)
     res: dict = dict(kernel=kernel)
+    if kernel == "reference_matmul":
+        # not a kernel of this library: torch.matmul (cuBLAS) on the same operands in the same harness, as the
+        # yardstick for the products above; it is on no path of the library
+        copies = max(2, min(64, (1 << 30) // (n * k * 2)))
+        ws = [(torch.randn(n, k, device=dev) * 0.05).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        torch.matmul(x, ws[0].T, out=out)
+        us = _replayed_us([lambda w=w: torch.matmul(x, w.T, out=out) for w in ws], reps)
+        res.update(m=m, n=n, k=k, us=us, weights_gb_per_s=n * k * 2 / us / 1e3, tflops=2.0 * m * n * k / us / 1e6)
+        return res
     if kernel.startswith("gemm"):
         fn = getattr(K, kernel)
         copies = max(2, min(64, (1 << 30) // (n * k * 2)))           # about 1 GB of weights in rotation
@@ -329,4 +395,4 @@ def kernel_run(kernel: str, *, m: int = 8, n: int = 16384, k: int = 2048, swiglu
 
 
 KERNELS = ("gemm_small_m", "gemm_tc_swap", "gemm_tc", "attention_decode", "attention_decode_tc", "attention_prefill",
-           "attention_prefill_tc", "sample")
+           "attention_prefill_tc", "sample", "reference_matmul")
