@@ -144,15 +144,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (unsigned)i; };
 
-    // which sequence and which pair of tiles of it; heavy (late) pairs first
-    int b = 0, pair = (int)(gridDim.x - 1 - blockIdx.x);
+    // which sequence and which pair of tiles of it.  Blocks are handed out heads first, then pairs, and the
+    // heavy (late) pairs come first: every head's longest pair starts in the first wave and the short ones fill
+    // the gaps at the end (longest job first), instead of a head's long pairs starting when the grid is nearly done
+    int b = 0, pair = (int)(gridDim.y - 1 - blockIdx.y);
     for (; b < B; ++b) {
         const int pairs = (cu[b + 1] - cu[b] + TILES * BQ - 1) / (TILES * BQ);
         if (pair < pairs) break;
         pair -= pairs;
     }
     if (b >= B) return;
-    const int h = blockIdx.y, g = h / (nh / nkv);
+    const int h = blockIdx.x, g = h / (nh / nkv);
     const int row0 = cu[b] + pair * TILES * BQ;
     const int nq = min(TILES * BQ, cu[b + 1] - row0);
     const int pos0 = starts[b] + pair * TILES * BQ;
@@ -381,7 +383,8 @@ MV_API int mv_attention_prefill_tc(const void* q, const void* pool, long long po
         cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
         attr_set = true;
     }
-    dim3 grid((N + TILES * BQ - 1) / (TILES * BQ) + B, nh);
+    dim3 grid(nh, (N + TILES * BQ - 1) / (TILES * BQ) + B);
+    if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
     // a plain launch, not a programmatic one (see attention_decode_tc.cu); the kernel after it still
     // starts under this one's tail
     attention_prefill_tc_kernel<<<grid, AT_THREADS, AT_SMEM, stream>>>(

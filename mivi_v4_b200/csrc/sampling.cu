@@ -530,8 +530,11 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
               float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
               float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
               unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
-              int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out) {
+              int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out,
+              const int* __restrict__ flag_src, int* __restrict__ flag_dst) {
     mv_pdl_begin();
+    // a word that travels with the tokens: the device's error flag as the step before this kernel left it
+    if (flag_dst && blockIdx.x == 0 && threadIdx.x == 0) *flag_dst = *flag_src;
     __shared__ Shared sh;
     extern __shared__ float tiles[];
     sample_row(logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen, pres_pen, freq_pen, recent, n_recent,
@@ -723,8 +726,10 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __r
                       float temperature, int top_k, float top_p, float min_p, float rep_pen, float pres_pen,
                       float freq_pen, const int* __restrict__ recent, const int* __restrict__ n_recent,
                       unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps,
-                      int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out) {
+                      int* __restrict__ ring, const int* __restrict__ ring_row, int* __restrict__ out,
+                      const int* __restrict__ flag_src, int* __restrict__ flag_dst) {
     mv_pdl_begin();
+    if (flag_dst && blockIdx.x == 0 && threadIdx.x == 0) *flag_dst = *flag_src;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ Shared sh;
     __shared__ ClusterShared cs;
@@ -894,8 +899,10 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, float* __r
 MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int V, float temperature,
                      int top_k, float top_p, float min_p, float rep_pen, float pres_pen, float freq_pen,
                      const int* recent, const int* n_recent, unsigned long long seed, const int* streams,
-                     const int* steps, int* ring, const int* ring_row, int* out, cudaStream_t stream) {
+                     const int* steps, int* ring, const int* ring_row, int* out, const int* flag_src, int* flag_dst,
+                     cudaStream_t stream) {
     if (B <= 0) return 0;
+    if (!flag_src) flag_dst = nullptr;
     constexpr size_t TILES = (size_t)(THREADS / 32) * 32 * 33 * sizeof(float);   // a 32 x 33 tile a warp
     static bool attr_set = false;
     if (!attr_set) {
@@ -937,10 +944,11 @@ MV_API int mv_sample(const float* logits, long long ld, float* work, int B, int 
         cfg.attrs = attr;
         cfg.numAttrs = na;
         cudaLaunchKernelEx(&cfg, kernel, logits, ld, work, V, temperature, top_k, top_p, min_p, rep_pen,
-                           pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out);
+                           pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out, flag_src,
+                           flag_dst);
         return mv_launch_status();
     }
     mv_launch(sample_kernel, B, THREADS, TILES, stream, logits, ld, work, V, temperature, top_k, top_p, min_p,
-              rep_pen, pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out);
+              rep_pen, pres_pen, freq_pen, recent, n_recent, seed, streams, steps, ring, ring_row, out, flag_src, flag_dst);
     return mv_launch_status();
 }

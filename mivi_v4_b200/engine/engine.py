@@ -107,7 +107,8 @@ class Engine:
         return self.cache.length(slot)
 
     def graph_keys(self) -> List[tuple]:
-        """The decode-step shapes recorded so far: (sequences, ((cache group, page-table width), ...))."""
+        """The decode-step shapes recorded so far: (sequences, ((cache group, page-table width), ...), whether
+        the recording ends with the copy of the error flag)."""
         return list(self._graphs)
 
     def check_errors(self) -> None:
@@ -288,11 +289,13 @@ class Engine:
         return self._decode(slots, toks, None)
 
     def _decode(self, slots: np.ndarray, toks: Optional[np.ndarray],
-                device_tokens: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+                device_tokens: Optional[torch.Tensor], note_errors: bool = True) -> Optional[torch.Tensor]:
         """One more token for each of ``slots`` (an array that names each slot once is checked here),
         the token ids from the host (``toks``) or from the device (``device_tokens``, int32).  Works on
         arrays over the sequences; the only per-sequence work is a new page when one crosses a page's
-        end.  Returns None, with nothing touched, if the step cannot run as it stands."""
+        end.  Returns None, with nothing touched, if the step cannot run as it stands.  ``note_errors``:
+        the step ends with the copy of the device's error flag to the host; a caller whose next launch
+        carries the flag itself (the sampling kernel, with the tokens) saves the copy."""
         cache = self.cache
         B = int(slots.size)
         if not cache.are_assigned(slots) or (B > 1 and np.unique(slots).size != B):
@@ -312,7 +315,7 @@ class Engine:
                     cache.reserve(s, 1)
             width = _width_for(int(blocks.max()))
             widths = tuple((g, width) for g in cache.kv_groups)
-        key = (B, widths)
+        key = (B, widths, bool(note_errors))
         rec = self._graphs.get(key)
         if rec is not None and rec.generation != self._gws.generation:
             del self._graphs[key]                         # recorded over buffers that have moved since
@@ -371,7 +374,8 @@ class Engine:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, pool=self._graph_pool), L.looking_ahead(order, self.model.weight_extents()):
             captured = self.model.forward(ctx, self.cache)
-            K.note_device_errors(self.device)
+            if key[2]:
+                K.note_device_errors(self.device)
         n_kernels = K.launch_count() - n0
         K.add_launches(-n_kernels)                        # recorded, not run
         if captured.data_ptr() != logits.data_ptr() or gws.generation != settled:
@@ -383,7 +387,8 @@ class Engine:
         self.h2d_bytes += ctx.h2d_bytes
         return logits
 
-    def decode_from_device(self, slots: Sequence[int], device_tokens: torch.Tensor) -> Optional[torch.Tensor]:
+    def decode_from_device(self, slots: Sequence[int], device_tokens: torch.Tensor,
+                           note_errors: bool = True) -> Optional[torch.Tensor]:
         """One more token for each of ``slots``, the token ids being ``device_tokens`` (int32 [len(slots)],
         on the device, e.g. what the sampling kernel just wrote): the step is enqueued without the host
         waiting for them.  Returns the logits of all, or None if the step cannot run now (no room in the
@@ -395,7 +400,7 @@ class Engine:
             arr = np.asarray(slots, dtype=np.int64)
         except (TypeError, ValueError):
             return None
-        return self._decode(arr, None, device_tokens)
+        return self._decode(arr, None, device_tokens, note_errors)
 
     # ---- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 256,
@@ -463,15 +468,21 @@ class _EngineBackend:
                 picks = [i for i, _ in goers]
                 src = out_dev if picks == list(range(out_dev.numel())) else \
                     out_dev[torch.tensor(picks, device=out_dev.device)]
-                nxt = eng.decode_from_device([r.handle for _, r in goers], src)
+                # the sampling kernel after it carries the error flag to the host with the tokens
+                nxt = eng.decode_from_device([r.handle for _, r in goers], src, note_errors=False)
                 if nxt is not None:
-                    out2 = sampler.launch(nxt, [r.index for _, r in goers], [len(r.output) + 1 for _, r in goers],
-                                          [[] for _ in goers], slot=1 - cur, states=[r.handle for _, r in goers])
+                    with K.profiling(eng.profile), K.profile_stage("sampling"):
+                        out2 = sampler.launch(nxt, [r.index for _, r in goers], [len(r.output) + 1 for _, r in goers],
+                                              [[] for _ in goers], slot=1 - cur, states=[r.handle for _, r in goers],
+                                              carry_flag=True)
                     host2, event2 = sampler.read_async(out2, slot=1 - cur)
                     self._early = dict(handles=[r.handle for _, r in goers], out=out2, host=host2, event=event2,
                                        set=1 - cur)
         event.synchronize()
-        eng.check_errors()                       # exact here: the flag's copy was enqueued before the tokens'
+        code = sampler.flag(cur)                 # the flag as this step's sampling kernel saw it, if it carried it
+        if code:
+            K.raise_device_error(eng.device, code)
+        eng.check_errors()                       # and the copy that steps of the step function end with
         tokens = host.tolist()
         result = [tokens[i] for i in rows]
         self._last = dict(zip(handles, result))

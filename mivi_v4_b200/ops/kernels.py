@@ -45,7 +45,7 @@ _SIGNATURES = {
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
                                 _I, _I, _P],
-        "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P],
+        "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
         "mv_gemm_small_m": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P],
@@ -581,6 +581,18 @@ def raise_seen_device_errors(device) -> None:
         raise KernelError(_error_text(key, code))
 
 
+def raise_device_error(device, code: int) -> None:
+    """A kernel's fault arrived on the host by another way than the mirror (with the sampled tokens):
+    clear the flag and raise."""
+    key = torch.device(device).index or 0
+    torch.cuda.synchronize(device)
+    _error_flag(device).zero_()
+    torch.cuda.synchronize(device)
+    if key in _error_mirrors:
+        _error_mirrors[key].zero_()
+    raise KernelError(_error_text(key, int(code)))
+
+
 def check_device_errors() -> None:
     """Raise if a kernel reported a fault (synchronises the device)."""
     for key, flag in _error_flags.items():
@@ -1040,12 +1052,15 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
            presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
            recent: Optional[torch.Tensor] = None, n_recent: Optional[torch.Tensor] = None, seed: int = 0,
            streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None,
-           ring: Optional[torch.Tensor] = None, ring_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+           ring: Optional[torch.Tensor] = None, ring_rows: Optional[torch.Tensor] = None,
+           flag_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of ``logits`` [B, V] (float32, rows may be strided).  ``work``: scratch of
     ``sample_scratch_width(V)`` floats a row.  The recent tokens that the penalties look at come
     either from the caller (``recent`` [B, 64], ``n_recent``) or from ``ring`` [states, 128], which the
     kernel keeps itself: row b uses state ``ring_rows[b]``, looks at the places of its last
-    min(steps[b], 64) steps and writes the token it samples to place steps[b] mod 128."""
+    min(steps[b], 64) steps and writes the token it samples to place steps[b] mod 128.
+    ``flag_to`` (int32 [1] on the device): the kernel also copies the device's error flag there, so
+    that it reaches the host with the tokens."""
     B, V = logits.shape
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 on a CUDA device with unit column stride")
@@ -1065,6 +1080,8 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
         _need(streams, "streams", torch.int32, (B,), True), _need(steps, "steps", torch.int32, (B,), True),
         _need(ring, "recent ring", torch.int32, (None, RECENT_RING), True),
         _need(ring_rows, "ring rows", torch.int32, (B,), ring is None),
-        _need(out, "sample out", torch.int32, (B,)), _stream()), "mv_sample")
+        _need(out, "sample out", torch.int32, (B,)),
+        _error_flag(logits.device).data_ptr() if flag_to is not None else None,
+        _need(flag_to, "flag copy", torch.int32, (1,), True), _stream()), "mv_sample")
     account(B * V * 4)
     return out
