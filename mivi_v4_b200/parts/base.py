@@ -6,9 +6,10 @@ Interfaces by role (``step`` is an engine.step.StepContext, ``resid`` the
 
 norm          forward(x_f32[N, dim], out_dtype, step, rows=None) -> [n, dim]
 position      rotary() -> (inv_freq f32[hd/2], style) or None
-mixer         cache_need() -> KVNeed | StateNeed | None
-              forward(u[N, hidden], resid, step, cache_view) -> None
-feed_forward  forward(g[N, hidden], resid, step) -> None
+mixer         cache_need() -> KVNeed | StateNeed | None | a list of those
+              forward(u[N, hidden], resid, step, cache_view) -> None   (a list of views for a list of needs)
+feed_forward  forward(g[N, hidden], resid, step) -> None; one that overrides cache_need() is also passed
+              view=<its view or list of views>
 block         cache_need(); forward(resid, step, cache_view) -> None
 embedding     forward(step) -> resid f32[N, hidden]
 head          forward(f[n, hidden], step, embedding) -> logits f32[n, vocab]
@@ -28,6 +29,10 @@ class Part:
     # on the step's host-side lists: a model with such a part runs its decode steps launch by launch
     # instead of replaying a recorded CUDA graph.
     graph_safe = True
+
+    def cache_need(self):
+        """What this part keeps per sequence between steps: None, a KVNeed, a StateNeed, or a list of those."""
+        return None
 
     def carries_norm(self, step):
         """(accepts, emits): whether, in this step, the part's first product can take rows that still

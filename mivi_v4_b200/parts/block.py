@@ -22,7 +22,18 @@ class PreNormBlock(Part):
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
 
     def cache_need(self):
-        return self.mixer.cache_need()
+        """The mixer's needs, followed by the feed-forward's if it keeps something too (the block's need is
+        then a list, and ``forward`` deals the views out again)."""
+        need = self.mixer.cache_need()
+        extra = self.ffn.cache_need() if hasattr(self.ffn, "cache_need") else None
+        if extra is None:
+            self._views = None
+            return need
+        mixer_list = isinstance(need, (list, tuple))
+        mine = list(need) if mixer_list else ([] if need is None else [need])
+        ffn_list = isinstance(extra, (list, tuple))
+        self._views = (len(mine), mixer_list, ffn_list)
+        return mine + (list(extra) if ffn_list else [extra])
 
     def entry_link(self, step):
         """The first norm of this block as a link that the block before may fill, or None."""
@@ -35,6 +46,12 @@ class PreNormBlock(Part):
         norms are not kernels of their own where the parts allow it: the product that completes the
         residual stream writes the next norm's rows, the product that reads them applies its scale."""
         N, H = resid.shape
+        ffn_kw = {}
+        if getattr(self, "_views", None) is not None:
+            n_mixer, mixer_list, ffn_list = self._views
+            views = list(view)
+            view = views[:n_mixer] if mixer_list else (views[0] if n_mixer else None)
+            ffn_kw["view"] = views[n_mixer:] if ffn_list else views[n_mixer]
         carry = step.carry_norms
         _, mixer_emits = self.mixer.carries_norm(step) if carry else (False, False)
         ffn_accepts, ffn_emits = self.ffn.carries_norm(step) if carry else (False, False)
@@ -52,7 +69,7 @@ class PreNormBlock(Part):
             kw["emit"] = mid
         with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
             self.mixer.forward(u, resid, step, view, **kw)
-        kw = {}
+        kw = dict(ffn_kw)
         if mid is not None:
             g, kw["scale"] = mid.xg, mid
         else:

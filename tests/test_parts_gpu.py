@@ -240,6 +240,39 @@ def register_toy_parts():
                 linear(torch.relu(h).to(step.dtype), self.down[e], y)
                 resid.index_add_(0, rows, y * prob[rows, e, None])
 
+    @register("feed_forward", "toy_counted", replace=True)
+    class CountedFeedForward(Part):
+        """A feed-forward with state per sequence: relu(g Wup^T) Wdown^T times (1 + tokens seen so far / 50).
+        It overrides ``cache_need`` and is handed its view by the block."""
+        graph_safe = False
+
+        def __init__(self, hidden: int, ff: int):
+            self.hidden, self.ff = hidden, ff
+
+        def param_specs(self):
+            return {"up.weight": ParamSpec((self.ff, self.hidden)), "down.weight": ParamSpec((self.hidden, self.ff))}
+
+        def load(self, t):
+            self.up, self.down = t["up.weight"], t["down.weight"]
+
+        def cache_need(self):
+            return StateNeed((1,))
+
+        def forward(self, g, resid, step, view=None):
+            assert view is not None and tuple(view.state.shape[1:]) == (1,)
+            factor = torch.empty(g.shape[0], 1, dtype=torch.float32, device=g.device)
+            row = 0
+            for slot, n in zip(step.host_slots, step.host_lens):
+                seen = float(view.state[slot, 0])
+                factor[row:row + n, 0] = 1.0 + (seen + torch.arange(1, n + 1, device=g.device)) / 50.0
+                view.state[slot, 0] = seen + n
+                row += n
+            h = torch.empty(g.shape[0], self.ff, dtype=torch.float32, device=g.device)
+            linear(g, self.up, h)
+            y = torch.empty(g.shape[0], self.hidden, dtype=torch.float32, device=g.device)
+            linear(torch.relu(h).to(step.dtype), self.down, y)
+            resid.add_(y * factor)
+
     @register("position", "toy_stretched_rope", replace=True)
     class StretchedRope(Part):
         """Another position encoding: a rotation whose pair i turns by pos / factor^(i / pairs) * theta^(-2i/hd),
@@ -283,6 +316,9 @@ def register_toy_parts():
             if kind.endswith("+routed"):
                 kind = kind[:-len("+routed")]
                 ffn = PartSpec("toy_top1_experts", dict(hidden=H, ff=c.ff, experts=c.experts), prefix=pre + "moe.")
+            if kind.endswith("+counted"):
+                kind = kind[:-len("+counted")]
+                ffn = PartSpec("toy_counted", dict(hidden=H, ff=c.ff), prefix=pre + "cnt.")
             if kind == "sum":
                 mixer = PartSpec("toy_running_sum", dict(hidden=H, decay=c.decay), prefix=pre + "sum.")
             elif kind == "sum2":
@@ -351,6 +387,8 @@ def toy_plain(cfg, w, tokens, margins=None):
         kind, pre = cfg["layer_types"][b], f"toy.{b}."
         routed = kind.endswith("+routed")
         kind = kind[:-len("+routed")] if routed else kind
+        counted = kind.endswith("+counted")
+        kind = kind[:-len("+counted")] if counted else kind
         u = P.plain_rms_norm(x, f(pre + "n1.weight"), 1e-5)
         if kind == "attn_stretched":
             x = x + plain_stretched_attention(u, f(pre + "attn.q_proj.weight"), f(pre + "attn.k_proj.weight"),
@@ -389,6 +427,9 @@ def toy_plain(cfg, w, tokens, margins=None):
                 hid = torch.relu(g[t] @ f(pre + f"moe.experts.{e}.up.weight").T)
                 y[t] = hid @ f(pre + f"moe.experts.{e}.down.weight").T * prob[t, e]
             x = x + y
+        elif counted:
+            t = torch.arange(1, len(tokens) + 1, dtype=torch.float64)[:, None]
+            x = x + (torch.relu(g @ f(pre + "cnt.up.weight").T) @ f(pre + "cnt.down.weight").T) * (1.0 + t / 50.0)
         else:
             x = x + P.plain_swiglu(g, f(pre + "ff.w1.weight"), f(pre + "ff.w3.weight"), f(pre + "ff.w2.weight"))
     if margins is not None:
@@ -401,6 +442,8 @@ TOYS = {
     "state": dict(layer_types=["sum", "conv", "sum"], schedule=[[0, None], [1, None], [2, None]]),
     # a mixer with two states of different shape and dtype (a list of cache needs), run twice
     "two_states": dict(layer_types=["sum2", "attn"], schedule=[[0, None], [1, None], [0, None]]),
+    # a feed-forward with state of its own, beside a mixer with one state, two states, and keys and values
+    "ffn_state": dict(layer_types=["sum+counted", "sum2+counted", "attn+counted"], schedule=[[0, None], [1, None], [2, None]]),
     # the layer order is data: block 0 runs twice (same weights, a cache of its own each time)
     "twice": dict(layer_types=["conv", "attn", "sum"], schedule=[[0, None], [1, None], [0, None], [2, None], [1, None]]),
     # the last attention layer has no keys and values of its own and reads the first one's cache
