@@ -89,7 +89,8 @@ class GroupedQueryAttention(Part):
         self.position = position
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.window, self.shared_kv = int(window), bool(shared_kv)
-        self.scale = 1.0 / math.sqrt(self.hd)
+        # a position part may put a constant factor on the scores
+        self.scale = 1.0 / math.sqrt(self.hd) * float(getattr(position, "score_scale", lambda: 1.0)())
 
     def nested(self):
         return {"position": self.position}

@@ -1,5 +1,8 @@
 """Position encodings.  A mixer that rotates its queries and keys asks its
-position part for ``rotary()``; a part that encodes nothing returns None."""
+position part for ``rotary()``; a part that encodes nothing returns None.  A part may
+also define ``score_scale()``: a constant factor on the attention scores (an encoding
+that stretches its frequencies and makes up for it by sharpening the softmax); the
+mixer multiplies its 1/sqrt(head_dim) by it."""
 from __future__ import annotations
 
 from typing import Optional, Tuple
@@ -34,6 +37,9 @@ class Rope(Part):
             inv = 1.0 / (torch.tensor(self.theta, dtype=torch.float64) ** (2.0 * i / self.head_dim))
             self._inv_freq = inv.to(torch.float32).to(device)
         return self._inv_freq, self.style == "half_split"
+
+    def score_scale(self) -> float:
+        return 1.0
 
 
 @register("position", "none")

@@ -287,6 +287,9 @@ def register_toy_parts():
                 self.table = stretched_inv_freq(self.head_dim, self.theta, self.factor).to(torch.float32).to(device)
             return self.table, False
 
+        def score_scale(self):
+            return 1.0 + 0.1 * math.log(self.factor)    # the scores are sharpened to make up for the stretch
+
     @dataclass
     class ToyConfig:
         hidden_size: int
@@ -369,7 +372,7 @@ def plain_stretched_attention(u, wq, wk, wv, wo, nh, nkv, hd, theta, factor):
     out = torch.zeros(T, nh, hd, dtype=torch.float64)
     for h in range(nh):
         g = h // (nh // nkv)
-        sc = (q[:, h] @ k[:, g].T) / hd ** 0.5
+        sc = (q[:, h] @ k[:, g].T) / hd ** 0.5 * (1.0 + 0.1 * math.log(factor))
         sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
         out[:, h] = torch.softmax(sc, -1) @ v[:, g]
     return out.reshape(T, nh * hd) @ wo.T
