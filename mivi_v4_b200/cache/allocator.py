@@ -7,6 +7,7 @@ twice and never freed twice.
 """
 from __future__ import annotations
 
+import heapq
 from typing import List
 
 
@@ -22,8 +23,9 @@ class IndexPool:
         self.n = n
         self.what = what
         # lowest index first: a freed index is the next one taken, which makes
-        # reuse happen early and faults of reuse show in tests
-        self._free: List[int] = list(range(n - 1, -1, -1))
+        # reuse happen early and faults of reuse show in tests.  A heap: a sequence of thousands of
+        # pages gives them all back at once when it ends.
+        self._free: List[int] = list(range(n))
         self._held = [False] * n
 
     @property
@@ -40,7 +42,7 @@ class IndexPool:
     def take(self) -> int:
         if not self._free:
             raise CacheError(f"no free {self.what}: all {self.n} are in use")
-        i = self._free.pop()
+        i = heapq.heappop(self._free)
         if self._held[i]:
             raise CacheError(f"{self.what} {i} was on the free list while held")      # cannot happen
         self._held[i] = True
@@ -52,13 +54,13 @@ class IndexPool:
         if not self._held[i]:
             raise CacheError(f"{self.what} {i} is given back but is not held")
         self._held[i] = False
-        self._free.append(i)
-        self._free.sort(reverse=True)
+        heapq.heappush(self._free, i)
 
     def grow(self, n: int) -> None:
         if n < self.n:
             raise CacheError(f"cannot shrink the {self.what} pool from {self.n} to {n}")
-        self._free = list(range(n - 1, self.n - 1, -1)) + self._free
+        for i in range(self.n, n):
+            heapq.heappush(self._free, i)
         self._held += [False] * (n - self.n)
         self.n = n
 

@@ -214,7 +214,8 @@ class Engine:
             if chunk_items:
                 lg = self._run(chunk_items, chunk_places)
                 if lg is not None:
-                    out[torch.tensor(chunk_dst, device=self.device)] = lg
+                    # the rows' places go up like the step's other integers: no copy that the host waits for
+                    out.index_copy_(0, self.ws.stage("chunk_rows", chunk_dst).long(), lg)
             chunk_items, chunk_places, chunk_dst, room = [], [], [], self.max_step_tokens
 
         for idx, ((slot, toks), w) in enumerate(zip(items, places)):
