@@ -489,6 +489,9 @@ int k_slices(int N, int K) {
     const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
     int slices = 2 * 148 / tiles;
     slices = slices >= 8 ? 8 : (slices >= 4 ? 4 : (slices >= 2 ? 2 : 1));   // clusters of other sizes schedule worse
+    // more tiles than the GPU holds at once: still two slices (measured at 64 tokens on [65536, 2048]:
+    // 65 us against 73 with one; two blocks a multiprocessor overlap one's reduce with the other's loads)
+    if (slices < 2 && kblocks >= 8) slices = 2;
     while (slices > 1 && kblocks / slices < 2) slices >>= 1;
     return slices < 1 ? 1 : slices;
 }

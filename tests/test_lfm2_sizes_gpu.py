@@ -81,6 +81,26 @@ def test_whole_prompts(folder, models, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_a_prompt_of_several_row_tiles(folder, models, dtype):
+    """700 tokens: three row tiles of the product that pairs two multiprocessors (every projection is wide
+    enough for it at this length), the tcgen05 attention over several key blocks; whole, and as chunks of 300
+    and 400 tokens beside a second, short sequence."""
+    eng = make_engine(models, dtype)
+    a, b = prompts(V, [700, 45], seed=6)
+    s = eng.open()
+    got = eng.step([(s, a)], "all")
+    eng.close(s)
+    check(got, folder, a, dtype, "700 tokens whole")
+    sa, sb = eng.open(), eng.open()
+    first = eng.step([(sa, a[:300]), (sb, b[:20])], "all")
+    second = eng.step([(sb, b[20:]), (sa, a[300:])], "all")
+    eng.close(sa), eng.close(sb)
+    check(torch.cat([first[:300], second[25:]]), folder, a, dtype, "700 tokens in chunks of 300 and 400")
+    check(torch.cat([first[300:], second[:25]]), folder, b, dtype, "the short sequence beside it")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_last_32_one_by_one(folder, models, dtype):
     eng = make_engine(models, dtype)
     for toks in prompts(V, [1, 65, 130, 200], seed=3)[2:]:
