@@ -324,7 +324,7 @@ def main() -> int:
     nums = measure.model_numbers(model)
     pk, pk_src = peaks()
     if args.stages:
-        lens = [PREFILL_TOKENS] if args.stages == "prefill" else [args.prompt_len] * args.batch
+        lens = [args.tokens] if args.stages == "prefill" else [args.prompt_len] * args.batch
         if args.replayed:
             rep = measure.replayed_kernels(model, lens, prefill=args.stages == "prefill")
             measure.print_replayed_kernels(rep, f"{args.stages} step as the engine runs it, {len(lens)} sequence(s) of "

@@ -1,7 +1,8 @@
-// Y[M, N] = X[M, K] . W[N, K]^T for a decode step (M <= 64 tokens) on the
+// Y[M, N] = X[M, K] . W[N, K]^T for a step of few tokens (a decode step, a short prompt) on the
 // fifth-generation tensor cores, with the roles of the operands swapped: a tile
-// of 128 rows of W is the MMA's M side, the tokens are its N side (16, 32 or 64
-// columns of tensor memory).  The cost of the step is reading W once, so the
+// of 128 rows of W is the MMA's M side, the tokens are its N side (16 to 128
+// columns of tensor memory; more tokens than 128 are tiles of 128 along the grid's z, whose
+// blocks find W in the L2 cache after the first).  The cost of the step is reading W once, so the
 // kernel is a pipeline that keeps TMA loads of W in flight: one lane issues the
 // loads of 128 x 64 tiles into a ring of stages, one lane issues the MMAs and
 // hands the stages back, and nothing passes through registers until the end.
@@ -108,6 +109,8 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slices = gridDim.x, slice = blockIdx.x;
     const int n0 = blockIdx.y * BM;
+    const int mt0 = blockIdx.z * BN;                    // this block's first token (TAIL 1 and 2: always 0)
+    const int m_end = min(M, mt0 + BN);
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + slices - 1) / slices;
     const int kb0 = slice * per;
@@ -148,7 +151,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             mv_pdl_wait();
             for (int i = 0; i < first; ++i)
-                tma_load_2d(tiles0 + i * L::STAGE_BYTES + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * i);
+                tma_load_2d(tiles0 + i * L::STAGE_BYTES + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, mt0, full0 + 8 * i);
             for (int i = first; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const unsigned phase = (unsigned)(i / STAGES) & 1u;
@@ -158,11 +161,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                 for (int t = 0; t < NW; ++t)
                     tma_load_2d(a_dst + t * L::A_BYTES, &map_w, (kb0 + i) * BK, n0 + t * N, full0 + 8 * s);
-                tma_load_2d(a_dst + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, 0, full0 + 8 * s);
+                tma_load_2d(a_dst + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, mt0, full0 + 8 * s);
             }
         }
         __syncwarp();
-        if (ahead.w && ahead.bytes > 0) {
+        if (ahead.w && ahead.bytes > 0 && blockIdx.z == 0) {
             // this block's own loads are on their way: ask L2 for the block's share of what comes next
             const long long lines = ahead.bytes >> 7;
             const long long nblk = (long long)gridDim.x * gridDim.y, me = (long long)blockIdx.y * gridDim.x + blockIdx.x;
@@ -387,7 +390,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         constexpr int CH = 2;
         const int r = 4 * lane, n = n0 + r;
         const bool vec_ok = n + 3 < N && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0;   // else one by one
-        for (int m0 = slice + slices * warp; m0 < M; m0 += CH * slices * WARPS_ALL) {
+        for (int m0 = mt0 + slice + slices * warp; m0 < m_end; m0 += CH * slices * WARPS_ALL) {
             float4 part[CH][8], old[CH];
             float ss[CH];
 #pragma unroll
@@ -395,15 +398,15 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int m = m0 + c * slices * WARPS_ALL;
                 // a carried norm's sums of this token: lane p holds sums p, p + 32, ...
                 ss[c] = 0.f;
-                if (link.scale_part && m < M)
+                if (link.scale_part && m < m_end)
                     for (int p = lane; p < link.n_scale_part; p += 32)
                         ss[c] += link.scale_part[(size_t)m * link.scale_stride + p];
 #pragma unroll
                 for (int s = 0; s < 8; ++s)
-                    part[c][s] = (m < M && s < slices) ? *reinterpret_cast<const float4*>(share[s] + m * BM + r)
+                    part[c][s] = (m < m_end && s < slices) ? *reinterpret_cast<const float4*>(share[s] + (m - mt0) * BM + r)
                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
                 old[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (mode == 2 && m < M) {
+                if (mode == 2 && m < m_end) {
                     const float* o = (const float*)out + (size_t)m * ldo + n;
                     if (vec_ok) old[c] = *reinterpret_cast<const float4*>(o);
                     else {
@@ -417,7 +420,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
                 const int m = m0 + c * slices * WARPS_ALL;
-                if (m >= M) break;
+                if (m >= m_end) break;
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int s = 0; s < 8; ++s) {
@@ -485,9 +488,9 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // Slices of K (at most 8, the portable cluster size): as many blocks as fit the GPU at two a
 // multiprocessor, each with at least two K blocks.
-int k_slices(int N, int K) {
-    const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
-    int slices = 2 * 148 / tiles;
+int k_slices(int N, int K, int per_sm = 2, int token_tiles = 1) {
+    const int tiles = ((N + BM - 1) / BM) * token_tiles, kblocks = (K + BK - 1) / BK;
+    int slices = per_sm * 148 / tiles;
     slices = slices >= 8 ? 8 : (slices >= 4 ? 4 : (slices >= 2 ? 2 : 1));   // clusters of other sizes schedule worse
     // more tiles than the GPU holds at once: still two slices (measured at 64 tokens on [65536, 2048]:
     // 65 us against 73 with one; two blocks a multiprocessor overlap one's reduce with the other's loads)
@@ -511,7 +514,7 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
     }
     const int tiles = (N + BM - 1) / BM;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(slices, tiles);
+    cfg.gridDim = dim3(slices, tiles, (M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = L::TOTAL;
     cfg.stream = stream;
@@ -538,15 +541,15 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
 
 }  // namespace
 
-// Same contract as mv_gemm_small_m (modes 0-3, 1 <= M <= 64, K a multiple of 8,
-// 16-byte aligned operands; scale_part / emit_x as there, with one sum per tile of 128 rows), plus
-// the error flag of the bounded waits.
+// Same contract as mv_gemm_small_m (modes 0-3, K a multiple of 8, 16-byte aligned operands;
+// scale_part / emit_x as there, with one sum per tile of 128 rows) for any M >= 1, plus the error
+// flag of the bounded waits.
 MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
                            int K, int ldo, const float* scale_part, int n_scale_part, int scale_stride, int dim,
                            float eps, const float* emit_g, void* emit_x, float* emit_part, int emit_stride,
                            const void* next_w, long long next_bytes, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    if (K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && N % 32) return (int)cudaErrorInvalidValue;
     if (emit_x && (mode != 2 || ldo != N || !emit_g || !emit_part || emit_stride < (N + BM - 1) / BM))
         return (int)cudaErrorInvalidValue;
@@ -568,9 +571,16 @@ MV_API int mv_gemm_tc_swap(const void* X, const void* W, const float* bias, void
     // A ring of 8 stages fills a multiprocessor's shared memory with one block.  Clusters of such
     // blocks need 8 free multiprocessors in one GPC each, and only 15 fit the GPU at a time: a
     // product that is cut along K takes 4 stages, so that two blocks share a multiprocessor.
+    const Ahead ahead = {next_w, next_bytes};
+    if (M > 64) {
+        // More tokens: tiles of 128 tokens along the grid's z (three stages of 32 KB, two blocks a
+        // multiprocessor).  Tiles of 256 tokens (one block a multiprocessor) measured slower at every size:
+        // each block reads its own copy of X from the L2 cache, and that traffic grows with the tile.
+        return launch<128, 3>(X, W, bias, out, mode, M, N, K, ldo, link, ConvTail{}, HeadTail{}, ahead, err, stream,
+                              k_slices(N, K, 2, (M + 127) / 128));
+    }
     const int slices = k_slices(N, K);
     const bool deep = slices == 1;
-    const Ahead ahead = {next_w, next_bytes};
 #define MV_GO(BN) return deep ? launch<BN, 8>(X, W, bias, out, mode, M, N, K, ldo, link, ConvTail{}, HeadTail{}, ahead, err, stream, slices) \
                               : launch<BN, 4>(X, W, bias, out, mode, M, N, K, ldo, link, ConvTail{}, HeadTail{}, ahead, err, stream, slices)
     if (M <= 16) MV_GO(16);

@@ -23,11 +23,17 @@ class Workspace:
     def __init__(self, device):
         self.device = torch.device(device)
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        # the views handed out, by (name, dtype, shape): a step asks for the same ones layer after layer
+        self._views: Dict[tuple, torch.Tensor] = {}
         # counts the allocations: launches recorded while it had one value name addresses that are
         # still the buffers' addresses for as long as it keeps that value
         self.generation = 0
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        vkey = (name, dtype, tuple(shape))
+        view = self._views.get(vkey)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -37,7 +43,13 @@ class Workspace:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
-        return buf[:n].view(*shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]                # views of the buffer that was replaced
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = buf[:n].view(*shape)
+        self._views[vkey] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
@@ -54,6 +66,8 @@ class Workspace:
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]
         return buf[:n].view(*shape)
 
     def stage(self, name: str, values) -> torch.Tensor:
@@ -85,10 +99,10 @@ class Workspace:
         return dst
 
 
-# Steps in which the products around a norm carry it: those of at most 64 tokens, whose products run on
-# the two weight-streaming kernels.  Measured on the 1.2B-parameter shape: 0.85 -> 0.79 ms a step at 8
-# tokens.
-CARRY_NORMS_MAX_TOKENS = 64
+# Steps in which the products around a norm may carry it: every bfloat16 step; which products can is
+# theirs to say (``ops.linear.norm_link_ok``: the two weight-streaming kernels of at most 64 tokens, and
+# the prefill product of two multiprocessors a tile).  Measured on the 1.2B-parameter shape: 0.85 -> 0.79 ms
+# a step at 8 tokens.
 
 
 class StepContext:
@@ -116,7 +130,7 @@ class StepContext:
         self.max_len = max(self.host_lens, default=0)
         self.max_context = max((s + n for s, n in zip(starts, self.host_lens)), default=0)
         # steps of few tokens in bfloat16 let the products around a norm carry it (MIVI_CARRY_NORMS=0: never)
-        self.carry_norms = (dtype == torch.bfloat16 and 1 <= self.n_tokens <= CARRY_NORMS_MAX_TOKENS
+        self.carry_norms = (dtype == torch.bfloat16 and self.n_tokens >= 1
                             and os.environ.get("MIVI_CARRY_NORMS", "1") != "0")
         self._link = None
 

@@ -54,7 +54,7 @@ _SIGNATURES = {
         "mv_gemm_small_m_heads": [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
                                   _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-        "mv_gemm_tc_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "mv_gemm_tc_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P, _P],
         "mv_gemm_tc_swap_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q,
                                       _P, _P],
@@ -222,7 +222,15 @@ def _guard(lib: str, file: str, device, n_pages: int = 0x7fffffff, n_slots: int 
         raise KernelError(f"{name}: CUDA error {code}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  A step asks a hundred times: the two direct calls cost a
+    tenth of building a ``torch.cuda.Stream`` object each time."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -246,8 +254,15 @@ def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{name}: dtype {t.dtype}, expected {dtype}")
     if shape is not None:
-        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
-            raise KernelError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+        have = t.shape
+        bad = len(shape) != len(have)
+        if not bad:
+            for s, d in zip(shape, have):         # a plain loop: this runs hundreds of times a step
+                if s is not None and s != d:
+                    bad = True
+                    break
+        if bad:
+            raise KernelError(f"{name}: shape {tuple(have)}, expected {tuple(shape)}")
     return t.data_ptr()
 
 
@@ -614,15 +629,18 @@ def gemm_tc_pair_takes(M: int, N: int) -> bool:
     if _PREFILL_GEMM == "single" or M <= 128 or N < 128:
         return False
     tiles = -(-M // 256) * -(-N // 256)
-    return _PREFILL_GEMM == "pair" or tiles >= n_sms() // 3
+    return _PREFILL_GEMM == "pair" or tiles >= 48 * n_sms() // 148
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, swiglu: bool = False, pair: Optional[bool] = None) -> torch.Tensor:
+            accumulate: bool = False, swiglu: bool = False, pair: Optional[bool] = None,
+            scale: Optional[NormLink] = None, emit: Optional[NormLink] = None) -> torch.Tensor:
     """out = x @ w.T, bfloat16 operands, on the tcgen05 tensor cores (TMA
     loads, accumulator in tensor memory): the matrix product of prefill.
     ``pair``: True: the kernel in which two multiprocessors share a 256 x 256 tile, False: the
-    one-multiprocessor kernels, None: by shape (``gemm_tc_pair_takes``)."""
+    one-multiprocessor kernels, None: by shape (``gemm_tc_pair_takes``).  ``scale`` / ``emit``: the two
+    ends of a :class:`NormLink`; only the pair kernel carries norms (an emitting product needs N in
+    steps of 32)."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
@@ -645,10 +663,21 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
         _need(out, "gemm out", None, (M, N))
         _dt(out)
     if pair is None:
-        pair = gemm_tc_pair_takes(M, N)
+        pair = gemm_tc_pair_takes(M, N) or ((scale is not None or emit is not None) and M > 128 and N >= 128)
     elif pair and (M <= 128 or N < 128):
         raise KernelError(f"gemm_tc: the pair kernel needs more than 128 rows and at least 128 columns, got {M} x {N}")
-    entry = "mv_gemm_tc_pair" if pair else "mv_gemm_tc"
+    if pair:
+        if emit is not None and N % 32:
+            raise KernelError(f"gemm_tc: a product that emits a norm needs N in steps of 32, got {N}")
+        link = _link_args(x, M, N, K, mode, scale, emit, -(-N // 256))
+        _check(_fn("bf16", "mv_gemm_tc_pair")(
+            _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
+            out.data_ptr(), mode, M, N, K, ldo, *link, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_pair")
+        _account_gemm(x, w, out, accumulate)
+        return out
+    if scale is not None or emit is not None:
+        raise KernelError("gemm_tc: only the kernel of two multiprocessors a tile carries norms")
+    entry = "mv_gemm_tc"
     _check(_fn("bf16", entry)(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
         out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), entry)
@@ -659,17 +688,18 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
 def gemm_tc_swap(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
                  accumulate: bool = False, swiglu: bool = False, scale: Optional[NormLink] = None,
                  emit: Optional[NormLink] = None, ahead: Optional[tuple] = None) -> torch.Tensor:
-    """out = x @ w.T for at most 64 rows of x on the tcgen05 tensor cores with the
-    operands' roles swapped (rows of w on the MMA's M side): a TMA pipeline that
-    streams w once.  Same contract as ``gemm_small_m``."""
+    """out = x @ w.T on the tcgen05 tensor cores with the operands' roles swapped (rows of w
+    on the MMA's M side, up to 256 tokens a tile on its N side): a TMA pipeline that streams w
+    once, K cut over the blocks of a cluster.  Same contract as ``gemm_small_m``, for any number of
+    rows: the kernel of steps whose cost is reading the weights."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
         raise KernelError(f"gemm: x is [{M}, {K}] but w is [{N}, {K2}]")
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tc_swap: operands must be bfloat16, got {x.dtype} and {w.dtype}")
-    if not 1 <= M <= SMALL_M_MAX or K % 8 or K < 8:
-        raise KernelError(f"gemm_tc_swap: needs 1..{SMALL_M_MAX} rows and K a multiple of 8, got M={M}, K={K}")
+    if M < 1 or K % 8 or K < 8:
+        raise KernelError(f"gemm_tc_swap: needs at least one row and K a multiple of 8, got M={M}, K={K}")
     ldo = N
     if swiglu:
         if N % 32:
@@ -870,6 +900,9 @@ _n_sms = {}
 
 def n_sms(device=None) -> int:
     """Multiprocessors of the device (asked once); 148 where no device can be asked (planning on a CPU)."""
+    if device is None and _n_sms:
+        if len(_n_sms) == 1:                      # the usual case, asked many times a step
+            return next(iter(_n_sms.values()))
     if not torch.cuda.is_available():
         return 148
     key = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)

@@ -112,13 +112,37 @@ def tensor_core_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16) -> bool:
+_PREFILL_CARRY = os.environ.get("MIVI_CARRY_NORMS_PREFILL", "0") == "1"
+_MID_GEMM = os.environ.get("MIVI_MID_GEMM", "auto")              # swap | tc | auto
+
+
+def swap_takes(n_rows: int, w: torch.Tensor) -> bool:
+    """Whether a product of more than 64 rows with ``w`` goes to the kernel with swapped operands
+    (``gemm_tc_swap``: a block has 128 rows of w and 128 tokens, K cut over a cluster) rather than to
+    the prefill kernels: while its blocks are few enough that cutting K is what fills the device.
+    Measured on the five products of the 1.2B-parameter shape at 65 to 1,024 rows; the down projection
+    (K = 8,192: 16 us against 50 at 128 rows, 23 against 47 at 512) gains most.  MIVI_MID_GEMM=swap|tc
+    forces one."""
+    if _MID_GEMM != "auto":
+        return _MID_GEMM == "swap"
+    blocks = -(-w.shape[0] // 128) * -(-n_rows // 128)
+    return blocks <= 100 or (blocks <= 148 and (n_rows <= 96 or w.shape[1] >= 4096))
+
+
+def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16, emits: bool = False) -> bool:
     """Whether a product of ``n_rows`` rows with ``w`` takes a kernel that can carry a
-    norm (``scale`` / ``emit`` of :func:`linear`): one of the two of at most 64 rows.  (In the
-    tcgen05 kernel of more rows the epilogue is on the critical path: carrying the norm there
-    measured 8 % slower than the norm kernels it saved.)"""
-    return (1 <= n_rows <= K.SMALL_M_MAX and x_dtype == torch.bfloat16
-            and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
+    norm (``scale`` of :func:`linear`, or ``emit`` with ``emits``): the weight-streaming kernels do
+    both; the prefill product of two multiprocessors a tile applies a scale for nothing, but as the
+    one that emits it measured slower than the norm kernel it saves (4.70 against 4.59 ms for a
+    prompt of 2,048 tokens: with one tile a pair the epilogue's reading of the old rows is exposed),
+    so it emits only with MIVI_CARRY_NORMS_PREFILL=1."""
+    if not (x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0):
+        return False
+    if 1 <= n_rows <= K.SMALL_M_MAX or swap_takes(n_rows, w):
+        return True
+    if not K.gemm_tc_pair_takes(n_rows, w.shape[0]):
+        return False
+    return (_PREFILL_CARRY and w.shape[0] % 32 == 0) if emits else True
 
 
 _FUSED_CONV = os.environ.get("MIVI_FUSED_CONV", "1") != "0"
@@ -197,12 +221,14 @@ def linear_swiglu(x: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, *
     ``w_grouped`` alternate in groups of 16 (gate rows, then the up rows of the
     same features): the activation runs in the product's epilogue, so gate and
     up never go to memory.  Needs ``tensor_core_ok``."""
-    if scale is not None or x.shape[0] <= K.SMALL_M_MAX:
+    if x.shape[0] <= K.SMALL_M_MAX:
         fn = _small_m(x.shape[0])
         return fn(x, w_grouped, out, swiglu=True, scale=scale, **_ahead(w_grouped, fn))
+    if swap_takes(x.shape[0], w_grouped):
+        return K.gemm_tc_swap(x, w_grouped, out, swiglu=True, scale=scale, **_ahead(w_grouped, K.gemm_tc_swap))
     if _order is not None:
         _order.next_after(w_grouped)
-    return K.gemm_tc(x, w_grouped, out, swiglu=True)
+    return K.gemm_tc(x, w_grouped, out, swiglu=True, scale=scale)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
@@ -213,8 +239,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
     stream without a separate pass.  ``scale`` / ``emit`` (see ``NormLink``) need
     ``norm_link_ok`` for these operands."""
     if scale is not None or emit is not None:
-        if not norm_link_ok(x.shape[0], w, x.dtype) or x.data_ptr() % 16:
+        if not norm_link_ok(x.shape[0], w, x.dtype, emits=emit is not None) or x.data_ptr() % 16:
             raise K.KernelError("linear: these operands cannot carry a norm; ask norm_link_ok first")
+        if x.shape[0] > K.SMALL_M_MAX and swap_takes(x.shape[0], w):
+            return K.gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit,
+                                  **_ahead(w, K.gemm_tc_swap))
+        if x.shape[0] > K.SMALL_M_MAX:
+            if _order is not None:
+                _order.next_after(w)
+            return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit, pair=True)
         fn = _small_m(x.shape[0])
         return fn(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit, **_ahead(w, fn))
     if w.dtype == torch.float32 and x.dtype != torch.float32:
@@ -224,6 +257,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
         if x.shape[0] <= K.SMALL_M_MAX:
             fn = _small_m(x.shape[0])
             return fn(x, w, out, bias=bias, accumulate=accumulate, **_ahead(w, fn))
+        if swap_takes(x.shape[0], w):
+            return K.gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, **_ahead(w, K.gemm_tc_swap))
         if _order is not None:
             _order.next_after(w)
         return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate)

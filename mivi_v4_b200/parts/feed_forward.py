@@ -43,7 +43,7 @@ class SwiGLU(Part):
 
     def carries_norm(self, step):
         n = step.n_tokens
-        return (bool(self.group) and norm_link_ok(n, self.w13, step.dtype)), norm_link_ok(n, self.w2, step.dtype)
+        return (bool(self.group) and norm_link_ok(n, self.w13, step.dtype)), norm_link_ok(n, self.w2, step.dtype, emits=True)
 
     def forward(self, g, resid, step, scale=None, emit=None) -> None:
         N = g.shape[0]

@@ -49,7 +49,7 @@ class ShortConv(Part):
 
     def carries_norm(self, step):
         n = step.n_tokens
-        return norm_link_ok(n, self.w_in, step.dtype), norm_link_ok(n, self.w_out, step.dtype)
+        return norm_link_ok(n, self.w_in, step.dtype), norm_link_ok(n, self.w_out, step.dtype, emits=True)
 
     def forward(self, u, resid, step, view, scale=None, emit=None) -> None:
         N, H = u.shape
@@ -125,7 +125,7 @@ class GroupedQueryAttention(Part):
 
     def carries_norm(self, step):
         n = step.n_tokens
-        return norm_link_ok(n, self.w_qkv, step.dtype), norm_link_ok(n, self.w_o, step.dtype)
+        return norm_link_ok(n, self.w_qkv, step.dtype), norm_link_ok(n, self.w_o, step.dtype, emits=True)
 
     def forward(self, u, resid, step, view, scale=None, emit=None) -> None:
         N = u.shape[0]
