@@ -36,6 +36,25 @@ constexpr int THREADS = 192;
 
 #include "gemm_tc_store.cuh"
 
+// The consuming end of a norm carried by products (see gemm_small_m.cu; null when unused): the rows of X
+// still lack their norm's scale, so every row of the result is multiplied by
+// rsqrt(sum of the row's partial sums / dim + eps).
+struct RowScale {
+    const float* part;                 // [rows][stride], n sums of squares per row
+    int n, stride;
+    float inv_dim, eps;
+};
+__device__ __forceinline__ float row_sum(const RowScale& rs, int row, int M) {
+    float ss = 0.f;
+    if (rs.part && row < M)
+        for (int p = 0; p < rs.n; ++p) ss += rs.part[(size_t)row * rs.stride + p];
+    return ss;
+}
+__device__ __forceinline__ void scale_chunk(unsigned (&r)[32], float sc) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sc);
+}
+
 template <int BN, int STAGES>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -49,7 +68,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
-               int* __restrict__ err) {
+               const RowScale rs, int* __restrict__ err) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -118,13 +137,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
         const int row = m0 + quarter * 32 + lane;
+        const float ss = row_sum(rs, row, M);            // asked for while the products still run
         if (mbar_wait(acc_bar, 0, err, 3)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float sc = rs.part ? 1.0f / sqrtf(ss * rs.inv_dim + rs.eps) : 1.f;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned r[32];
                 tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (rs.part) scale_chunk(r, sc);
                 if (row < M) store_chunk(r, row, n0 + c0, N, mode, bias, out, ldo);
             }
         }
@@ -161,7 +183,7 @@ template <int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
-                    int* __restrict__ err) {
+                    const RowScale rs, int* __restrict__ err) {
     using L = WideLayout<STAGES>;
     constexpr int BN = L::BN;
     extern __shared__ unsigned char smem_raw[];
@@ -254,15 +276,18 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int acc = local & 1;
             const unsigned acc_phase = (unsigned)(local >> 1) & 1u;
             const int row = m0 + quarter * 32 + lane;
+            const float ss = row_sum(rs, row, M);        // asked for while the tile's products still run
             ok = mbar_wait(acc_full0 + 8 * acc, acc_phase, err, 3);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float sc = rs.part ? 1.0f / sqrtf(ss * rs.inv_dim + rs.eps) : 1.f;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= N) break;
                 unsigned r[32];
                 tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (rs.part) scale_chunk(r, sc);
                 if (row < M) store_chunk(r, row, n0 + c0, N, mode, bias, out, ldo);
             }
             // this warp has read its lanes of the accumulator: hand it back
@@ -290,7 +315,7 @@ int sm_count() {
 
 template <int STAGES>
 int launch_wide(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-                int* err, cudaStream_t stream) {
+                const RowScale& rs, int* err, cudaStream_t stream) {
     using L = WideLayout<STAGES>;
     CUtensorMap ma, mb;
     if (!tensor_map(X, M, K, BM, &ma) || !tensor_map(W, N, K, L::BN, &mb)) return (int)cudaErrorInvalidValue;
@@ -301,13 +326,13 @@ int launch_wide(const void* X, const void* W, const float* bias, void* out, int 
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + L::BN - 1) / L::BN);
     const int blocks = tiles < sm_count() ? tiles : sm_count();
-    gemm_tc_wide_kernel<STAGES><<<blocks, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, err);
+    gemm_tc_wide_kernel<STAGES><<<blocks, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, rs, err);
     return mv_launch_status();
 }
 
 template <int BN, int STAGES>
 int launch(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N, int K, int ldo,
-           int* err, cudaStream_t stream) {
+           const RowScale& rs, int* err, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
     CUtensorMap ma, mb;
     if (!tensor_map(X, M, K, BM, &ma) || !tensor_map(W, N, K, BN, &mb)) return (int)cudaErrorInvalidValue;
@@ -317,7 +342,7 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, err);
+    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, rs, err);
     return mv_launch_status();
 }
 
@@ -326,15 +351,20 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
 // mode: 0 store float32, 1 store bfloat16, 2 add into float32, 3 SwiGLU (W rows in groups
 // of 16 gate + 16 up; out is bfloat16 [M, N/2] with row stride ldo).  ``err`` points to a
 // device int that a block sets (1 producer, 2 MMA, 3 epilogue) if a wait ran out.
-// Needs K a multiple of 8 and 16-byte aligned operands.
+// Needs K a multiple of 8 and 16-byte aligned operands.  scale_part (or null): the consuming end of a
+// carried norm, [M][scale_stride] with n_scale_part sums of squares a row over ``dim`` elements.
 MV_API int mv_gemm_tc(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
-                      int K, int ldo, int* err, cudaStream_t stream) {
+                      int K, int ldo, const float* scale_part, int n_scale_part, int scale_stride, int dim, float eps,
+                      int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (mode == 3 && (N % 32 || ldo % 2)) return (int)cudaErrorInvalidValue;
-    if (N <= 64) return launch<64, 4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
+    RowScale rs = {};
+    if (scale_part) rs = RowScale{scale_part, n_scale_part, scale_stride, 1.0f / (float)dim, eps};
+    if (N <= 64) return launch<64, 4>(X, W, bias, out, mode, M, N, K, ldo, rs, err, stream);
     // wide enough for 128 x 256 tiles to give every SM work: the persistent kernel
     const long long wide_tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    if (N >= 256 && wide_tiles >= 96) return launch_wide<4>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
-    return launch<128, 3>(X, W, bias, out, mode, M, N, K, ldo, err, stream);
+    if (N >= 256 && wide_tiles >= 96) return launch_wide<4>(X, W, bias, out, mode, M, N, K, ldo, rs, err, stream);
+    return launch<128, 3>(X, W, bias, out, mode, M, N, K, ldo, rs, err, stream);
 }

@@ -53,7 +53,7 @@ _SIGNATURES = {
         "mv_gemm_small_m_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_small_m_heads": [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
                                   _P, _I, _I, _I, _F, _P, _Q, _P],
-        "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P],
         "mv_gemm_tc_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P, _P],
         "mv_gemm_tc_swap_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q,
@@ -639,7 +639,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
     loads, accumulator in tensor memory): the matrix product of prefill.
     ``pair``: True: the kernel in which two multiprocessors share a 256 x 256 tile, False: the
     one-multiprocessor kernels, None: by shape (``gemm_tc_pair_takes``).  ``scale`` / ``emit``: the two
-    ends of a :class:`NormLink`; only the pair kernel carries norms (an emitting product needs N in
+    ends of a :class:`NormLink`; every kernel here applies a scale, only the pair kernel emits (N in
     steps of 32)."""
     M, K = x.shape
     N, K2 = w.shape
@@ -663,7 +663,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
         _need(out, "gemm out", None, (M, N))
         _dt(out)
     if pair is None:
-        pair = gemm_tc_pair_takes(M, N) or ((scale is not None or emit is not None) and M > 128 and N >= 128)
+        pair = gemm_tc_pair_takes(M, N) or (emit is not None and M > 128 and N >= 128)
     elif pair and (M <= 128 or N < 128):
         raise KernelError(f"gemm_tc: the pair kernel needs more than 128 rows and at least 128 columns, got {M} x {N}")
     if pair:
@@ -675,12 +675,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Option
             out.data_ptr(), mode, M, N, K, ldo, *link, _error_flag(x.device).data_ptr(), _stream()), "mv_gemm_tc_pair")
         _account_gemm(x, w, out, accumulate)
         return out
-    if scale is not None or emit is not None:
-        raise KernelError("gemm_tc: only the kernel of two multiprocessors a tile carries norms")
+    if emit is not None:
+        raise KernelError("gemm_tc: only the kernel of two multiprocessors a tile emits a norm")
+    link = _link_args(x, M, N, K, mode, scale, None, 0)
     entry = "mv_gemm_tc"
     _check(_fn("bf16", entry)(
         _need(x, "gemm x"), _need(w, "gemm w"), _need(bias, "gemm bias", torch.float32, (N,), True),
-        out.data_ptr(), mode, M, N, K, ldo, _error_flag(x.device).data_ptr(), _stream()), entry)
+        out.data_ptr(), mode, M, N, K, ldo, *link[:5], _error_flag(x.device).data_ptr(), _stream()), entry)
     _account_gemm(x, w, out, accumulate)
     return out
 
@@ -911,7 +912,8 @@ def n_sms(device=None) -> int:
     return _n_sms[key]
 
 
-DECODE_ATTENTION_MAX_TOKENS = 128      # steps with more query tokens split the work over the queries
+DECODE_ATTENTION_MAX_TOKENS = 128      # steps with more query tokens split the work over the queries,
+DECODE_ATTENTION_MAX_QUERIES = 2       # unless no sequence brings more than this many (a large decode batch)
 
 
 def attention_decode_plan(N: int, nh: int, nkv: int, context_cap: int = 0):

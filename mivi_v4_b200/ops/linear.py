@@ -132,17 +132,15 @@ def swap_takes(n_rows: int, w: torch.Tensor) -> bool:
 def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bfloat16, emits: bool = False) -> bool:
     """Whether a product of ``n_rows`` rows with ``w`` takes a kernel that can carry a
     norm (``scale`` of :func:`linear`, or ``emit`` with ``emits``): the weight-streaming kernels do
-    both; the prefill product of two multiprocessors a tile applies a scale for nothing, but as the
-    one that emits it measured slower than the norm kernel it saves (4.70 against 4.59 ms for a
+    both; the prefill kernels apply a scale for nothing, but as the one that emits, the kernel of two
+    multiprocessors a tile measured slower than the norm kernel it saves (4.70 against 4.59 ms for a
     prompt of 2,048 tokens: with one tile a pair the epilogue's reading of the old rows is exposed),
     so it emits only with MIVI_CARRY_NORMS_PREFILL=1."""
     if not (x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0):
         return False
-    if 1 <= n_rows <= K.SMALL_M_MAX or swap_takes(n_rows, w):
+    if 1 <= n_rows <= K.SMALL_M_MAX or swap_takes(n_rows, w) or not emits:
         return True
-    if not K.gemm_tc_pair_takes(n_rows, w.shape[0]):
-        return False
-    return (_PREFILL_CARRY and w.shape[0] % 32 == 0) if emits else True
+    return _PREFILL_CARRY and w.shape[0] % 32 == 0 and K.gemm_tc_pair_takes(n_rows, w.shape[0])
 
 
 _FUSED_CONV = os.environ.get("MIVI_FUSED_CONV", "1") != "0"
@@ -247,7 +245,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optiona
         if x.shape[0] > K.SMALL_M_MAX:
             if _order is not None:
                 _order.next_after(w)
-            return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit, pair=True)
+            return K.gemm_tc(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit,
+                             pair=True if emit is not None else None)
         fn = _small_m(x.shape[0])
         return fn(x, w, out, bias=bias, accumulate=accumulate, scale=scale, emit=emit, **_ahead(w, fn))
     if w.dtype == torch.float32 and x.dtype != torch.float32:

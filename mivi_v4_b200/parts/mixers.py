@@ -150,12 +150,13 @@ class GroupedQueryAttention(Part):
                 K.qk_prepare(qkv, self.q_norm, self.k_norm, eps, inv_freq, half_split, step.positions,
                              step.seq_of, view.page_table, view.pool, q, nh, nkv, hd)
         o = self.scratch(step, "mix", (N, nh * hd), step.dtype)
-        if N <= K.DECODE_ATTENTION_MAX_TOKENS and K.attention_decode_tc_supported(step.dtype, hd, view.pool,
-                                                                                 self.window, nh, nkv):
+        # few query tokens, or many sequences with a token or two each: every query token on its own
+        few = N <= K.DECODE_ATTENTION_MAX_TOKENS or step.max_len <= K.DECODE_ATTENTION_MAX_QUERIES
+        if few and K.attention_decode_tc_supported(step.dtype, hd, view.pool, self.window, nh, nkv):
             # few query tokens, head size 64: flash decoding with both products on tcgen05
             K.attention_decode_tc(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                   self.scale, step.ws)
-        elif N <= K.DECODE_ATTENTION_MAX_TOKENS:
+        elif few:
             K.attention_decode(q, view.pool, view.page_table, step.positions, step.seq_of, o, nh, nkv, hd,
                                self.scale, self.window, step.ws)
         elif (N >= 128 * step.n_seqs and K.attention_prefill_tc_supported(step.dtype, hd, view.pool, self.window)):
@@ -171,8 +172,7 @@ class GroupedQueryAttention(Part):
         if K.profiling_on():
             # keys that the step's queries read (each query its own context), for the attention launch
             pairs = sum(n * s + n * (n + 1) // 2 for s, n in zip(step.host_starts, step.host_lens))
-            rows = sum(s + n for s, n in zip(step.host_starts, step.host_lens)) if N > K.DECODE_ATTENTION_MAX_TOKENS \
-                else pairs
+            rows = pairs if few else sum(s + n for s, n in zip(step.host_starts, step.host_lens))
             K.account(2 * nkv * hd * view.pool.element_size() * rows + 2 * N * nh * hd * q.element_size(),
                       4 * nh * hd * pairs)
         linear(o, self.w_o, resid, accumulate=True, emit=emit)

@@ -118,6 +118,9 @@ def test_gemm_small_m(kernel, M, N, Kd):
                           for H, F, sw in ((64, 48, False), (200, 96, True), (2048, 160, False), (9600, 64, True))] +
                          [("gemm_tc_swap", M, H, F, sw) for M in (65, 200, 515)
                           for H, F, sw in ((200, 96, True), (2048, 160, False))] +
+                         # the one-multiprocessor prefill kernels only apply a scale: the swapped kernel emits
+                         [("gemm_tc_one", M, H, F, sw) for M in (65, 200, 1000)
+                          for H, F, sw in ((200, 96, True), (2048, 48, False), (2048, 4096, True))] +
                          # the prefill product of two multiprocessors a tile: more than 128 rows, an emitting
                          # product's width in steps of 32, a consuming one's at least 128
                          [("gemm_tc_pair", M, H, F, sw) for M in (129, 300, 1000)
@@ -127,7 +130,9 @@ def test_gemm_carries_a_norm(kernel, M, H, F, swiglu):
     """x_new = x + z Wo^T; y = rmsnorm(x_new) * g, then y W1^T (or its SwiGLU): the first product
     writes the rows bf16(x_new * g) and the tile sums, the second applies the scale."""
     import functools
-    gemm = functools.partial(K().gemm_tc, pair=True) if kernel == "gemm_tc_pair" else getattr(K(), kernel)
+    gemm = functools.partial(K().gemm_tc, pair=True) if kernel == "gemm_tc_pair" else \
+        functools.partial(K().gemm_tc, pair=False) if kernel == "gemm_tc_one" else getattr(K(), kernel)
+    emitter = K().gemm_tc_swap if kernel == "gemm_tc_one" else gemm
     from mivi_v4_b200.ops.linear import linear
     eps = 1e-5
     z, wo = rnd(M, 72, dtype=torch.bfloat16), rnd(H, 72, dtype=torch.bfloat16, seed=1)
@@ -138,12 +143,12 @@ def test_gemm_carries_a_norm(kernel, M, H, F, swiglu):
     link = K().NormLink(None, g, eps, H, torch.empty(M, H, dtype=torch.bfloat16, device=DEV),
                         torch.full((M, -(-H // 64) * 4), float("nan"), device=DEV))
     resid = x.clone()
-    gemm(z, wo, resid, accumulate=True, emit=link)
+    emitter(z, wo, resid, accumulate=True, emit=link)
     K().check_device_errors()
     x_new = x.double() + z.double() @ wo.double().T
     assert torch.allclose(resid.double(), x_new, rtol=1e-5, atol=1e-4)
     assert link.n_partials == {"gemm_small_m": -(-H // (32 if H >= 9472 else 16)), "gemm_tc_swap": -(-H // 128),
-                               "gemm_tc_pair": -(-H // 256)}[kernel]
+                               "gemm_tc_one": -(-H // 128), "gemm_tc_pair": -(-H // 256)}[kernel]
     ss = link.partials[:, :link.n_partials].double().sum(1)
     assert torch.allclose(ss, (x_new ** 2).sum(1), rtol=1e-5)
     # the rows handed on are x_new * g, rounded once to bfloat16 (x_new itself is a float32 sum: 1e-5)
