@@ -15,7 +15,8 @@ steps; ``e2e`` is the same through ``Engine.generate`` with host token lists in
 and out; ``prefill`` is one 2,048-token prompt (the workloads: their own unequal
 prompts in one step); ``roofline`` compares the bytes a decode step must read
 (every weight once, the cache of the live sequences) with the measured copy
-bandwidth; ``points`` holds decode at batch 1 and 64 with their own fractions.
+bandwidth; ``points`` holds decode at batch 1, 64 and 256 with their own fractions, and the prefill of
+512 tokens (tokens a second).
 The timing itself is the library's (``mivi_v4_b200/measure.py``); this file adds
 the benchmark's configurations, the clocks and the line.
 """
@@ -249,7 +250,7 @@ def run_workload(which: str, steps_arg, warmup: int) -> int:
                               f"{min(lens)}..{max(lens)} (sum {T})", max(lens) + new, pk_src, nums["weight_bytes"]),
         "clocks": clocks, "gpu_launches": res["launches"],
         "prefill": {"value": T / (res["prefill_ms"] * 1e-3), "tokens": T, "ms": res["prefill_ms"], "tflops": pre_tflops,
-                    "frac": pre_tflops / pk["bf16_tflops"]},
+                    "frac": pre_tflops / pk["bf16_tflops"], "frac_of_sustained": pre_tflops / pk["bf16_tflops_sustained"]},
         "roofline": {"bound": "hbm", "bytes_per_step": point["bytes_per_step"], "achieved": point["gb_per_s"],
                      "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": point["frac"]},
         "e2e": {"value": e["decode_tokens_per_s"], "unit": "tokens/s", "prefill_tokens_per_s": e["prefill_tokens_per_s"],
@@ -267,7 +268,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help="run the first LAYERS layers of the 16 (sizes unchanged); both numbers go into config")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the end-to-end run")
+    ap.add_argument("--no-points", action="store_true", help="skip the further points and the end-to-end run")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the two further workloads instead of the default benchmark")
     ap.add_argument("--stages", default=None, choices=["decode", "prefill"],
@@ -345,17 +346,22 @@ def main() -> int:
                      + nums["attn_flops"](PREFILL_TOKENS))
         pre_tflops = pre_flops / (pre_ms * 1e-3) / 1e12
         prefill = {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
-                   "tflops": pre_tflops, "frac": pre_tflops / pk["bf16_tflops"]}
+                   "tflops": pre_tflops, "frac": pre_tflops / pk["bf16_tflops"],
+                   # frac is against the burst figure (one step, timed alone); the library product under the
+                   # power cap of a long run settles lower, for comparison:
+                   "frac_of_sustained": pre_tflops / pk["bf16_tflops_sustained"]}
 
         points, e2e = {}, None
         if not args.no_points:
-            for b in (1, 64):
+            for b in (1, 64, 256):
                 # enough steps that the first one's enqueue (the GPU idles meanwhile) does not weigh
                 r = measure.decode_run(model, [PROMPT] * b, max(32, steps), warmup, room_each=CONTEXT)
                 pt = decode_point(nums, r, b, pk)
                 points[f"decode_b{b}"] = pt["value"]
                 points[f"decode_b{b}_ms"] = pt["ms_per_step"]
                 points[f"decode_b{b}_frac"] = pt["frac"]
+            # a prompt of a quarter of the headline's length, where the step's launches weigh more
+            points["prefill_512"] = 512 / (measure.prefill_run(model, 512, reps=5, warmup=3) * 1e-3)
             # at least 256 steps: generation's ends (the prefill before the first token, the last step, which
             # has no successor enqueued behind it) then weigh as little as they do in service
             e = measure.generate_run(model, [PROMPT] * args.batch, max(steps, 256) + 1, warmup_tokens=warmup + 1)

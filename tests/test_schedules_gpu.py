@@ -186,3 +186,28 @@ def test_many_decode_shapes_share_one_workspace(folders):
     # after the first step (which sized the workspace) nothing more is held, whatever the number of shapes
     assert max(mem) - mem[0] <= (1 << 20), (mem[0], max(mem))
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name,B", [("AL", 150), ("BL", 200), ("FL", 70)])
+def test_decoding_more_sequences_than_a_token_tile(folders, name, B, dtype):
+    """Batches of 70 to 200 sequences: their prompts in one step of several hundred tokens, then one token
+    each for four steps (more rows than the 64 of the weight-streaming kernels and the 128 of a token
+    tile; the attention of a decode step stays with the kernel that takes every query token on its own)."""
+    Vn = config_of(name)["vocab_size"]
+    lens = [3 + (7 * i) % 11 for i in range(B)]
+    seqs = prompts(Vn, [n + 4 for n in lens], seed=31)
+    eng = engine(folders[name], dtype, max_tokens=64 * B, max_batch=B)
+    slots = [eng.open() for _ in range(B)]
+    eng.step([(s, t[:n]) for s, t, n in zip(slots, seqs, lens)], None)
+    got = []
+    for k in range(4):
+        got.append(eng.step([(s, [t[n + k]]) for s, t, n in zip(slots, seqs, lens)], "last"))
+    eng.check_errors()
+    for b in range(0, B, 13):                  # every thirteenth sequence against the plain implementation
+        rows = torch.stack([g[b] for g in got])
+        check(rows, folders[name], seqs[b], dtype, f"{name}: sequence {b} of {B}",
+              rows=list(range(lens[b], lens[b] + 4)))
+    for s in slots:
+        eng.close(s)
+    eng.cache.check()
