@@ -12,11 +12,13 @@
 //               block into rings of three stages each;
 //   warp 1      MMA, for either tile: S = Q K^T (128 x 128 x 64) into the tile's S
 //               columns of tensor memory, and O += P V (128 x 64 x 128) into the
-//               tile's O columns, V taken MN-major as it lies in the cache.  The
-//               order is PV(tile, j), QK(tile, j + 1), tile by tile, so that one
-//               tile's softmax runs while the tensor cores work for the other;
+//               tile's O columns, V taken MN-major as it lies in the cache.  S(tile, j + 1)
+//               is issued as soon as the softmax warps have taken S(tile, j) into
+//               registers, so both products run under the softmax arithmetic and a
+//               tile's next row of S is there when its softmax comes back for it;
 //   warps 4-11  softmax, four warps per tile, one query row per thread: the row of
-//               S from tensor memory into registers, mask, maximum, P = exp2(...)
+//               S from tensor memory into registers (then the S columns are handed
+//               back), mask, maximum, P = exp2(...), once PV of the block before is done,
 //               as bfloat16 into shared memory in the swizzled K-major layout the
 //               MMA wants, row sum in float32.  O stays in tensor memory; the
 //               reference maximum of a row is only moved when the new maximum
@@ -46,7 +48,7 @@ constexpr float RESCALE_ABOVE = 8.0f;              // log2 of how far a row's ma
 // barriers, 8 bytes each
 enum { B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + STAGES_KV, B_VFULL = B_KEMPTY + STAGES_KV,
        B_VEMPTY = B_VFULL + STAGES_KV, B_SFULL = B_VEMPTY + STAGES_KV, B_PFULL = B_SFULL + TILES,
-       B_PVDONE = B_PFULL + TILES, B_COUNT = B_PVDONE + TILES };
+       B_PVDONE = B_PFULL + TILES, B_SFREE = B_PVDONE + TILES, B_COUNT = B_SFREE + TILES };
 static_assert(B_COUNT * 8 + 8 <= 256, "barrier area");
 
 // MN-major operand (V: rows are keys = K of the product, 128 bytes = 64 values of d per row), 128-byte swizzle:
@@ -178,6 +180,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(bar(B_SFULL + t), 1);
             mbar_init(bar(B_PFULL + t), 4);
             mbar_init(bar(B_PVDONE + t), 1);
+            mbar_init(bar(B_SFREE + t), 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -241,14 +244,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int j = 0; j < nb_max && ok; ++j) {
                     const int s = j % STAGES_KV, s1 = (j + 1) % STAGES_KV;
                     const unsigned ph = (unsigned)(j / STAGES_KV) & 1u, ph1 = (unsigned)((j + 1) / STAGES_KV) & 1u;
+                    // S(t, j + 1) as soon as the tile's softmax warps hold S(t, j) in registers
+                    if (j + 1 < nb_max) {
+                        if (!(ok = mbar_wait(bar(B_KFULL + s1), ph1, err, 14))) break;
+#pragma unroll
+                        for (int t = 0; t < TILES; ++t) {
+                            if (!ok || j + 1 >= nb[t]) continue;
+                            if (!(ok = mbar_wait(bar(B_SFREE + t), (unsigned)j & 1u, err, 15))) break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            issue_qk(t, j + 1);
+                        }
+                        if (!ok) break;
+                        mma_commit(bar(B_KEMPTY + s1));
+                    }
                     if (!(ok = mbar_wait(bar(B_VFULL + s), ph, err, 17))) break;
-                    if (j + 1 < nb_max && !(ok = mbar_wait(bar(B_KFULL + s1), ph1, err, 14))) break;
-    #pragma unroll
+#pragma unroll
                     for (int t = 0; t < TILES; ++t) {
                         if (!ok || j >= nb[t]) continue;
                         if (!(ok = mbar_wait(bar(B_PFULL + t), (unsigned)j & 1u, err, 16))) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    #pragma unroll
+#pragma unroll
                         for (int k = 0; k < BKV / 16; ++k) {
                             // A: P, K-major, sub-tile k / 4 (64 keys), 32 bytes per 16 keys within it
                             const unsigned a_addr = p_s + t * P_BYTES + (k >> 2) * (BQ * 128) + (k & 3) * 32;
@@ -257,11 +272,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             mma_f16(tmem_base + O_COL0 + (unsigned)t * HD, smem_desc(a_addr), smem_desc_mn(b_addr),
                                     idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                         }
-                        if (j == nb[t] - 1) mma_commit(bar(B_PVDONE + t));
-                        if (j + 1 < nb[t]) issue_qk(t, j + 1);
+                        mma_commit(bar(B_PVDONE + t));         // P and O of this tile are free again once it is done
                     }
                     mma_commit(bar(B_VEMPTY + s));
-                    if (j + 1 < nb_max) mma_commit(bar(B_KEMPTY + s1));
                 }
             }
         }
@@ -278,7 +291,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float m = -INFINITY, l = 0.f;                        // m: the reference maximum of the row's exponentials
         bool ok = true;
         for (int j = 0; j < my_nb && ok; ++j) {
-            // S(t, j) complete, and with it every earlier MMA: P and O of block j - 1 are no longer in use
             ok = mbar_wait(bar(B_SFULL + t), (unsigned)j & 1u, err, 19);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -288,6 +300,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_ld32(s_addr + 64, s2);
             tmem_ld32(s_addr + 96, s3);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // the row is in registers: the S columns go back to the MMA warp for the next key block
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_SFREE + t));
             const int key0 = j * BKV;
             const int visible = pos - key0 + 1;               // keys of this block that the row sees
             // warp-uniform: the block reaches past the tile's first query
@@ -297,6 +313,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (mx > m && (m == -INFINITY || (mx - m) * scale_log2 > RESCALE_ABOVE)) {
                 corr = m == -INFINITY ? 0.f : ex2((m - mx) * scale_log2);
                 m = mx;
+            }
+            // P (shared memory) and O (tensor memory) are the block before's until its PV is done
+            if (j > 0) {
+                ok = mbar_wait(bar(B_PVDONE + t), (unsigned)(j - 1) & 1u, err, 20);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
@@ -330,7 +352,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PFULL + t));
         }
-        if (ok && my_nb > 0) ok = mbar_wait(bar(B_PVDONE + t), 0, err, 21);
+        if (ok && my_nb > 0) ok = mbar_wait(bar(B_PVDONE + t), (unsigned)(my_nb - 1) & 1u, err, 21);
         if (ok && my_nb > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l;
