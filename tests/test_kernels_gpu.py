@@ -361,7 +361,8 @@ def test_qk_prepare_many_tokens_heads_of_64(dtype, nh, nkv, normed, rotated):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("H,k,bias", [(8, 3, False), (200, 4, True), (64, 2, False), (16, 1, True), (24, 7, False)])
+@pytest.mark.parametrize("H,k,bias", [(8, 3, False), (200, 4, True), (64, 2, False), (16, 1, True), (24, 7, False),
+                                      (10, 3, True), (2048, 3, False)])
 def test_shortconv_any_cut(out_dtype, H, k, bias):
     """Whole sequences against the plain loop, then the same sequences cut at
     every place: the state carries the left context."""
