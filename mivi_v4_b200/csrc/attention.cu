@@ -140,17 +140,20 @@ __global__ void qk_prepare_kernel(const float* __restrict__ qkv, const float* __
 // many tokens: one warp a token.  A lane holds four consecutive elements (two pairs) of a head, so
 // a half-warp is one head and the warp takes two heads a round, eight heads' loads in flight before
 // any is used.  The rotation of a lane's two pairs at this position is worked out once for all the
-// token's heads, and the per-head sums of squares need four shuffles inside the half-warp.
+// token's heads, and the per-head sums of squares need four shuffles inside the half-warp.  With few
+// tokens (a large decode batch, a short prompt) a token's heads are dealt out to ``split`` warps, eight
+// head slots a round each, so that the step still fills the device.
 template <typename T>
 __global__ void __launch_bounds__(256)
 qk_prepare_hd64_kernel(const float* __restrict__ qkv, const float* __restrict__ wq, const float* __restrict__ wk,
                        float eps, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                        const int* __restrict__ seq_of, const int* __restrict__ page_table, int table_stride,
                        int page_shift, T* __restrict__ pool, long long page_stride, int append,
-                       T* __restrict__ q_out, int N, int nh, int nkv) {
+                       T* __restrict__ q_out, int N, int nh, int nkv, int split) {
     mv_pdl_begin();
     constexpr int HD = 64, U = 4;
-    const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int n = wid / split, part = wid - n * split;
     if (n >= N) return;
     const int lane = threadIdx.x & 31, sub = lane & 15, hsel = lane >> 4;
     const int slots = nh + 2 * nkv;
@@ -170,7 +173,9 @@ qk_prepare_hd64_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         if (mv_page_ok(page)) kv_row = pool + (size_t)page * page_stride + (size_t)(pos & (page_size - 1)) * HD;
     }
     const float* row = qkv + (size_t)n * slots * HD + 4 * sub;
-    for (int base = 0; base < slots; base += 2 * U) {
+    const int per = ((slots + split - 1) / split + 2 * U - 1) / (2 * U) * (2 * U);       // whole rounds a warp
+    const int last = min(slots, (part + 1) * per);
+    for (int base = part * per; base < last; base += 2 * U) {
         float4 v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -224,19 +229,22 @@ MV_API int mv_qk_prepare(const float* qkv, const float* wq, const float* wk, flo
     if (hd % 2 || hd > MV_MAX_HEAD_DIM || (page_size & (page_size - 1))) return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    if (hd == 64 && !half_split && N >= 256 && nkv > 0 &&
+    if (hd == 64 && !half_split && N >= 65 && nkv > 0 &&
         ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool | (uintptr_t)wq | (uintptr_t)wk) & 15) == 0) &&
         (page_stride * (dtype == MV_DT_BF16 ? 2 : 4)) % 16 == 0) {
-        // many tokens with heads of 64: a warp a token
-        const unsigned tblocks = (unsigned)((N + 7) / 8);
+        // many tokens with heads of 64: a warp a token; fewer than fill the device: several warps a token
+        const int rounds = (nh + 2 * nkv + 7) / 8;
+        int split = (2 * 148 * 8 + N - 1) / N;
+        split = split < 1 ? 1 : (split > rounds ? rounds : split);
+        const unsigned tblocks = (unsigned)(((long long)N * split + 7) / 8);
         if (dtype == MV_DT_BF16)
             mv_launch(qk_prepare_hd64_kernel<__nv_bfloat16>, tblocks, 256, 0, stream, qkv, wq, wk, eps, inv_freq,
                       positions, seq_of, page_table, table_stride, page_shift, (__nv_bfloat16*)pool, page_stride,
-                      append, (__nv_bfloat16*)q_out, N, nh, nkv);
+                      append, (__nv_bfloat16*)q_out, N, nh, nkv, split);
         else
             mv_launch(qk_prepare_hd64_kernel<float>, tblocks, 256, 0, stream, qkv, wq, wk, eps, inv_freq, positions,
                       seq_of, page_table, table_stride, page_shift, (float*)pool, page_stride, append,
-                      (float*)q_out, N, nh, nkv);
+                      (float*)q_out, N, nh, nkv, split);
         return mv_launch_status();
     }
     // many tokens: four head slots a warp, whose loads overlap; few: one, for more warps
