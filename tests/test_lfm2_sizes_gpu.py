@@ -173,6 +173,28 @@ def test_tokens_and_tiles_agree(folder, models, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("B", [100, 200])
+def test_decode_batches_beyond_a_token_tile(folder, models, dtype, B):
+    """100 and 200 sequences at these widths: a prefill step of several hundred tokens (its products cut along K
+    on the kernel with swapped operands, the norms carried from it into the prefill kernels) and decode steps of
+    more rows than the 64 of the weight-streaming kernels and the 128 of a token tile.  Every seventeenth
+    sequence is held against the plain implementation."""
+    lens = [2 + (5 * i) % 9 for i in range(B)]
+    seqs = prompts(V, [n + 3 for n in lens], seed=41)
+    eng = make_engine(models, dtype, max_tokens=64 * B, max_batch=B)
+    slots = [eng.open() for _ in range(B)]
+    first = eng.step([(s, t[:n]) for s, t, n in zip(slots, seqs, lens)], "last")
+    got = [first] + [eng.step([(s, [t[n + k]]) for s, t, n in zip(slots, seqs, lens)], "last") for k in range(3)]
+    eng.check_errors()
+    for b in range(0, B, 17):
+        rows = torch.stack([g[b] for g in got])
+        check(rows, folder, seqs[b], dtype, f"sequence {b} of {B}", rows=list(range(lens[b] - 1, lens[b] + 3)))
+    for s in slots:
+        eng.close(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_decoding_from_500_to_1100_cached_tokens(folder, models, dtype):
     """Decode steps replayed from recorded launches while the cache grows past 512 tokens (the page table
     of the recording widens: another recording) and past 1,024 (the tcgen05 decode attention starts to
