@@ -100,9 +100,9 @@ class Workspace:
 
 
 # Steps in which the products around a norm may carry it: every bfloat16 step; which products can is
-# theirs to say (``ops.linear.norm_link_ok``: the two weight-streaming kernels of at most 64 tokens, and
-# the prefill product of two multiprocessors a tile).  Measured on the 1.2B-parameter shape: 0.85 -> 0.79 ms
-# a step at 8 tokens.
+# theirs to say (``ops.linear.norm_link_ok``: every tensor-core kernel applies a carried norm's scale, the
+# weight-streaming kernels, which steps of up to about a thousand tokens use, also emit one).  Measured on
+# the 1.2B-parameter shape: 0.85 -> 0.79 ms a step at 8 tokens.
 
 
 class StepContext:
