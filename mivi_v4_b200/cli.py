@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 from typing import List
@@ -222,5 +223,19 @@ def main(argv=None) -> int:
             print(f"{a.command}: no CUDA device; this library runs on a GPU only (there is no CPU path)",
                   file=sys.stderr)
             return 2
-    return {"replay": cmd_replay, "generate": cmd_generate, "info": cmd_info, "random": cmd_random, "doctor": cmd_doctor,
-            "bench": cmd_bench}[a.command](a)
+    try:
+        return {"replay": cmd_replay, "generate": cmd_generate, "info": cmd_info, "random": cmd_random,
+                "doctor": cmd_doctor, "bench": cmd_bench}[a.command](a)
+    except Exception as e:            # the library's own errors as one line, anything else as it is
+        if type(e).__name__ in ("ConfigError", "WeightsError", "SafetensorsError", "StepError", "CacheError",
+                                "GenerationError", "KernelError", "BuildError") and not os.environ.get("MIVI_TRACEBACK"):
+            print(f"mivi {a.command}: {type(e).__name__}: {e}", file=sys.stderr)
+            return 1
+        if not isinstance(e, BrokenPipeError):
+            raise
+        # the reader of our output went away (``| head``): nothing more to say, and no traceback
+        try:
+            sys.stdout = open(os.devnull, "w")
+        except OSError:
+            pass
+        return 0

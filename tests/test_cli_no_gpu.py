@@ -36,3 +36,13 @@ def test_gpu_verbs_refuse_clearly_without_a_gpu(tmp_path, capsys):
     assert main(["generate", "-m", str(tmp_path), "--prompt-ids", "1,2"]) == 2
     err = capsys.readouterr().err
     assert "no CUDA device" in err and "Traceback" not in err
+
+
+def test_the_librarys_own_errors_are_one_line(tmp_path, capsys):
+    from mivi_v4_b200.cli import main
+    assert main(["info", "-m", str(tmp_path / "nothing_here")]) == 1
+    err = capsys.readouterr().err
+    assert err.startswith("mivi info: ConfigError: no config.json") and "Traceback" not in err
+    (tmp_path / "config.json").write_text(json.dumps(dict(TINY_B, num_hidden_layers=0)))
+    assert main(["info", "-m", str(tmp_path)]) == 1
+    assert "ConfigError" in capsys.readouterr().err
