@@ -38,11 +38,12 @@ struct NormLink {
 };
 
 // The gated short convolution of a decode step as the epilogue of its input projection (TAIL 1;
-// crates/mivi-model/src/ssm.rs:81-140): W is [3 H, K] with the rows of B, C and x one after another.
-// A block takes 128 channels, that is the same 128 rows out of each third: three W tiles a K block,
-// three accumulators in tensor memory.  After the slices are added a lane holds B, C and x of four
-// channels of a token and finishes them: B * x, the k taps over the sequence's k-1 kept values, the
-// shift of those, C *.
+// crates/mivi-model/src/ssm.rs:81-140).  The rows of W [3 H, K] come regrouped: 32 channels' B rows, then
+// their C rows, then their x rows, group after group, so that a block's one tile of 96 rows (the MMA still
+// works on 128: the last 32 rows of a stage are never loaded and their results never read) holds all three of
+// its 32 channels.  The block count, the stage size and the two blocks a multiprocessor are those of the plain
+// product.  After the slices are added a lane finishes one channel of a token: B * x, the k taps over the
+// sequence's k-1 kept values, the shift of those, C *.
 struct ConvTail {
     const float* taps;                 // [H][k]
     const float* conv_bias;            // [H] or null
@@ -79,14 +80,15 @@ struct Ahead {
 
 template <int BN, int STAGES, int TAIL>
 struct SwapLayout {
-    static constexpr int NW = TAIL == 1 ? 3 : 1;     // W tiles (and accumulators) a K block
+    static constexpr int W_ROWS = TAIL == 1 ? 96 : BM;   // rows of W that a tile loads (TAIL 1: 32 channels' B, C and x rows)
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = NW * A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TX_BYTES = W_ROWS * BK * 2 + B_BYTES;        // what the loads of a stage bring
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int CSUM_BYTES = NW * BM * BN * 4;   // [accumulator][token][row]: a warp reads consecutive words
+    static constexpr int CSUM_BYTES = BM * BN * 4;        // [token][row]: a warp reads consecutive words
     static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 8;
     static constexpr int TOTAL = (TILE_BYTES > CSUM_BYTES ? TILE_BYTES : CSUM_BYTES) + BAR_BYTES + 1024;
-    static constexpr int TMEM_COLS = NW * BN <= 32 ? 32 : (NW * BN <= 64 ? 64 : (NW * BN <= 128 ? 128 : 256));
+    static constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
 };
 
 template <int BN, int STAGES, int TAIL>
@@ -96,7 +98,6 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const NormLink link, const ConvTail tail, const HeadTail heads, const Ahead ahead,
                     int* __restrict__ err) {
     using L = SwapLayout<BN, STAGES, TAIL>;
-    constexpr int NW = L::NW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int DATA_BYTES = L::TILE_BYTES > L::CSUM_BYTES ? L::TILE_BYTES : L::CSUM_BYTES;
@@ -108,7 +109,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slices = gridDim.x, slice = blockIdx.x;
-    const int n0 = blockIdx.y * BM;
+    const int n0 = blockIdx.y * L::W_ROWS;
     const int mt0 = blockIdx.z * BN;                    // this block's first token (TAIL 1 and 2: always 0)
     const int m_end = min(M, mt0 + BN);
     const int kblocks = (K + BK - 1) / BK;
@@ -143,25 +144,20 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             const int first = nkb < STAGES ? nkb : STAGES;
             for (int i = 0; i < first; ++i) {
-                mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
-#pragma unroll
-                for (int t = 0; t < NW; ++t)          // TAIL 1: the same rows of the B, C and x thirds, N rows apart
-                    tma_load_2d(tiles0 + i * L::STAGE_BYTES + t * L::A_BYTES, &map_w, (kb0 + i) * BK, n0 + t * N,
-                                full0 + 8 * i);
+                mbar_expect_tx(full0 + 8 * i, L::TX_BYTES);
+                tma_load_2d(tiles0 + i * L::STAGE_BYTES, &map_w, (kb0 + i) * BK, n0, full0 + 8 * i);
             }
             mv_pdl_wait();
             for (int i = 0; i < first; ++i)
-                tma_load_2d(tiles0 + i * L::STAGE_BYTES + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, mt0, full0 + 8 * i);
+                tma_load_2d(tiles0 + i * L::STAGE_BYTES + L::A_BYTES, &map_x, (kb0 + i) * BK, mt0, full0 + 8 * i);
             for (int i = first; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const unsigned phase = (unsigned)(i / STAGES) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, err, 1)) break;
-                mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * s, L::TX_BYTES);
                 const unsigned a_dst = tiles0 + s * L::STAGE_BYTES;
-#pragma unroll
-                for (int t = 0; t < NW; ++t)
-                    tma_load_2d(a_dst + t * L::A_BYTES, &map_w, (kb0 + i) * BK, n0 + t * N, full0 + 8 * s);
-                tma_load_2d(a_dst + NW * L::A_BYTES, &map_x, (kb0 + i) * BK, mt0, full0 + 8 * s);
+                tma_load_2d(a_dst, &map_w, (kb0 + i) * BK, n0, full0 + 8 * s);
+                tma_load_2d(a_dst + L::A_BYTES, &map_x, (kb0 + i) * BK, mt0, full0 + 8 * s);
             }
         }
         __syncwarp();
@@ -181,13 +177,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (!mbar_wait(full0 + 8 * s, phase, err, 2)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned a_addr = tiles0 + s * L::STAGE_BYTES;
-                const unsigned b_addr = a_addr + NW * L::A_BYTES;
+                const unsigned b_addr = a_addr + L::A_BYTES;
 #pragma unroll
-                for (int t = 0; t < NW; ++t)
-#pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        mma_f16(tmem_base + (unsigned)(t * BN), smem_desc(a_addr + t * L::A_BYTES + k * 32),
-                                smem_desc(b_addr + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BK / 16; ++k)
+                    mma_f16(tmem_base, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
+                            (i > 0 || k > 0) ? 1u : 0u);
                 mma_commit(empty0 + 8 * s);
             }
             mma_commit(acc_bar);
@@ -199,7 +193,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (acc_ok) acc_ok = mbar_wait(acc_bar, 0, err, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-        for (int c0 = 0; c0 < NW * BN; c0 += (BN < 32 ? BN : 32)) {
+        for (int c0 = 0; c0 < BN; c0 += (BN < 32 ? BN : 32)) {
             unsigned v[32];
             if (acc_ok) {
                 tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
@@ -230,94 +224,41 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     constexpr int WARPS_ALL = THREADS / 32;
     if constexpr (TAIL == 1) {
-        // The convolution: an item is 128 channels of one token, four consecutive channels a lane, whose
-        // B, C and x sums lie in the three accumulators' regions of every slice.
-        const int r = 4 * lane, d = n0 + r;                  // N counts channels here
+        // An item is one token's 32 channels of this block, a channel a lane; N counts channels.
+        const int d = 32 * (int)blockIdx.y + lane;
         const int k = tail.k;
-        const bool fast = k <= 4 && (N & 3) == 0 && (ldo & 3) == 0 &&
-                          ((((uintptr_t)tail.state | (uintptr_t)tail.taps | (uintptr_t)bias | (uintptr_t)tail.conv_bias) & 15) == 0) &&
-                          (((uintptr_t)out & 7) == 0);
         for (int m = slice + slices * warp; m < M; m += slices * WARPS_ALL) {
             float ss = 0.f;
             if (link.scale_part)
                 for (int p = lane; p < link.n_scale_part; p += 32)
                     ss += link.scale_part[(size_t)m * link.scale_stride + p];
-            float4 part[3][8];
+            float part[3][8];
 #pragma unroll
             for (int t = 0; t < 3; ++t)
 #pragma unroll
                 for (int sl = 0; sl < 8; ++sl)
-                    part[t][sl] = sl < slices ? *reinterpret_cast<const float4*>(share[sl] + (t * BN + m) * BM + r)
-                                              : make_float4(0.f, 0.f, 0.f, 0.f);
-            float v[3][4];
+                    part[t][sl] = sl < slices ? share[sl][m * BM + 32 * t + lane] : 0.f;
+            float v[3] = {0.f, 0.f, 0.f};
 #pragma unroll
-            for (int t = 0; t < 3; ++t) {
-                v[t][0] = v[t][1] = v[t][2] = v[t][3] = 0.f;
+            for (int t = 0; t < 3; ++t)
 #pragma unroll
-                for (int sl = 0; sl < 8; ++sl) {
-                    v[t][0] += part[t][sl].x; v[t][1] += part[t][sl].y; v[t][2] += part[t][sl].z; v[t][3] += part[t][sl].w;
-                }
-            }
+                for (int sl = 0; sl < 8; ++sl) v[t] += part[t][sl];
             float sc = 1.f;
             if (link.scale_part) sc = 1.0f / sqrtf(mv_warp_sum(ss) * link.inv_dim + link.eps);
+            if (d >= N) continue;
+            float Bv = v[0] * sc, Cv = v[1] * sc, Xv = v[2] * sc;
+            if (bias) { Bv += bias[d]; Cv += bias[N + d]; Xv += bias[2 * N + d]; }
+            const float bx = Bv * Xv;
             float* st = tail.state + (size_t)tail.slots[m] * (k - 1) * N;
-            __nv_bfloat16* z = (__nv_bfloat16*)out + (size_t)m * ldo;
-            if (fast && d + 3 < N) {
-                // widths up to 4, everything 16-byte aligned: the kept values, the taps and the biases of the
-                // lane's four channels come in 16-byte loads that are all requested before any is used
-                float4 kept[3], tp[4], bb[3], cb = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < 3; ++j)
-                    kept[j] = j < k - 1 ? *reinterpret_cast<const float4*>(st + (size_t)j * N + d) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)               // the 4 k taps of channels d .. d + 3 lie one after another
-                    tp[j] = j < k ? *reinterpret_cast<const float4*>(tail.taps + (size_t)d * k + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int t = 0; t < 3; ++t)
-                    bb[t] = bias ? *reinterpret_cast<const float4*>(bias + t * N + d) : make_float4(0.f, 0.f, 0.f, 0.f);
-                if (tail.conv_bias) cb = *reinterpret_cast<const float4*>(tail.conv_bias + d);
-                const float* tpf = reinterpret_cast<const float*>(tp);
-                const float* kf[3] = {reinterpret_cast<const float*>(&kept[0]), reinterpret_cast<const float*>(&kept[1]),
-                                      reinterpret_cast<const float*>(&kept[2])};
-                const float* cbf = reinterpret_cast<const float*>(&cb);
-                float bxv[4], zv[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float Bv = v[0][e] * sc + reinterpret_cast<const float*>(&bb[0])[e];
-                    const float Cv = v[1][e] * sc + reinterpret_cast<const float*>(&bb[1])[e];
-                    const float Xv = v[2][e] * sc + reinterpret_cast<const float*>(&bb[2])[e];
-                    bxv[e] = Bv * Xv;
-                    float y = cbf[e];
-#pragma unroll
-                    for (int j = 0; j < 3; ++j)
-                        if (j < k - 1) y = fmaf(tpf[e * k + j], kf[j][e], y);
-                    y = fmaf(tpf[e * k + (k - 1)], bxv[e], y);
-                    zv[e] = Cv * y;
-                }
-#pragma unroll
-                for (int j = 1; j < 3; ++j)
-                    if (j < k - 1) *reinterpret_cast<float4*>(st + (size_t)(j - 1) * N + d) = kept[j];   // shift towards the older end
-                if (k > 1) *reinterpret_cast<float4*>(st + (size_t)(k - 2) * N + d) = make_float4(bxv[0], bxv[1], bxv[2], bxv[3]);
-                mv_store4(z + d, zv[0], zv[1], zv[2], zv[3]);
-                continue;
+            float y = tail.conv_bias ? tail.conv_bias[d] : 0.f;
+            for (int j = 0; j < k - 1; ++j) {
+                const float old = st[(size_t)j * N + d];
+                y = fmaf(tail.taps[d * k + j], old, y);
+                if (j > 0) st[(size_t)(j - 1) * N + d] = old;        // shift towards the older end
             }
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int c = d + e;
-                if (c >= N) break;
-                float Bv = v[0][e] * sc, Cv = v[1][e] * sc, Xv = v[2][e] * sc;
-                if (bias) { Bv += bias[c]; Cv += bias[N + c]; Xv += bias[2 * N + c]; }
-                const float bx = Bv * Xv;
-                float y = tail.conv_bias ? tail.conv_bias[c] : 0.f;
-                for (int j = 0; j < k - 1; ++j) {
-                    const float old = st[(size_t)j * N + c];
-                    y = fmaf(tail.taps[c * k + j], old, y);
-                    if (j > 0) st[(size_t)(j - 1) * N + c] = old;        // shift towards the older end
-                }
-                if (k > 1) st[(size_t)(k - 2) * N + c] = bx;
-                y = fmaf(tail.taps[c * k + (k - 1)], bx, y);
-                z[c] = __float2bfloat16_rn(Cv * y);
-            }
+            if (k > 1) st[(size_t)(k - 2) * N + d] = bx;
+            y = fmaf(tail.taps[d * k + (k - 1)], bx, y);
+            ((__nv_bfloat16*)out)[(size_t)m * ldo + d] = __float2bfloat16_rn(Cv * y);
         }
     } else if constexpr (TAIL == 2) {
         // The heads: an item is the tile's two heads of one token; a half-warp holds a head, a lane four
@@ -505,14 +446,15 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
            cudaStream_t stream, int slices) {
     using L = SwapLayout<BN, STAGES, TAIL>;
     CUtensorMap mw, mx;
-    // TAIL 1: W has three times N rows (the B, C and x thirds), N counts channels
-    if (!tensor_map(W, TAIL == 1 ? 3 * N : N, K, BM, &mw) || !tensor_map(X, M, K, BN, &mx)) return (int)cudaErrorInvalidValue;
+    // TAIL 1: W has three times N rows (B, C and x rows in groups of 32 channels), N counts channels
+    if (!tensor_map(W, TAIL == 1 ? 3 * N : N, K, L::W_ROWS, &mw) || !tensor_map(X, M, K, BN, &mx))
+        return (int)cudaErrorInvalidValue;
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, STAGES, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         attr_set = true;
     }
-    const int tiles = (N + BM - 1) / BM;
+    const int tiles = TAIL == 1 ? (N + 31) / 32 : (N + BM - 1) / BM;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(slices, tiles, (M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
@@ -601,39 +543,36 @@ NormLink scale_link(const float* scale_part, int n_scale_part, int scale_stride,
     }
     return link;
 }
-// slices of K for a product of ``tiles`` row tiles whose blocks are alone on a multiprocessor
-int k_slices_single(int tiles, int K) {
-    const int kblocks = (K + BK - 1) / BK;
-    int slices = 148 / (tiles < 1 ? 1 : tiles);
-    slices = slices >= 8 ? 8 : (slices >= 4 ? 4 : (slices >= 2 ? 2 : 1));
-    while (slices > 1 && kblocks / slices < 2) slices >>= 1;
-    return slices < 1 ? 1 : slices;
-}
 }  // namespace
 
 // A decode step's gated short convolution together with its input projection, for 1 <= M <= 64 rows
-// (one a sequence): [B | C | x] = X W^T (+ bias[3 H]) with W [3 H, K]; z[m, c] = C * (conv_bias + sum_j
-// taps[c][j] * value j of the sequence's kept B*x values followed by this token's); ``state``
-// [slots][k-1][H] is shifted and updated for slots[m].  ``z`` is bfloat16 [M, H].  scale_part etc. as
-// in mv_gemm_tc_swap.
+// (one a sequence): [B | C | x] = X W^T (+ bias[3 H]); z[m, c] = C * (conv_bias + sum_j taps[c][j] * value j of
+// the sequence's kept B*x values followed by this token's); ``state`` [slots][k-1][H] is shifted and updated
+// for slots[m].  ``z`` is bfloat16 [M, H].  W's rows come regrouped by 32 channels ([B of 32 | C of 32 | x of
+// 32] group after group; H a multiple of 32); ``bias`` in the original order [3 H].  scale_part etc. as in
+// mv_gemm_tc_swap.
 MV_API int mv_gemm_tc_swap_shortconv(const void* X, const void* W, const float* bias, const float* taps,
-                                     const float* conv_bias, float* state, const int* slots, void* z, int M, int H,
-                                     int K, int k, const float* scale_part, int n_scale_part, int scale_stride,
-                                     int dim, float eps, const void* next_w, long long next_bytes, int* err,
-                                     cudaStream_t stream) {
+                                             const float* conv_bias, float* state, const int* slots, void* z, int M,
+                                             int H, int K, int k, const float* scale_part, int n_scale_part,
+                                             int scale_stride, int dim, float eps, const void* next_w,
+                                             long long next_bytes, int* err, cudaStream_t stream) {
     if (M <= 0 || H <= 0) return 0;
-    if (M > 64 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || k < 1 || k > 16 || !taps ||
+    if (M > 64 || H % 32 || K <= 0 || K % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || k < 1 || k > 16 || !taps ||
         (!state && k > 1) || !slots)
         return (int)cudaErrorInvalidValue;
     if (scale_part && (n_scale_part <= 0 || n_scale_part > scale_stride || dim <= 0)) return (int)cudaErrorInvalidValue;
     const NormLink link = scale_link(scale_part, n_scale_part, scale_stride, dim, eps);
     const ConvTail tail = {taps, conv_bias, state, slots, k};
     const Ahead ahead = {next_w, next_bytes};
-    const int slices = k_slices_single((H + BM - 1) / BM, K);
-#define MV_GO(BN, ST) return launch<BN, ST, 1>(X, W, bias, z, 1, M, H, K, H, link, tail, HeadTail{}, ahead, err, stream, slices)
-    if (M <= 16) MV_GO(16, 4);
-    if (M <= 32) MV_GO(32, 4);
-    MV_GO(64, 3);
+    // blocks of 96 rows, two a multiprocessor: K is cut as for a plain product of as many tiles
+    const int kblocks = (K + BK - 1) / BK;
+    int slices = 2 * 148 / (H / 32);
+    slices = slices >= 8 ? 8 : (slices >= 4 ? 4 : (slices >= 2 ? 2 : 1));
+    while (slices > 1 && kblocks / slices < 2) slices >>= 1;
+#define MV_GO(BN) return launch<BN, 4, 1>(X, W, bias, z, 1, M, H, K, H, link, tail, HeadTail{}, ahead, err, stream, slices)
+    if (M <= 16) MV_GO(16);
+    if (M <= 32) MV_GO(32);
+    MV_GO(64);
 #undef MV_GO
 }
 

@@ -727,10 +727,13 @@ def gemm_tc_swap_shortconv(x: torch.Tensor, w_in: torch.Tensor, b_in: Optional[t
                            b_conv: Optional[torch.Tensor], state: torch.Tensor, slots: torch.Tensor,
                            out: torch.Tensor, *, scale: Optional[NormLink] = None,
                            ahead: Optional[tuple] = None) -> torch.Tensor:
-    """``gemm_small_m_shortconv`` for up to 64 rows, on the tcgen05 kernel with swapped operands: a block
-    takes 128 channels and keeps the B, C and x rows of them in three accumulators."""
+    """``gemm_small_m_shortconv`` for up to 64 rows, on the tcgen05 kernel with swapped operands.  The rows
+    of ``w_in`` come regrouped by :func:`group_conv_rows` (32 channels' B, C and x rows together; the width a
+    multiple of 32), so that a block's one tile holds all three of its channels."""
     M, K = x.shape
     H, k = taps.shape
+    if H % CONV_ROW_GROUP:
+        raise KernelError(f"shortconv: regrouped rows need a width in steps of {CONV_ROW_GROUP}, got {H}")
     if tuple(w_in.shape) != (3 * H, K):
         raise KernelError(f"shortconv: in_proj weight is {tuple(w_in.shape)}, expected [{3 * H}, {K}]")
     if x.dtype != torch.bfloat16 or w_in.dtype != torch.bfloat16:
@@ -745,14 +748,30 @@ def gemm_tc_swap_shortconv(x: torch.Tensor, w_in: torch.Tensor, b_in: Optional[t
     if slots.numel() < M:
         raise KernelError(f"shortconv: {slots.numel()} slots for {M} rows")
     sp, n_sp, s_stride, dim, eps = _link_args(x, M, 3 * H, K, 1, scale, None, 0)[:5]
-    _check(_fn("bf16", "mv_gemm_tc_swap_shortconv")(
+    entry = "mv_gemm_tc_swap_shortconv"
+    _check(_fn("bf16", entry)(
         _need(x, "gemm x"), _need(w_in, "gemm w"), _need(b_in, "in_proj bias", torch.float32, (3 * H,), True),
         _need(taps, "shortconv taps", torch.float32), _need(b_conv, "shortconv bias", torch.float32, (H,), True),
         state.data_ptr(), _need(slots, "slots", torch.int32), _need(out, "shortconv out", torch.bfloat16, (M, H)),
         M, H, K, k, sp, n_sp, s_stride, dim, eps, *(ahead or (None, 0)), _error_flag(x.device).data_ptr(), _stream()),
-        "mv_gemm_tc_swap_shortconv")
+        entry)
     _account_gemm(x, w_in, out, False)
     return out
+
+
+CONV_ROW_GROUP = 32
+
+
+def group_conv_rows(w_in: torch.Tensor) -> torch.Tensor:
+    """The rows of a short convolution's input projection [3 H, K] (B rows, C rows, x rows) regrouped for
+    ``gemm_tc_swap_shortconv``: the B rows of channels 0..31, their C rows, their x rows, then
+    the same of channels 32..63, and so on.  A copy; H a multiple of 32."""
+    H3, K = w_in.shape
+    H = H3 // 3
+    if H3 != 3 * H or H % CONV_ROW_GROUP:
+        raise KernelError(f"shortconv: cannot regroup the rows of a [{H3}, {K}] projection by {CONV_ROW_GROUP} channels")
+    g = CONV_ROW_GROUP
+    return w_in.view(3, H // g, g, K).permute(1, 0, 2, 3).reshape(H3, K).contiguous()
 
 
 def gemm_tc_swap_heads(x: torch.Tensor, w_qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],

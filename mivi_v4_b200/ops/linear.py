@@ -144,13 +144,20 @@ def norm_link_ok(n_rows: int, w: torch.Tensor, x_dtype: torch.dtype = torch.bflo
 
 
 _FUSED_CONV = os.environ.get("MIVI_FUSED_CONV", "1") != "0"
-# From 9 rows on the fused kernel exists too (``kernels.gemm_tc_swap_shortconv``: three accumulators a block
-# of 128 channels) but measured slower than the two kernels it replaces (decode steps of 64 sequences of
-# the 1.2B-parameter shape: 1.29 ms with it, 1.20 with its K cut in 4 instead of 8, 1.12 without): a block
-# holds 168 KB of shared memory, so one runs per multiprocessor and its phases (load, move the three
-# accumulators to shared memory, add the slices, convolve) do not overlap with another block's.
-# MIVI_FUSED_CONV_TC=1 turns it on.
+# From 9 rows on the fused kernel is the tcgen05 one over a copy of the projection whose rows are regrouped by 32
+# channels (``kernels.gemm_tc_swap_shortconv``, ``kernels.group_conv_rows``; the mixer keeps the copy).  It takes
+# ten launches out of a decode step of the 1.2B-parameter shape and leaves its time where it was (64 sequences:
+# 1,053 us with it, 1,047 without; 32: 0.99 against 0.96 ms): the convolution kernels it replaces run under the
+# products' tails anyway.  So it is off, and MIVI_FUSED_CONV_TC=1 turns it on.  (An earlier form, three
+# accumulators a block of 128 channels, was 15 % slower than the two kernels: its blocks were alone on a
+# multiprocessor.)
 _FUSED_CONV_TC = os.environ.get("MIVI_FUSED_CONV_TC", "0") == "1"
+
+
+def conv_rows_grouped(n_rows: int, w_in: torch.Tensor) -> bool:
+    """Whether the fused convolution of a step of ``n_rows`` rows reads the projection's rows regrouped
+    (``kernels.group_conv_rows``): the tcgen05 kernel's range."""
+    return _small_m(n_rows) is K.gemm_tc_swap
 
 
 def shortconv_decode_fused_ok(n_rows: int, x: torch.Tensor, w_in: torch.Tensor) -> bool:
@@ -158,20 +165,27 @@ def shortconv_decode_fused_ok(n_rows: int, x: torch.Tensor, w_in: torch.Tensor) 
     projection (``kernels.gemm_small_m_shortconv``): the steps whose products take the
     register-streaming kernel, bfloat16 operands.  One launch less a layer; MIVI_FUSED_CONV=0
     keeps the two kernels."""
-    return (_FUSED_CONV and not K.DEBUG_CHECKS and 1 <= n_rows <= K.SMALL_M_MAX and tensor_core_ok(x, w_in)
-            and (n_rows <= K.SHORTCONV_FUSED_MAX_ROWS if _small_m(n_rows) is K.gemm_small_m else _FUSED_CONV_TC))
+    if not (_FUSED_CONV and not K.DEBUG_CHECKS and 1 <= n_rows <= K.SMALL_M_MAX and tensor_core_ok(x, w_in)):
+        return False
+    if _small_m(n_rows) is K.gemm_small_m:
+        return n_rows <= K.SHORTCONV_FUSED_MAX_ROWS
+    return _FUSED_CONV_TC and (w_in.shape[0] // 3) % K.CONV_ROW_GROUP == 0
 
 
 def linear_shortconv_decode(x: torch.Tensor, w_in: torch.Tensor, b_in, taps, b_conv, state, slots, out, *,
-                            scale: Optional[K.NormLink] = None) -> torch.Tensor:
+                            scale: Optional[K.NormLink] = None, grouped: bool = False) -> torch.Tensor:
     """The input projection and the convolution of a decode step in one kernel (the register-streaming
-    one up to 8 rows, the tcgen05 one from there to 64); needs ``shortconv_decode_fused_ok``."""
+    one up to 8 rows, the tcgen05 one from there to 64); needs ``shortconv_decode_fused_ok``.  ``grouped``:
+    ``w_in`` is the regrouped copy that ``conv_rows_grouped`` asks for."""
     ahead = {}
     if _order is not None:
         nxt = _order.next_after(w_in)
         ahead = {"ahead": nxt} if nxt is not None else {}
-    fn = K.gemm_tc_swap_shortconv if _small_m(x.shape[0]) is K.gemm_tc_swap else K.gemm_small_m_shortconv
-    return fn(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
+    if _small_m(x.shape[0]) is K.gemm_tc_swap:
+        if not grouped:
+            raise K.KernelError("linear_shortconv_decode: the tcgen05 kernel reads the regrouped projection")
+        return K.gemm_tc_swap_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
+    return K.gemm_small_m_shortconv(x, w_in, b_in, taps, b_conv, state, slots, out, scale=scale, **ahead)
 
 
 _FUSED_QK = os.environ.get("MIVI_FUSED_QK", "1") != "0"

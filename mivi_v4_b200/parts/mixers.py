@@ -8,7 +8,7 @@ import torch
 
 from ..cache.needs import KVNeed, StateNeed
 from ..ops import kernels as K
-from ..ops.linear import (heads_fused_ok, linear, linear_heads, linear_shortconv_decode, norm_link_ok,
+from ..ops.linear import (conv_rows_grouped, heads_fused_ok, linear, linear_heads, linear_shortconv_decode, norm_link_ok,
                           shortconv_decode_fused_ok)
 from .base import Part
 from .registry import register
@@ -41,6 +41,7 @@ class ShortConv(Part):
 
     def load(self, t) -> None:
         self.w_in, self.w_out = t["in_proj.weight"], t["out_proj.weight"]
+        self.w_in_grouped = None
         self.taps = t["conv.weight"].reshape(self.hidden, self.kernel).contiguous()
         self.b_in, self.b_conv, self.b_out = t.get("in_proj.bias"), t.get("conv.bias"), t.get("out_proj.bias")
 
@@ -55,9 +56,15 @@ class ShortConv(Part):
         N, H = u.shape
         z = self.scratch(step, "mix", (N, H), step.dtype)
         if step.is_decode and N == step.n_seqs and shortconv_decode_fused_ok(N, u, self.w_in):
-            # a few sequences, one token each: the convolution is the projection's epilogue
-            linear_shortconv_decode(u, self.w_in, self.b_in, self.taps, self.b_conv, view.state, step.slots, z,
-                                    scale=scale)
+            # a few sequences, one token each: the convolution is the projection's epilogue (from 9 sequences
+            # on over a copy of the projection whose rows are regrouped, made when first wanted)
+            w_in, grouped = self.w_in, conv_rows_grouped(N, self.w_in)
+            if grouped:
+                if self.w_in_grouped is None:
+                    self.w_in_grouped = K.group_conv_rows(self.w_in)
+                w_in = self.w_in_grouped
+            linear_shortconv_decode(u, w_in, self.b_in, self.taps, self.b_conv, view.state, step.slots, z,
+                                    scale=scale, grouped=grouped)
             linear(z, self.w_out, resid, bias=self.b_out, accumulate=True, emit=emit)
             return
         p = self.scratch(step, "proj", (N, 3 * H), torch.float32)

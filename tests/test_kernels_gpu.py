@@ -638,20 +638,28 @@ def test_shortconv_long_steps(out_dtype, H, k, bias):
             assert torch.allclose(torch.cat(a).double().cpu(), b_, rtol=tol, atol=tol), cuts
 
 
-@pytest.mark.parametrize("kernel,M", [("mma", 1), ("mma", 3), ("mma", 8), ("tc", 1), ("tc", 8), ("tc", 9), ("tc", 20),
-                                      ("tc", 33), ("tc", 64)])
-@pytest.mark.parametrize("H,Kd,k,bias,scaled", [(16, 8, 3, False, False), (200, 72, 4, True, True), (40, 2048, 1, True, False),
-                                                (2048, 2048, 3, False, True), (24, 8200, 7, False, False),
-                                                (300, 264, 2, True, True)])
+_CONV_SHAPES = [(16, 8, 3, False, False), (200, 72, 4, True, True), (40, 2048, 1, True, False),
+                (2048, 2048, 3, False, True), (24, 8200, 7, False, False), (300, 264, 2, True, True)]
+# the tcgen05 kernel over regrouped rows: widths in steps of 32
+_CONV_SHAPES_GROUPED = [(32, 8, 3, False, False), (96, 72, 4, True, True), (64, 2048, 1, True, False),
+                        (2048, 2048, 3, False, True), (160, 8200, 7, False, False), (1536, 264, 2, True, True)]
+
+
+@pytest.mark.parametrize("kernel,M,H,Kd,k,bias,scaled",
+                         [("mma", M) + sh for M in (1, 3, 8) for sh in _CONV_SHAPES] +
+                         [("tc", M) + sh for M in (1, 8, 9, 20, 33, 64) for sh in _CONV_SHAPES_GROUPED])
 def test_gemm_small_m_shortconv(kernel, M, H, Kd, k, bias, scaled):
     """The decode step's convolution as the epilogue of its input projection (the register-streaming
-    kernel up to 8 rows, the tcgen05 kernel with three accumulators up to 64): several steps in a
-    row over slots in any order, against a float64 expression and against the two separate kernels
-    (same outputs within rounding, same kind of state)."""
+    kernel up to 8 rows; the tcgen05 kernel up to 64, over rows regrouped by 32 channels): several steps in a row over slots in any order, against a float64 expression
+    and against the two separate kernels (same outputs within rounding, same kind of state)."""
     from mivi_v4_b200.ops.kernels import NormLink
     fused = K().gemm_small_m_shortconv if kernel == "mma" else K().gemm_tc_swap_shortconv
     g = torch.Generator().manual_seed(H + Kd + k + M)
     w_in = (torch.randn(3 * H, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16).to(DEV)
+    w_fused = w_in
+    if kernel == "tc":
+        w_fused = K().group_conv_rows(w_in)
+        assert torch.equal(w_fused[32:64], w_in[H:H + 32]) and torch.equal(w_fused[64:96], w_in[2 * H:2 * H + 32])
     taps = torch.randn(H, k, generator=g).to(DEV)
     b_in = torch.randn(3 * H, generator=g).to(DEV) if bias else None
     b_conv = torch.randn(H, generator=g).to(DEV) if bias else None
@@ -685,7 +693,7 @@ def test_gemm_small_m_shortconv(kernel, M, H, Kd, k, bias, scaled):
         hist = torch.cat([hist[:, 1:], bx[:, None]], dim=1) if k > 1 else hist
 
         out = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
-        fused(x, w_in, b_in, taps, b_conv, state, slots, out, scale=link)
+        fused(x, w_fused, b_in, taps, b_conv, state, slots, out, scale=link)
         K().check_device_errors()
         tol = dict(rtol=2e-2, atol=2e-2 * float(want.abs().max()))
         assert torch.allclose(out.double().cpu(), want, **tol), step
