@@ -240,7 +240,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (n0 + 32 * c >= N) break;
                     unsigned r[32];
                     tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + 32 * c), r);
-                    if (link.emit_x) request(c + 1, nxt);
+                    if (link.emit_x && c + 1 < BN / 32) request(c + 1, nxt);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     // 16-byte piece q of row ``lane`` lies at piece q ^ (lane % 8): no bank is asked twice, neither here nor below
 #pragma unroll
